@@ -1,0 +1,318 @@
+"""ctypes binding of include/cake_b200.h and the reference-shaped operators."""
+import ctypes
+import os
+
+import numpy as np
+
+KMN, MKN, NKM, NA = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_TF32X3, KERNEL_FFMA = 0, 1, 2
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libcake_b200.so")
+_lib = None
+
+_fp = ctypes.POINTER(ctypes.c_float)
+_i, _vp, _sz = ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+
+
+class CakeError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, code, text):
+        super().__init__("cake_b200 status %d: %s" % (code, text))
+        self.code = code
+
+
+class Stats(ctypes.Structure):
+    """cakeb200_stats: timings (ms, CUDA events) and choices of the last call."""
+    _fields_ = [("ms_h2d", ctypes.c_float), ("ms_prepass", ctypes.c_float), ("ms_gemm", ctypes.c_float),
+                ("ms_d2h", ctypes.c_float), ("kernel", _i), ("sched", _i), ("tile_m", _i), ("tile_n", _i),
+                ("tile_k", _i), ("launches", _i)]
+
+    def as_dict(self):
+        return {k: getattr(self, k) for k, _ in self._fields_}
+
+
+class Cntx(ctypes.Structure):
+    """cakeb200_cntx: the fields of cake_cntx_t the block-sizing formulas read
+    (reference include/common.h:138-151)."""
+    _fields_ = [("alpha_n", ctypes.c_double), ("mr", _i), ("nr", _i), ("L1", _i), ("L2", _i), ("L3", _i),
+                ("ncores", _i)]
+
+    @classmethod
+    def make(cls, L1, L2, L3, ncores, mr=6, nr=16):
+        c = cls()
+        c.alpha_n, c.mr, c.nr, c.L1, c.L2, c.L3, c.ncores = 1.0, mr, nr, L1, L2, L3, ncores
+        return c
+
+
+class BlkDims(ctypes.Structure):
+    """cakeb200_blk_dims == blk_dims_t (reference include/common.h:108-135)."""
+    _names = ["m_c", "k_c", "n_c", "m_c1", "k_c1", "n_c1", "m_c1_last_core", "n_c1_last_core", "k_c1_last_core",
+              "mr_rem", "nr_rem", "k_rem", "p_l", "pm_l", "pn_l", "pm", "pn", "m_pad", "k_pad", "n_pad", "Mb", "Kb",
+              "Nb", "M_padded", "N_padded", "sch"]
+    _fields_ = [(n, _i) for n in _names]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n in self._names}
+
+
+_SIGNATURES = {
+    "cakeb200_last_error": (ctypes.c_char_p, []),
+    "cakeb200_get_stats": (None, [ctypes.POINTER(Stats)]),
+    "cakeb200_device_count": (_i, []),
+    "cakeb200_query_cntx": (_i, [ctypes.POINTER(Cntx)]),
+    "cakeb200_sgemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "cakeb200_sgemm_async": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "cakeb200_sgemm_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "cakeb200_sp_sgemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "cakeb200_conv2d": (_i, [_vp, _vp, _vp] + [_i] * 10 + [_vp]),
+    "cakeb200_im2col": (_i, [_vp, _vp] + [_i] * 8 + [_vp]),
+    "cakeb200_init_block_dims": (_i, [_i, _i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _i, _i, _i, _i]),
+    "cakeb200_derive_schedule": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(Cntx)]),
+    "cakeb200_set_schedule": (_i, [_i, _i, _i, _i]),
+    "cakeb200_packed_A_size": (_sz, [_i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _i]),
+    "cakeb200_packed_B_size": (_sz, [_i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx)]),
+    "cakeb200_packed_C_size": (_sz, [_i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _i]),
+}
+for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
+    _SIGNATURES["cakeb200_" + _n] = (_i, [_vp, _vp, _i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _vp])
+
+EXPORTED_SYMBOLS = sorted(_SIGNATURES)
+
+
+def library_path():
+    return _LIB_PATH
+
+
+def lib():
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError("libcake_b200.so is missing: run `python -m cake_on_cpu_b200.build` "
+                               "(there is no CPU fallback)")
+        L = ctypes.CDLL(_LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise CakeError(rc, lib().cakeb200_last_error().decode(errors="replace"))
+
+
+def last_stats():
+    s = Stats()
+    lib().cakeb200_get_stats(ctypes.byref(s))
+    return s.as_dict()
+
+
+def device_count():
+    return lib().cakeb200_device_count()
+
+
+def _is_torch(x):
+    return type(x).__module__.startswith("torch")
+
+
+def _ptr(x):
+    """Raw address of a contiguous float32 numpy array or torch tensor."""
+    if _is_torch(x):
+        import torch
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise TypeError("expected a contiguous float32 tensor")
+        return ctypes.c_void_p(x.data_ptr())
+    if not isinstance(x, np.ndarray) or x.dtype != np.float32 or not x.flags["C_CONTIGUOUS"]:
+        raise TypeError("expected a C-contiguous float32 array")
+    return ctypes.c_void_p(x.ctypes.data)
+
+
+def _empty_like_kind(ref, shape):
+    if _is_torch(ref):
+        import torch
+        return torch.empty(shape, dtype=torch.float32, device=ref.device)
+    return np.empty(shape, np.float32)
+
+
+def _stream_of(x, stream):
+    if stream is not None:
+        return ctypes.c_void_p(int(stream))
+    if _is_torch(x) and x.is_cuda:
+        import torch
+        return ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    return None
+
+
+# ------------------------------------------------------------------ the product
+
+def cake_sgemm(A, B, C=None, p=1, cake_cntx=None, packedA=False, packedB=False, alpha=1.0, beta=0.0, sch=NA,
+               kernel=KERNEL_AUTO, stream=None):
+    """C = A @ B through the reference's operator interface
+    (cake_sgemm, reference include/cake.h:12-14, src/cake_sgemm.cpp:9-175).
+
+    ``alpha`` is accepted and ignored and ``beta`` is a flag, exactly as in the
+    reference: K-first overwrites C, M-first / N-first add A@B to C when
+    ``beta != 0``.  ``sch`` picks the tile order (NA = derive from the shape).
+    ``p`` and ``cake_cntx`` are accepted for signature parity; one process
+    drives one GPU here.  Returns C.
+    """
+    if packedA or packedB:
+        raise NotImplementedError("pre-packed operands go through the C++ API (include/cake.h)")
+    M, K = A.shape
+    K2, N = B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if C is None:
+        C = _empty_like_kind(A, (M, N))
+        beta = 0.0
+    accumulate = 1 if (beta != 0 and sch in (MKN, NKM)) else 0
+    if beta != 0 and sch == NA:
+        # the schedule decides whether beta is honoured; resolve it the way the library will
+        accumulate = 1 if last_schedule_for(M, N, K) != KMN else 0
+    _check(lib().cakeb200_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, accumulate, sch, kernel, _stream_of(C, stream)))
+    return C
+
+
+def last_schedule_for(M, N, K):
+    """Schedule the library derives for a shape on the current device."""
+    c = cake_query_cntx()
+    c.ncores = 1
+    return init_block_dims(M, N, K, 1, c, NA).sch
+
+
+def cake_sgemm_async(dA, dB, dC, M, N, K, accumulate=0, sch=NA, kernel=KERNEL_AUTO, stream=0):
+    """Enqueue C = A @ B on ``stream`` for raw device addresses; no synchronisation."""
+    _check(lib().cakeb200_sgemm_async(ctypes.c_void_p(dA), ctypes.c_void_p(dB), ctypes.c_void_p(dC), M, N, K,
+                                      accumulate, sch, kernel, ctypes.c_void_p(stream)))
+
+
+def cake_sgemm_batched(A, B, C=None, kernel=KERNEL_AUTO, stream=None):
+    """Batch of independent products, A[b] @ B[b] (the reference's small-matrix
+    path, reference include/cake.h:52-72, is one cake_sgemm per item)."""
+    batch, M, K = A.shape
+    _, _, N = B.shape
+    if C is None:
+        C = _empty_like_kind(A, (batch, M, N))
+    _check(lib().cakeb200_sgemm_batched(_ptr(A), _ptr(B), _ptr(C), M, N, K, batch, kernel, _stream_of(C, stream)))
+    return C
+
+
+def cake_sp_sgemm(A, B, C=None, kernel=KERNEL_FFMA, stream=None):
+    """C = A @ B for a mostly-zero A (row-skipping product of the reference's
+    sparse microkernel, reference src/kernels/haswell/sparse.cpp:7-131)."""
+    M, K = A.shape
+    _, N = B.shape
+    if C is None:
+        C = _empty_like_kind(A, (M, N))
+    _check(lib().cakeb200_sp_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, kernel, _stream_of(C, stream)))
+    return C
+
+
+def cake_conv2d(x, w, stride=1, pad=0, out=None, kernel=KERNEL_AUTO, stream=None):
+    """NCHW convolution via im2col + SGEMM (reference examples/cake_conv.cpp:1007-1066)."""
+    b, cin, H, W = x.shape
+    cout, cin2, hf, wf = w.shape
+    if cin != cin2:
+        raise ValueError("channel mismatch")
+    Ho, Wo = (H + 2 * pad - hf) // stride + 1, (W + 2 * pad - wf) // stride + 1
+    if out is None:
+        out = _empty_like_kind(x, (b, cout, Ho, Wo))
+    _check(lib().cakeb200_conv2d(_ptr(x), _ptr(w), _ptr(out), b, cin, H, W, cout, hf, wf, stride, pad, kernel,
+                                 _stream_of(out, stream)))
+    return out
+
+
+def im2col(x, hf, wf, stride=1, pad=0, stream=None):
+    """im_2_col (reference examples/cake_conv.cpp:1178-1213) with batch and padding."""
+    b, cin, H, W = x.shape
+    Ho, Wo = (H + 2 * pad - hf) // stride + 1, (W + 2 * pad - wf) // stride + 1
+    col = _empty_like_kind(x, (cin * hf * wf, b * Ho * Wo))
+    _check(lib().cakeb200_im2col(_ptr(x), _ptr(col), b, cin, H, W, hf, wf, stride, pad, _stream_of(col, stream)))
+    return col
+
+
+# ------------------------------------------------------- context and tiling
+
+def cake_query_cntx():
+    c = Cntx()
+    _check(lib().cakeb200_query_cntx(ctypes.byref(c)))
+    return c
+
+
+def init_block_dims(M, N, K, p, cake_cntx, sch=NA, mcu=0, kcu=0, ncu=0):
+    x = BlkDims()
+    _check(lib().cakeb200_init_block_dims(M, N, K, p, ctypes.byref(x), ctypes.byref(cake_cntx), sch, mcu, kcu, ncu))
+    return x
+
+
+def derive_schedule(M, N, K, p, mc_ret, cake_cntx):
+    return lib().cakeb200_derive_schedule(M, N, K, p, mc_ret, ctypes.byref(cake_cntx))
+
+
+def set_schedule(sch, M, N, K):
+    return lib().cakeb200_set_schedule(sch, M, N, K)
+
+
+def cake_sgemm_packed_A_size(M, K, p, x, cake_cntx, sch):
+    return lib().cakeb200_packed_A_size(M, K, p, ctypes.byref(x), ctypes.byref(cake_cntx), sch)
+
+
+def cake_sgemm_packed_B_size(K, N, p, x, cake_cntx):
+    return lib().cakeb200_packed_B_size(K, N, p, ctypes.byref(x), ctypes.byref(cake_cntx))
+
+
+def cake_sgemm_packed_C_size(M, N, p, x, cake_cntx, sch):
+    return lib().cakeb200_packed_C_size(M, N, p, ctypes.byref(x), ctypes.byref(cake_cntx), sch)
+
+
+# ------------------------------------------------------------------ packing
+
+def _pack(name, mat, packed, d0, d1, p, x, cake_cntx, stream):
+    fn = getattr(lib(), "cakeb200_" + name)
+    _check(fn(_ptr(mat), _ptr(packed), d0, d1, p, ctypes.byref(x), ctypes.byref(cake_cntx), _stream_of(packed, stream)))
+
+
+def pack_A(A, M, K, p, x, cake_cntx, A_p=None, stream=None):
+    if A_p is None:
+        A_p = _empty_like_kind(A, (cake_sgemm_packed_A_size(M, K, p, x, cake_cntx, x.sch) // 4,))
+    _pack("pack_A", A, A_p, M, K, p, x, cake_cntx, stream)
+    return A_p
+
+
+def pack_B(B, K, N, p, x, cake_cntx, B_p=None, stream=None):
+    if B_p is None:
+        B_p = _empty_like_kind(B, (cake_sgemm_packed_B_size(K, N, p, x, cake_cntx) // 4,))
+    _pack("pack_B", B, B_p, K, N, p, x, cake_cntx, stream)
+    return B_p
+
+
+def pack_C(C, M, N, p, x, cake_cntx, C_p=None, stream=None):
+    if C_p is None:
+        C_p = _empty_like_kind(C, (cake_sgemm_packed_C_size(M, N, p, x, cake_cntx, x.sch) // 4,))
+    _pack("pack_C", C, C_p, M, N, p, x, cake_cntx, stream)
+    return C_p
+
+
+def unpack_C(C_p, M, N, p, x, cake_cntx, C=None, stream=None):
+    if C is None:
+        C = _empty_like_kind(C_p, (M, N))
+    _pack("unpack_C", C, C_p, M, N, p, x, cake_cntx, stream)
+    return C
+
+
+def unpack_A(A_p, M, K, p, x, cake_cntx, A=None, stream=None):
+    if A is None:
+        A = _empty_like_kind(A_p, (M, K))
+    _pack("unpack_A", A, A_p, M, K, p, x, cake_cntx, stream)
+    return A
+
+
+def unpack_B(B_p, K, N, p, x, cake_cntx, B=None, stream=None):
+    if B is None:
+        B = _empty_like_kind(B_p, (K, N))
+    _pack("unpack_B", B, B_p, K, N, p, x, cake_cntx, stream)
+    return B

@@ -1,0 +1,534 @@
+// The C ABI (include/cake_b200.h): argument checking, host/device pointer
+// handling, kernel selection and timing.  No arithmetic happens here and there
+// is no CPU fallback: every product is computed by a kernel of this library.
+#include <algorithm>
+#include <climits>
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cakeb200 {
+
+int pack_A_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
+int pack_B_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
+int pack_C_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
+size_t sparse_scratch_bytes(int M, int K);
+int launch_sp_sgemm(const float*, const float*, float*, int, int, int, void*, cudaStream_t, int*);
+int launch_im2col(const float*, float*, int, int, int, int, int, int, int, int, cudaStream_t);
+
+namespace {
+thread_local char g_error[512] = "";
+thread_local cakeb200_stats g_stats = {};
+std::mutex g_state_mutex;
+constexpr int MAX_DEVICES = 64;
+DeviceState* g_states[MAX_DEVICES] = {};
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+DeviceState* device_state() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        cudaGetLastError();
+        set_error("no CUDA device is current");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    if (g_states[dev]) return g_states[dev];
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaGetDeviceProperties failed");
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+        return nullptr;
+    }
+    DeviceState* st = new DeviceState();
+    st->device = dev;
+    st->sm_count = prop.multiProcessorCount;
+    bool ok = cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i < 6 && ok; i++) ok = cudaEventCreate(&st->ev[i]) == cudaSuccess;
+    ok = ok && cudaMalloc((void**) &st->status_word, 256) == cudaSuccess;
+    ok = ok && cudaMemset(st->status_word, 0, 256) == cudaSuccess;
+    if (!ok) {
+        set_error("device state creation failed: %s", cudaGetErrorString(cudaGetLastError()));
+        delete st;
+        return nullptr;
+    }
+    g_states[dev] = st;
+    return st;
+}
+
+// Grow-only arena.  Growing waits for the device first: an earlier call's
+// kernels may still be reading the old block.
+static int grow(void** p, size_t* have, size_t need) {
+    if (need <= *have) return CAKEB200_OK;
+    CAKE_CUDA_OK(cudaDeviceSynchronize());
+    if (*p) CAKE_CUDA_OK(cudaFree(*p));
+    *p = nullptr;
+    *have = 0;
+    const size_t want = (need + (size_t(1) << 21) - 1) & ~((size_t(1) << 21) - 1);
+    CAKE_CUDA_OK(cudaMalloc(p, want));
+    *have = want;
+    return CAKEB200_OK;
+}
+int ensure_scratch(DeviceState* st, size_t bytes) { return grow(&st->scratch, &st->scratch_bytes, bytes); }
+
+namespace {
+
+bool on_device(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// A matrix argument that may live on the host: `dev` is where kernels see it.
+struct Operand {
+    const void* user = nullptr;
+    void* dev = nullptr;
+    size_t bytes = 0;
+    bool host = false;
+};
+
+int stage_in(DeviceState* st, int slot, Operand& op, const void* user, size_t bytes, bool copy, cudaStream_t s) {
+    op.user = user;
+    op.bytes = bytes;
+    op.host = !on_device(user);
+    if (!op.host) {
+        op.dev = const_cast<void*>(user);
+        return CAKEB200_OK;
+    }
+    int rc = grow(&st->staging[slot], &st->staging_bytes[slot], bytes);
+    if (rc) return rc;
+    op.dev = st->staging[slot];
+    if (copy) CAKE_CUDA_OK(cudaMemcpyAsync(op.dev, user, bytes, cudaMemcpyHostToDevice, s));
+    return CAKEB200_OK;
+}
+
+int stage_out(const Operand& op, cudaStream_t s) {
+    if (op.host) CAKE_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(op.user), op.dev, op.bytes, cudaMemcpyDeviceToHost, s));
+    return CAKEB200_OK;
+}
+
+int check_status_word(DeviceState* st, cudaStream_t s) {
+    int host_word[4] = {0, 0, 0, 0};
+    CAKE_CUDA_OK(cudaMemcpyAsync(host_word, st->status_word, sizeof(host_word), cudaMemcpyDeviceToHost, s));
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    if (host_word[0] != 0) {
+        set_error("device-side wait gave up (code %d, where %d, info %d)", host_word[0], host_word[1], host_word[2]);
+        cudaMemsetAsync(st->status_word, 0, 256, s);
+        cudaStreamSynchronize(s);
+        return CAKEB200_ERR_DEVICE_TIMEOUT;
+    }
+    return CAKEB200_OK;
+}
+
+void b200_cntx(DeviceState* st, cakeb200_cntx* c) {
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, st->device);
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    int ndev = 0;
+    cudaGetDeviceCount(&ndev);
+    c->alpha_n = 1.0;
+    c->mr = 128;
+    c->nr = 256;
+    c->L1 = (int) prop.sharedMemPerMultiprocessor;
+    c->L2 = prop.l2CacheSize;
+    c->L3 = (int) std::min<size_t>(total_b, (size_t) INT_MAX);
+    c->ncores = ndev;
+}
+
+// Tile order for a shape when the caller leaves the schedule open: the same
+// MEMA rule as derive_schedule with the device L2 in the role of the cache that
+// holds a CB block (src/block_sizing.cpp:434-462).
+int resolve_schedule(DeviceState* st, int M, int N, int K, int sched) {
+    if (sched != CAKEB200_SCHED_NA) return sched;
+    cakeb200_cntx c;
+    b200_cntx(st, &c);
+    c.ncores = 1;
+    cakeb200_blk_dims x;
+    if (cakeb200_init_block_dims(M, N, K, 1, &x, &c, CAKEB200_SCHED_NA, 0, 0, 0) != CAKEB200_OK) return CAKEB200_SCHED_KMN;
+    return x.sch;
+}
+
+// The tensor-core path pays a fixed operand-split pass; tiny products run on FFMA.
+int resolve_kernel(int kernel, long long M, long long N, long long K, long long batch) {
+    if (kernel != CAKEB200_KERNEL_AUTO) return kernel;
+    if (batch > 1) return CAKEB200_KERNEL_FFMA;
+    if (M >= 256 && N >= 256 && K >= 64 && M * N * K >= (1LL << 27)) return CAKEB200_KERNEL_TF32X3;
+    return CAKEB200_KERNEL_FFMA;
+}
+
+int run_dense(DeviceState* st, GemmProblem& g, int kernel, cudaStream_t s, bool timed) {
+    kernel = resolve_kernel(kernel, g.M, g.N, g.K, g.batch);
+    g_stats.kernel = kernel;
+    if (kernel == CAKEB200_KERNEL_FFMA) {
+        g_stats.launches += 1;
+        return launch_sgemm_ffma(g, s);
+    }
+    if (kernel != CAKEB200_KERNEL_TF32X3) {
+        set_error("unknown kernel id %d", kernel);
+        return CAKEB200_ERR_ARG;
+    }
+    const size_t need = tf32x3_scratch_bytes(g.M, g.N, g.K);
+    int rc = ensure_scratch(st, need);
+    if (rc) return rc;
+    g_stats.ms_prepass = timed ? -1.0f : 0.0f;  // -1: events 4,5 hold the split-pass time
+    return launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats,
+                               timed ? &st->ev[4] : nullptr);
+}
+
+bool bad_dims(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) {
+        set_error("matrix dimensions must be positive (M=%d N=%d K=%d)", M, N, K);
+        return true;
+    }
+    return false;
+}
+
+float elapsed(cudaEvent_t a, cudaEvent_t b) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, a, b) != cudaSuccess) cudaGetLastError();
+    return ms;
+}
+
+int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
+               int kernel, void* stream, bool blocking) {
+    g_stats = cakeb200_stats();
+    if (!A || !B || !C) {
+        set_error("null matrix pointer");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    if (sched < 0 || sched > CAKEB200_SCHED_NA) {
+        set_error("unknown schedule %d", sched);
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+
+    GemmProblem g = {};
+    g.M = M; g.N = N; g.K = K;
+    g.lda = K; g.ldb = N; g.ldc = N;
+    g.batch = 1;
+    g.accumulate = accumulate ? 1 : 0;
+    g.order = resolve_schedule(st, M, N, K, sched);
+    g_stats.sched = g.order;
+
+    if (!blocking) {
+        if (!on_device(A) || !on_device(B) || !on_device(C)) {
+            set_error("cakeb200_sgemm_async needs device pointers");
+            return CAKEB200_ERR_ARG;
+        }
+        g.A = A; g.B = B; g.C = C;
+        return run_dense(st, g, kernel, s, false);
+    }
+
+    Operand oa, ob, oc;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if ((rc = stage_in(st, 0, oa, A, (size_t) M * K * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, ob, B, (size_t) K * N * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oc, C, (size_t) M * N * 4, g.accumulate != 0, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    g.A = (const float*) oa.dev; g.B = (const float*) ob.dev; g.C = (float*) oc.dev;
+    if ((rc = run_dense(st, g, kernel, s, true))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oc, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    if ((rc = check_status_word(st, s))) return rc;
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_prepass = (g_stats.ms_prepass < 0.f) ? elapsed(st->ev[4], st->ev[5]) : 0.f;
+    const float mid = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_gemm = mid - g_stats.ms_prepass;
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
+typedef int (*pack_fn)(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
+
+// mat: rows x cols matrix, packed: packed buffer of packed_bytes; unpack moves packed -> mat.
+int pack_impl(pack_fn fn, const float* mat, size_t mat_bytes, float* packed, size_t packed_bytes, int d0, int d1,
+              int p, const cakeb200_blk_dims* x, const cakeb200_cntx* c, bool unpack, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!mat || !packed || !x || !c) {
+        set_error("null argument");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    Operand om, op;
+    int rc;
+    // unpack leaves matrix cells outside the packed image untouched, so the matrix is always copied in
+    if ((rc = stage_in(st, 0, om, mat, mat_bytes, true, s))) return rc;
+    if ((rc = stage_in(st, 1, op, packed, packed_bytes, unpack, s))) return rc;
+    if ((rc = fn((const float*) om.dev, (float*) op.dev, d0, d1, p, x, c, unpack, s))) return rc;
+    g_stats.launches = 1;
+    if ((rc = stage_out(unpack ? om : op, s))) return rc;
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    return CAKEB200_OK;
+}
+
+}  // namespace
+}  // namespace cakeb200
+
+using namespace cakeb200;
+
+extern "C" {
+
+const char* cakeb200_last_error(void) { return g_error; }
+
+void cakeb200_get_stats(cakeb200_stats* out) {
+    if (out) *out = g_stats;
+}
+
+int cakeb200_device_count(void) {
+    int n = 0, good = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    for (int i = 0; i < n; i++) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, i) == cudaSuccess && major == 10) good++;
+    }
+    return good;
+}
+
+int cakeb200_query_cntx(cakeb200_cntx* out) {
+    if (!out) return CAKEB200_ERR_ARG;
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    b200_cntx(st, out);
+    return CAKEB200_OK;
+}
+
+int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
+                   int kernel, void* stream) {
+    return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, true);
+}
+
+int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
+                         int kernel, void* stream) {
+    return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, false);
+}
+
+int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K, int batch, int kernel,
+                           void* stream) {
+    g_stats = cakeb200_stats();
+    if (!A || !B || !C || batch <= 0) {
+        set_error("bad argument");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    if (kernel == CAKEB200_KERNEL_TF32X3) {
+        set_error("the batched entry point runs on the FFMA kernel");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    Operand oa, ob, oc;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if ((rc = stage_in(st, 0, oa, A, (size_t) batch * M * K * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, ob, B, (size_t) batch * K * N * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oc, C, (size_t) batch * M * N * 4, false, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    GemmProblem g = {};
+    g.A = (const float*) oa.dev; g.B = (const float*) ob.dev; g.C = (float*) oc.dev;
+    g.M = M; g.N = N; g.K = K;
+    g.lda = K; g.ldb = N; g.ldc = N;
+    g.stride_a = (long long) M * K; g.stride_b = (long long) K * N; g.stride_c = (long long) M * N;
+    g.order = CAKEB200_SCHED_MKN;
+    for (int done = 0; done < batch; done += 65535) {  // gridDim.z limit
+        GemmProblem part = g;
+        part.batch = std::min(65535, batch - done);
+        part.A += (long long) done * g.stride_a;
+        part.B += (long long) done * g.stride_b;
+        part.C += (long long) done * g.stride_c;
+        if ((rc = launch_sgemm_ffma(part, s))) return rc;
+        g_stats.launches++;
+    }
+    g_stats.kernel = CAKEB200_KERNEL_FFMA;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oc, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
+int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int kernel, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!A || !B || !C) {
+        set_error("null matrix pointer");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    Operand oa, ob, oc;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if ((rc = stage_in(st, 0, oa, A, (size_t) M * K * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, ob, B, (size_t) K * N * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oc, C, (size_t) M * N * 4, false, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    if (kernel == CAKEB200_KERNEL_TF32X3) {
+        // dense tensor-core product on the operand as given (zeros multiply like any value)
+        GemmProblem g = {};
+        g.A = (const float*) oa.dev; g.B = (const float*) ob.dev; g.C = (float*) oc.dev;
+        g.M = M; g.N = N; g.K = K; g.lda = K; g.ldb = N; g.ldc = N; g.batch = 1;
+        g.order = resolve_schedule(st, M, N, K, CAKEB200_SCHED_NA);
+        if ((rc = run_dense(st, g, CAKEB200_KERNEL_TF32X3, s, false))) return rc;
+    } else {
+        if ((rc = ensure_scratch(st, sparse_scratch_bytes(M, K)))) return rc;
+        if ((rc = launch_sp_sgemm((const float*) oa.dev, (const float*) ob.dev, (float*) oc.dev, M, N, K, st->scratch, s,
+                                  &g_stats.launches)))
+            return rc;
+        g_stats.kernel = CAKEB200_KERNEL_FFMA;
+    }
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oc, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    if ((rc = check_status_word(st, s))) return rc;
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
+int cakeb200_im2col(const float* in, float* col, int batch, int cin, int H, int W, int hf, int wf, int stride,
+                    int pad, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!in || !col || batch <= 0 || cin <= 0 || H <= 0 || W <= 0 || hf <= 0 || wf <= 0 || stride <= 0 || pad < 0 ||
+        H + 2 * pad < hf || W + 2 * pad < wf) {
+        set_error("bad convolution geometry");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
+    Operand oi, oc;
+    int rc;
+    if ((rc = stage_in(st, 0, oi, in, (size_t) batch * cin * H * W * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, oc, col, (size_t) cin * hf * wf * batch * Ho * Wo * 4, false, s))) return rc;
+    if ((rc = launch_im2col((const float*) oi.dev, (float*) oc.dev, batch, cin, H, W, hf, wf, stride, pad, s))) return rc;
+    g_stats.launches = 1;
+    if ((rc = stage_out(oc, s))) return rc;
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    return CAKEB200_OK;
+}
+
+int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch, int cin, int H, int W, int cout,
+                    int hf, int wf, int stride, int pad, int kernel, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!in || !filters || !out || batch <= 0 || cin <= 0 || cout <= 0 || H <= 0 || W <= 0 || hf <= 0 || wf <= 0 ||
+        stride <= 0 || pad < 0 || H + 2 * pad < hf || W + 2 * pad < wf) {
+        set_error("bad convolution geometry");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
+    const int Kg = cin * hf * wf;
+    const long long plane = (long long) Ho * Wo, Ng = plane * batch;
+    if (Ng > INT_MAX) {
+        set_error("im2col matrix has more than 2^31-1 columns");
+        return CAKEB200_ERR_TOO_LARGE;
+    }
+    Operand oi, of, oo;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if ((rc = stage_in(st, 0, oi, in, (size_t) batch * cin * H * W * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, of, filters, (size_t) cout * Kg * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oo, out, (size_t) batch * cout * plane * 4, false, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+
+    // The im2col matrix lives in the scratch arena.
+    const size_t col_bytes = (size_t) Kg * Ng * 4;
+    (void) kernel;  // the per-image strided products run on the FFMA kernel
+    if ((rc = ensure_scratch(st, col_bytes))) return rc;
+    float* col = (float*) st->scratch;
+    if ((rc = launch_im2col((const float*) oi.dev, col, batch, cin, H, W, hf, wf, stride, pad, s))) return rc;
+    g_stats.launches++;
+
+    // One strided product per image: out[b] (cout x Ho*Wo) = F (cout x Kg) * col[:, b*Ho*Wo ...]
+    GemmProblem g = {};
+    g.A = (const float*) of.dev; g.B = col; g.C = (float*) oo.dev;
+    g.M = cout; g.N = (int) plane; g.K = Kg;
+    g.lda = Kg; g.ldb = (int) Ng; g.ldc = (int) plane;
+    g.stride_a = 0; g.stride_b = plane; g.stride_c = (long long) cout * plane;
+    g.order = CAKEB200_SCHED_MKN;
+    for (int done = 0; done < batch; done += 65535) {
+        GemmProblem part = g;
+        part.batch = std::min(65535, batch - done);
+        part.B += (long long) done * g.stride_b;
+        part.C += (long long) done * g.stride_c;
+        if ((rc = launch_sgemm_ffma(part, s))) return rc;
+        g_stats.launches++;
+    }
+    g_stats.kernel = CAKEB200_KERNEL_FFMA;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oo, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
+int cakeb200_pack_A(const float* A, float* A_p, int M, int K, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_A_dev, A, (size_t) M * K * 4, A_p, cakeb200_packed_A_size(M, K, p, x, c, x->sch), M, K, p, x, c, false, stream);
+}
+int cakeb200_unpack_A(float* A, const float* A_p, int M, int K, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_A_dev, A, (size_t) M * K * 4, (float*) A_p, cakeb200_packed_A_size(M, K, p, x, c, x->sch), M, K, p, x, c, true, stream);
+}
+int cakeb200_pack_B(const float* B, float* B_p, int K, int N, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_B_dev, B, (size_t) K * N * 4, B_p, cakeb200_packed_B_size(K, N, p, x, c), K, N, p, x, c, false, stream);
+}
+int cakeb200_unpack_B(float* B, const float* B_p, int K, int N, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_B_dev, B, (size_t) K * N * 4, (float*) B_p, cakeb200_packed_B_size(K, N, p, x, c), K, N, p, x, c, true, stream);
+}
+int cakeb200_pack_C(const float* C, float* C_p, int M, int N, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_C_dev, C, (size_t) M * N * 4, C_p, cakeb200_packed_C_size(M, N, p, x, c, x->sch), M, N, p, x, c, false, stream);
+}
+int cakeb200_unpack_C(float* C, const float* C_p, int M, int N, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* c, void* stream) {
+    if (!x || !c) return CAKEB200_ERR_ARG;
+    return pack_impl(pack_C_dev, C, (size_t) M * N * 4, (float*) C_p, cakeb200_packed_C_size(M, N, p, x, c, x->sch), M, N, p, x, c, true, stream);
+}
+
+}  // extern "C"

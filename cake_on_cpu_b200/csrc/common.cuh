@@ -1,0 +1,90 @@
+// Shared declarations for the sm_100a kernels and the C-ABI layer above them.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "cake_b200.h"
+
+namespace cakeb200 {
+
+// Last error text of the calling thread, returned by cakeb200_last_error().
+void set_error(const char* fmt, ...);
+
+#define CAKE_CUDA_OK(expr)                                                              \
+    do {                                                                                \
+        cudaError_t _e = (expr);                                                        \
+        if (_e != cudaSuccess) {                                                        \
+            cakeb200::set_error("%s failed at %s:%d: %s", #expr, __FILE__, __LINE__,    \
+                                cudaGetErrorString(_e));                                \
+            return CAKEB200_ERR_CUDA;                                                   \
+        }                                                                               \
+    } while (0)
+
+// One dense product C[M x N] (+)= A[M x K] * B[K x N], all row-major FP32 in
+// device memory.  `batch` independent products are laid `stride_*` elements apart.
+struct GemmProblem {
+    const float* A;
+    const float* B;
+    float* C;
+    int M, N, K;
+    int lda, ldb, ldc;
+    long long stride_a, stride_b, stride_c;
+    int batch;
+    int accumulate;  // 0: C = A*B, 1: C += A*B (the reference's beta != 0 behaviour)
+    int order;       // tile rasterisation: CAKEB200_SCHED_*
+};
+
+// Per-device state: scratch arena that grows on demand and is reused between calls.
+struct DeviceState {
+    int device = -1;
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void* staging[3] = {nullptr, nullptr, nullptr};
+    size_t staging_bytes[3] = {0, 0, 0};
+    int sm_count = 0;
+    int* status_word = nullptr;  // device-side error flag written by bounded waits
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // 4,5 bracket the operand-split pass
+};
+DeviceState* device_state();  // state of the current device (created on first use)
+int ensure_scratch(DeviceState* st, size_t bytes);
+
+// exact-FP32 FFMA path (sgemm_ffma.cu)
+int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);
+// 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
+size_t tf32x3_scratch_bytes(int M, int N, int K);
+int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
+                        int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
+
+
+#ifdef __CUDACC__
+// Linear tile index -> tile coordinates.  The order in which CTAs take tiles is
+// what remains of the reference's block schedules on a GPU:
+//   M-first (MKN): walk down a column of tiles, so one B panel stays hot;
+//   N-first (NKM): walk along a row of tiles, so one A panel stays hot;
+//   K-first (KMN): K runs innermost inside every tile; tiles are taken in bands
+//                  of 8 tile-rows that snake left-right, the analogue of the
+//                  snaking CB-block traversal of src/cake_sgemm_k_first.cpp:28-71.
+__device__ __forceinline__ void tile_coords(int id, int tiles_m, int tiles_n, int order, int& tm, int& tn) {
+    if (order == CAKEB200_SCHED_MKN) {
+        tm = id % tiles_m;
+        tn = id / tiles_m;
+    } else if (order == CAKEB200_SCHED_NKM) {
+        tn = id % tiles_n;
+        tm = id / tiles_n;
+    } else {
+        constexpr int G = 8;
+        const int band = id / (G * tiles_n);
+        const int first = band * G;
+        const int rows = min(G, tiles_m - first);
+        const int in_band = id - band * G * tiles_n;
+        tm = first + in_band % rows;
+        tn = in_band / rows;
+        if (band & 1) tn = tiles_n - 1 - tn;
+    }
+}
+#endif
+
+}  // namespace cakeb200

@@ -1,0 +1,540 @@
+// The reference's C++ API (include/cake.h) implemented over the C ABI.
+// Host logic only: argument translation, the reference's scalar/flag
+// semantics, multi-GPU row partitioning and timing.  All arithmetic on
+// matrices happens in the kernels behind cake_b200.h.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <climits>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <thread>
+#include <vector>
+
+#include "cake.h"
+
+static_assert(sizeof(blk_dims_t) == sizeof(cakeb200_blk_dims), "blk_dims_t must mirror cakeb200_blk_dims");
+
+namespace {
+
+double now_s() {
+    timespec t;
+    clock_gettime(CLOCK_REALTIME, &t);
+    return t.tv_sec + t.tv_nsec * 1e-9;
+}
+
+cakeb200_cntx to_abi(const cake_cntx_t* c) {
+    cakeb200_cntx r;
+    r.alpha_n = c->alpha_n;
+    r.mr = c->mr; r.nr = c->nr;
+    r.L1 = c->L1; r.L2 = c->L2; r.L3 = c->L3;
+    r.ncores = c->ncores;
+    return r;
+}
+
+cakeb200_blk_dims* as_abi(blk_dims_t* x) { return reinterpret_cast<cakeb200_blk_dims*>(x); }
+
+double fail(const char* what) {
+    fprintf(stderr, "cake: %s failed: %s\n", what, cakeb200_last_error());
+    return -1.0;
+}
+
+bool is_device_ptr(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Row blocks of M for `parts` devices, multiples of 128 rows except the last.
+std::vector<int> row_partition(int M, int parts) {
+    std::vector<int> cut(parts + 1, 0);
+    const int tiles = (M + 127) / 128;
+    for (int g = 0; g <= parts; g++) cut[g] = std::min(M, (int) (((long long) tiles * g / parts) * 128));
+    cut[parts] = M;
+    return cut;
+}
+
+// C = A*B (+C) with host operands spread over several devices: device g gets
+// rows cut[g]..cut[g+1] of A and C and all of B; no exchange between devices.
+int sgemm_multi_gpu(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
+                    int ngpu) {
+    const std::vector<int> cut = row_partition(M, ngpu);
+    std::vector<int> rc(ngpu, CAKEB200_OK);
+    std::vector<std::thread> workers;
+    int home = 0;
+    cudaGetDevice(&home);
+    for (int g = 0; g < ngpu; g++) {
+        workers.emplace_back([&, g] {
+            const int rows = cut[g + 1] - cut[g];
+            if (rows <= 0) return;
+            if (cudaSetDevice(g) != cudaSuccess) {
+                rc[g] = CAKEB200_ERR_CUDA;
+                return;
+            }
+            rc[g] = cakeb200_sgemm(A + (size_t) cut[g] * K, B, C + (size_t) cut[g] * N, rows, N, K, accumulate, sched,
+                                   CAKEB200_KERNEL_AUTO, nullptr);
+            if (rc[g]) fprintf(stderr, "cake: device %d: %s\n", g, cakeb200_last_error());
+        });
+    }
+    for (auto& w : workers) w.join();
+    cudaSetDevice(home);
+    for (int g = 0; g < ngpu; g++)
+        if (rc[g]) return rc[g];
+    return CAKEB200_OK;
+}
+
+int gpus_for(int p, int M, bool all_host) {
+    if (!all_host || p <= 1) return 1;
+    const int have = cakeb200_device_count();
+    const int by_rows = std::max(1, M / 512);  // at least 512 rows per device
+    return std::max(1, std::min(std::min(p, have), by_rows));
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ context
+
+double clamp_val(double d, double min, double max) {
+    const double t = d < min ? min : d;
+    return t > max ? max : t;
+}
+
+int lcm(int n1, int n2) {
+    int a = n1, b = n2;
+    while (b) {
+        int t = a % b;
+        a = b;
+        b = t;
+    }
+    return a ? n1 / a * n2 : 0;
+}
+
+cake_cntx_t* cake_query_cntx() {
+    cake_cntx_t* ret = (cake_cntx_t*) calloc(1, sizeof(cake_cntx_t));
+    cakeb200_cntx c;
+    if (cakeb200_query_cntx(&c) != CAKEB200_OK) {
+        fprintf(stderr, "cake_query_cntx: %s\n", cakeb200_last_error());
+        c.alpha_n = 1.0; c.mr = 128; c.nr = 256; c.L1 = 233472; c.L2 = 132120576; c.L3 = INT_MAX; c.ncores = 1;
+    }
+    ret->blis_cntx = NULL;
+    ret->alpha_n = 1.0;
+    ret->mr = c.mr; ret->nr = c.nr;
+    ret->m_map = 0; ret->n_map = 0;
+    ret->L1 = c.L1; ret->L2 = c.L2; ret->L3 = c.L3;
+    ret->ncores = c.ncores > 0 ? c.ncores : 1;
+    int clock_khz = 0, bus_bits = 0, dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&clock_khz, cudaDevAttrMemoryClockRate, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&bus_bits, cudaDevAttrGlobalMemoryBusWidth, dev) != cudaSuccess) {
+        cudaGetLastError();
+        clock_khz = 3996000; bus_bits = 7680;
+    }
+    ret->peak_dram_bw = 2.0 * clock_khz * 1e3 * (bus_bits / 8.0);
+    ret->peak_flops = 2.25e15 / 2 / 3;  // dense TF32 tensor rate shared by the three split products
+    return ret;
+}
+
+cake_cntx_t* cake_query_cntx_torch(int L2, int L3) {
+    cake_cntx_t* ret = cake_query_cntx();
+    ret->L2 = L2;
+    ret->L3 = L3;
+    return ret;
+}
+
+void update_mr_nr(cake_cntx_t* cake_cntx, int m_r, int n_r) {
+    cake_cntx->mr = m_r;
+    cake_cntx->nr = n_r;
+    cake_cntx->m_map = 0;
+    cake_cntx->n_map = 0;
+}
+
+int get_cache_size(int level) {
+    cakeb200_cntx c;
+    if (cakeb200_query_cntx(&c) != CAKEB200_OK) return 0;
+    return level == 1 ? c.L1 : level == 2 ? c.L2 : c.L3;
+}
+
+int get_num_physical_cores() { return std::max(1, cakeb200_device_count()); }
+
+enum sched derive_schedule(int M, int N, int K, int p, int mc_ret, cake_cntx_t* cake_cntx) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    return (enum sched) cakeb200_derive_schedule(M, N, K, p, mc_ret, &c);
+}
+
+enum sched set_schedule(enum sched sch, int M, int N, int K) { return (enum sched) cakeb200_set_schedule(sch, M, N, K); }
+
+void init_block_dims(int M, int N, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch, char* argv[],
+                     float type_size, int mcu, int kcu, int ncu) {
+    (void) argv; (void) type_size;
+    cakeb200_cntx c = to_abi(cake_cntx);
+    if (cakeb200_init_block_dims(M, N, K, p, as_abi(x), &c, sch, mcu, kcu, ncu) != CAKEB200_OK)
+        fprintf(stderr, "init_block_dims: bad argument\n");
+    cake_cntx->alpha_n = c.alpha_n;  // the reference mutates its context here (src/block_sizing.cpp:336)
+}
+
+void init_block_dims_2d(int M, int N, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch,
+                        char* argv[], float type_size, int mcu, int kcu, int ncu) {
+    // the 2-D core grid of the reference factors p = pm x pn; tiles of C are 2-D on a GPU anyway
+    init_block_dims(M, N, K, p, x, cake_cntx, sch == NA ? KMN : sch, argv, type_size, mcu, kcu, ncu);
+    x->pn = grid_dims_2d(M, N, K, p, cake_cntx->ncores);
+    x->pm = x->pn ? p / x->pn : p;
+}
+
+cache_dims_t* get_cache_dims(int M, int N, int K, int p, cake_cntx_t* cake_cntx, enum sched sch, char* argv[],
+                             float type_size, int mcu, int kcu, int ncu) {
+    blk_dims_t x;
+    init_block_dims(M, N, K, p, &x, cake_cntx, sch, argv, type_size, mcu, kcu, ncu);
+    cache_dims_t* r = (cache_dims_t*) malloc(sizeof(cache_dims_t));
+    r->m_c = x.m_c; r->k_c = x.k_c; r->n_c = x.n_c; r->sch = x.sch;
+    return r;
+}
+
+// pn closest to sqrt(p*N/M) that divides p (reference src/block_sizing.cpp:601-636)
+int grid_dims_2d(int M, int N, int K, int p, int ncores) {
+    (void) K; (void) ncores;
+    if (p <= 0 || M <= 0) return 1;
+    int want = (int) std::lround(std::sqrt(((double) p) * N / M));
+    want = std::max(1, std::min(want, p));
+    for (int d = 0; d < p; d++) {
+        if (want - d >= 1 && p % (want - d) == 0) return want - d;
+        if (want + d <= p && p % (want + d) == 0) return want + d;
+    }
+    return 1;
+}
+
+// ------------------------------------------------------------------ packing
+
+size_t cake_sgemm_packed_A_size(int M, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    return cakeb200_packed_A_size(M, K, p, as_abi(x), &c, sch);
+}
+size_t cake_sgemm_packed_B_size(int K, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    return cakeb200_packed_B_size(K, N, p, as_abi(x), &c);
+}
+size_t cake_sgemm_packed_C_size(int M, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    return cakeb200_packed_C_size(M, N, p, as_abi(x), &c, sch);
+}
+
+double pack_A(float* A, float* A_p, int M, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    const double t0 = now_s();
+    cakeb200_cntx c = to_abi(cake_cntx);
+    cakeb200_blk_dims d = *as_abi(x);
+    d.sch = sch;
+    if (cakeb200_pack_A(A, A_p, M, K, p, &d, &c, nullptr)) return fail("pack_A");
+    return now_s() - t0;
+}
+void pack_B(float* B, float* B_p, int K, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    cakeb200_blk_dims d = *as_abi(x);
+    d.sch = sch;
+    if (cakeb200_pack_B(B, B_p, K, N, p, &d, &c, nullptr)) fail("pack_B");
+}
+void pack_C(float* C, float* C_p, int M, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    cakeb200_blk_dims d = *as_abi(x);
+    d.sch = sch;
+    if (cakeb200_pack_C(C, C_p, M, N, p, &d, &c, nullptr)) fail("pack_C");
+}
+void unpack_C(float* C, float* C_p, int M, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
+    cakeb200_cntx c = to_abi(cake_cntx);
+    cakeb200_blk_dims d = *as_abi(x);
+    d.sch = sch;
+    if (cakeb200_unpack_C(C, C_p, M, N, p, &d, &c, nullptr)) fail("unpack_C");
+}
+
+// -------------------------------------------------------------- the product
+
+namespace {
+
+// packed operand -> plain row-major copy in device memory (caller cudaFree()s)
+float* unpacked_copy(bool is_A, float* packed, int rows, int cols, int M, int N, int K, int p, blk_dims_t* x,
+                     cake_cntx_t* cntx) {
+    float* plain = nullptr;
+    if (cudaMalloc((void**) &plain, (size_t) rows * cols * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    cakeb200_cntx c = to_abi(cntx);
+    const int rc = is_A ? cakeb200_unpack_A(plain, packed, M, K, p, as_abi(x), &c, nullptr)
+                        : cakeb200_unpack_B(plain, packed, K, N, p, as_abi(x), &c, nullptr);
+    if (rc) {
+        cudaFree(plain);
+        return nullptr;
+    }
+    return plain;
+}
+
+double sgemm_driver(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx, bool packedA,
+                    bool packedB, float beta, enum sched sch, int mcu, int kcu, int ncu) {
+    const double t0 = now_s();
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0 || p <= 0) {
+        fprintf(stderr, "cake_sgemm: bad argument\n");
+        return -1.0;
+    }
+    cake_cntx_t* own = nullptr;
+    if (cake_cntx == NULL) cake_cntx = own = cake_query_cntx();
+
+    blk_dims_t x;
+    init_block_dims(M, N, K, p, &x, cake_cntx, sch, NULL, 4, mcu, kcu, ncu);
+    sch = x.sch;
+    // K-first always overwrites C; the other two add to C when beta != 0 (src/cake_sgemm.cpp:87-136)
+    const int accumulate = (sch != KMN && beta != 0) ? 1 : 0;
+
+    float *A_plain = A, *B_plain = B;
+    int rc = CAKEB200_OK;
+    if (packedA && !(A_plain = unpacked_copy(true, A, M, K, M, N, K, p, &x, cake_cntx))) rc = CAKEB200_ERR_CUDA;
+    if (!rc && packedB && !(B_plain = unpacked_copy(false, B, K, N, M, N, K, p, &x, cake_cntx))) rc = CAKEB200_ERR_CUDA;
+    if (!rc) {
+        const bool all_host = !is_device_ptr(A_plain) && !is_device_ptr(B_plain) && !is_device_ptr(C);
+        const int ngpu = gpus_for(p, M, all_host);
+        rc = ngpu > 1 ? sgemm_multi_gpu(A_plain, B_plain, C, M, N, K, accumulate, sch, ngpu)
+                      : cakeb200_sgemm(A_plain, B_plain, C, M, N, K, accumulate, sch, CAKEB200_KERNEL_AUTO, nullptr);
+    }
+    if (packedA && A_plain && A_plain != A) cudaFree(A_plain);
+    if (packedB && B_plain && B_plain != B) cudaFree(B_plain);
+    if (own) free(own);
+    if (rc) return fail("cake_sgemm");
+    return now_s() - t0;
+}
+
+}  // namespace
+
+double cake_sgemm(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx, char* argv[],
+                  bool packedA, bool packedB, float alpha, float beta, enum sched sch, int mcu, int kcu, int ncu) {
+    (void) argv; (void) alpha;  // the reference never applies alpha
+    return sgemm_driver(A, B, C, M, N, K, p, cake_cntx, packedA, packedB, beta, sch, mcu, kcu, ncu);
+}
+
+double cake_sgemm_online(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                         char* argv[], bool packedA, bool packedB, float alpha, float beta, enum sched sch, int mcu,
+                         int kcu, int ncu) {
+    (void) argv; (void) alpha; (void) sch; (void) beta;  // K-first only, overwrites C (src/cake_sgemm.cpp:397-468)
+    return sgemm_driver(A, B, C, M, N, K, p, cake_cntx, packedA, packedB, 0, KMN, mcu, kcu, ncu);
+}
+
+double cake_sgemm_2d(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx, char* argv[],
+                     bool packedA, bool packedB, float alpha, float beta, enum sched sch, int mcu, int kcu, int ncu) {
+    (void) argv; (void) alpha; (void) sch; (void) beta;
+    return sgemm_driver(A, B, C, M, N, K, p, cake_cntx, packedA, packedB, 0, KMN, mcu, kcu, ncu);
+}
+
+double cake_sgemm_2d_small(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                           char* argv[], bool packedA, bool packedB, float alpha, float beta, enum sched sch) {
+    (void) argv; (void) alpha; (void) sch; (void) beta;
+    return sgemm_driver(A, B, C, M, N, K, p, cake_cntx, packedA, packedB, 0, KMN, 0, 0, 0);
+}
+
+double cake_sgemm_test(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                       char* argv[], bool packedA, bool packedB, float alpha, float beta, enum sched sch) {
+    (void) argv; (void) alpha;
+    return sgemm_driver(A, B, C, M, N, K, p, cake_cntx, packedA, packedB, beta, sch, 0, 0, 0);
+}
+
+void schedule_KMN(float* A_p, float* B_p, float* C, float** C_p, int M, int N, int K, int p,
+                  cake_cntx_t* cake_cntx, blk_dims_t* x) {
+    (void) C_p;  // per-core accumulation slabs of the CPU schedule; tensor memory plays that role
+    blk_dims_t d = *x;
+    d.sch = KMN;
+    float* A = unpacked_copy(true, A_p, M, K, M, N, K, p, &d, cake_cntx);
+    float* B = A ? unpacked_copy(false, B_p, K, N, M, N, K, p, &d, cake_cntx) : nullptr;
+    if (!A || !B || cakeb200_sgemm(A, B, C, M, N, K, 0, CAKEB200_SCHED_KMN, CAKEB200_KERNEL_AUTO, nullptr))
+        fail("schedule_KMN");
+    if (A) cudaFree(A);
+    if (B) cudaFree(B);
+}
+
+namespace {
+void schedule_packed_C(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                       blk_dims_t* x, enum sched sch, const char* who) {
+    blk_dims_t d = *x;
+    d.sch = sch;
+    cakeb200_cntx c = to_abi(cake_cntx);
+    float* A = unpacked_copy(true, A_p, M, K, M, N, K, p, &d, cake_cntx);
+    float* B = A ? unpacked_copy(false, B_p, K, N, M, N, K, p, &d, cake_cntx) : nullptr;
+    float* C = nullptr;
+    bool ok = A && B && cudaMalloc((void**) &C, (size_t) M * N * sizeof(float)) == cudaSuccess;
+    // C_p holds the running sum: bring it to plain layout, add the product, pack it back
+    ok = ok && !cakeb200_unpack_C(C, C_p, M, N, p, as_abi(&d), &c, nullptr);
+    ok = ok && !cakeb200_sgemm(A, B, C, M, N, K, 1, sch, CAKEB200_KERNEL_AUTO, nullptr);
+    ok = ok && !cakeb200_pack_C(C, C_p, M, N, p, as_abi(&d), &c, nullptr);
+    if (!ok) fail(who);
+    if (A) cudaFree(A);
+    if (B) cudaFree(B);
+    if (C) cudaFree(C);
+}
+}  // namespace
+
+void schedule_MKN(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                  blk_dims_t* x) {
+    schedule_packed_C(A_p, B_p, C_p, M, N, K, p, cake_cntx, x, MKN, "schedule_MKN");
+}
+
+void schedule_NKM(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                  blk_dims_t* x) {
+    schedule_packed_C(A_p, B_p, C_p, M, N, K, p, cake_cntx, x, NKM, "schedule_NKM");
+}
+
+// dispatcher (src/cake_sgemm.cpp:726-765): only the dense M-first / N-first arms are live in the reference
+void schedule(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx, blk_dims_t* x,
+              enum sched sch, bool sparse, bool small) {
+    if (sparse || small || sch == KMN) return;  // empty arms in the reference
+    if (sch == MKN) schedule_MKN(A_p, B_p, C_p, M, N, K, p, cake_cntx, x);
+    else if (sch == NKM) schedule_NKM(A_p, B_p, C_p, M, N, K, p, cake_cntx, x);
+    else fprintf(stderr, "unknown schedule\n");
+}
+
+bool cake_gemm_small(float* A, float* B, float* C, int M, int N, int K, int p, blk_dims_t* x,
+                     cake_cntx_t* cake_cntx, enum sched sch, char* argv[]) {
+    (void) p; (void) x; (void) cake_cntx; (void) sch; (void) argv;
+    // "small" = the operand pre-pass would cost more than a tenth of the product
+    // (the rule sketched in the reference, src/cake_sgemm.cpp:624-718)
+    const double flops = 2.0 * M * N * K, prepass_bytes = 12.0 * ((double) M * K + (double) K * N);
+    const bool small = (prepass_bytes / 6.5e12) > 0.1 * (flops / 1.5e14) || M < 256 || N < 256 || K < 64;
+    if (!small) return false;
+    if (cakeb200_sgemm(A, B, C, M, N, K, 0, CAKEB200_SCHED_MKN, CAKEB200_KERNEL_FFMA, nullptr)) {
+        fail("cake_gemm_small");
+        return false;
+    }
+    return true;
+}
+
+double cake_sgemm_small_batched(float* A, float* B, float* C, int M, int N, int K, int batch, int p,
+                                cake_cntx_t* cake_cntx) {
+    (void) p; (void) cake_cntx;
+    const double t0 = now_s();
+    if (cakeb200_sgemm_batched(A, B, C, M, N, K, batch, CAKEB200_KERNEL_AUTO, nullptr)) return fail("cake_sgemm_small_batched");
+    return now_s() - t0;
+}
+
+double cake_sp_sgemm(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                     float density_hint) {
+    (void) p; (void) cake_cntx;
+    const double t0 = now_s();
+    // above ~6 % nonzeros the dense tensor-core product is faster than skipping zeros
+    const int kernel = (density_hint > 0.06f && M >= 256 && N >= 256 && K >= 64) ? CAKEB200_KERNEL_TF32X3 : CAKEB200_KERNEL_FFMA;
+    if (cakeb200_sp_sgemm(A, B, C, M, N, K, kernel, nullptr)) return fail("cake_sp_sgemm");
+    return now_s() - t0;
+}
+
+double cake_sconv_im2col(float* in, float* filters, float* out, int batch, int Cin, int H, int W, int Cout, int Hf,
+                         int Wf, int stride, int pad, int p, cake_cntx_t* cake_cntx) {
+    (void) p; (void) cake_cntx;
+    const double t0 = now_s();
+    if (cakeb200_conv2d(in, filters, out, batch, Cin, H, W, Cout, Hf, Wf, stride, pad, CAKEB200_KERNEL_AUTO, nullptr))
+        return fail("cake_sconv_im2col");
+    return now_s() - t0;
+}
+
+float* im_2_col(float* In, int Wf, int Hf, int Win, int Hin, int Wout, int Hout, int Cin, int Cout, int s) {
+    (void) Cout;
+    float* mat = (float*) malloc((size_t) Cin * Wf * Hf * Wout * Hout * sizeof(float));
+    // Hout x Wout as given by the caller: no padding, stride s
+    if ((Hin - Hf) / s + 1 != Hout || (Win - Wf) / s + 1 != Wout ||
+        cakeb200_im2col(In, mat, 1, Cin, Hin, Win, Hf, Wf, s, 0, nullptr)) {
+        fprintf(stderr, "im_2_col: %s\n", cakeb200_last_error());
+        free(mat);
+        return NULL;
+    }
+    return mat;
+}
+
+// --------------------------------------------------------------------- util
+
+float rand_gen() { return ((float) (rand()) + 1.f) / ((float) RAND_MAX + 1.f); }
+
+float normalRandom() {
+    const float v1 = rand_gen(), v2 = rand_gen();
+    return cosf(2 * 3.14159265358979323846f * v2) * sqrtf(-2.f * logf(v1));
+}
+
+void rand_init(float* mat, int r, int c) {
+    for (long long i = 0; i < (long long) r * c; i++) mat[i] = (float) rand() / ((float) RAND_MAX) * 2.0f - 1.0f;
+}
+
+void print_array(float* arr, int len) {
+    for (int i = 0; i < len; i++) printf("%f ", arr[i]);
+    printf("\n\n");
+}
+
+void print_mat(float* arr, int r, int c) {
+    for (int i = 0; i < r; i++) {
+        for (int j = 0; j < c; j++) printf("%f ", arr[(size_t) i * c + j]);
+        printf("\n");
+    }
+    printf("\n");
+}
+
+void print_schedule(enum sched sch) {
+    static const char* names[] = {"KMN", "MKN", "NKM", "NA"};
+    printf("%s Cake Schedule\n", names[(int) sch & 3]);
+}
+
+// absolute tolerance 1e-3 per element, as the reference (src/util.cpp:139-169); 0 = equal
+bool mat_equals(float* C, float* C_check, int M, int N) {
+    long long wrong = 0;
+    for (long long i = 0; i < (long long) M * N; i++)
+        if (std::fabs(C_check[i] - C[i]) > 1e-3f) wrong++;
+    if (!wrong) {
+        printf("CORRECT!\n");
+        return 0;
+    }
+    printf("WRONG!\n%lld\n", wrong);
+    return 1;
+}
+
+// The reference recomputes A*B with a naive FP32 loop (src/util.cpp:173-202);
+// here the recomputation runs on the exact-FP32 kernel, one FMA chain over k per element.
+bool cake_sgemm_checker(float* A, float* B, float* C, int N, int M, int K) {
+    float* check = (float*) calloc((size_t) M * N, sizeof(float));
+    float* c_host = C;
+    std::vector<float> c_copy;
+    if (is_device_ptr(C)) {
+        c_copy.resize((size_t) M * N);
+        cudaMemcpy(c_copy.data(), C, c_copy.size() * sizeof(float), cudaMemcpyDeviceToHost);
+        c_host = c_copy.data();
+    }
+    bool ret = 1;
+    if (cakeb200_sgemm(A, B, check, M, N, K, 0, CAKEB200_SCHED_MKN, CAKEB200_KERNEL_FFMA, nullptr) == CAKEB200_OK)
+        ret = mat_equals(c_host, check, M, N);
+    else
+        fail("cake_sgemm_checker");
+    free(check);
+    return ret;
+}
+
+// the reference's own grid of awkward sizes (src/util.cpp:3-136)
+int run_tests() {
+    static const int dims[] = {1, 10, 96, 111, 960, 2111};
+    cake_cntx_t* cntx = cake_query_cntx();
+    int failures = 0, ran = 0;
+    for (int M : dims)
+        for (int K : dims)
+            for (int N : dims) {
+                std::vector<float> A((size_t) M * K), B((size_t) K * N), C((size_t) M * N);
+                srand(M * 31 + K * 17 + N);
+                rand_init(A.data(), M, K);
+                rand_init(B.data(), K, N);
+                const enum sched all[] = {KMN, MKN, NKM, NA};
+                for (enum sched s : all) {
+                    std::fill(C.begin(), C.end(), 0.f);
+                    if (cake_sgemm(A.data(), B.data(), C.data(), M, N, K, cntx->ncores, cntx, NULL, 0, 0, 1, 0, s) < 0 ||
+                        cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K)) {
+                        printf("FAILED M=%d K=%d N=%d sched=%d\n", M, K, N, (int) s);
+                        failures++;
+                    }
+                    ran++;
+                }
+            }
+    free(cntx);
+    printf(failures ? "FAILED\n" : "ALL TESTS PASSED!\n");
+    printf("%d cases, %d failures\n", ran, failures);
+    return failures;
+}

@@ -1,0 +1,586 @@
+// FP32 SGEMM on the 5th-generation tensor cores with split-precision operands
+// ("3xTF32"): every FP32 value v is written as hi + lo with hi = tf32(v) and
+// lo = tf32(v - hi); A*B is then hi*hi + hi*lo + lo*hi accumulated in FP32 in
+// tensor memory.  The dropped lo*lo term and the rounding of lo are of relative
+// size 2^-22, the same order as FP32 rounding itself.
+//
+// Role in the CAKE design.  The reference packs A and B into contiguous
+// operation blocks (src/pack_k_first.cpp, src/pack_ob.cpp) and walks CB blocks
+// in K-first / M-first / N-first order calling a register-tile outer-product
+// microkernel (src/cake_sgemm_k_first.cpp:9-153, src/kernels/haswell/dense.cpp:8).
+// Here:
+//   * packing     -> one bandwidth-bound pass that splits each operand into its
+//                    hi / lo planes (B is transposed on the way so that both
+//                    operands are K-major), then TMA boxes staged in a ring of
+//                    128-byte-swizzled shared-memory tiles;
+//   * CB block    -> a BM x BN tile of C held in tensor memory while K streams
+//                    through (K innermost); the schedule is the order in which
+//                    the persistent CTAs take tiles;
+//   * microkernel -> tcgen05.mma kind::tf32, 128 x BN x 8 per instruction.
+//
+// One CTA per SM, six warps: warp 0 issues TMA loads, warp 1 issues the MMAs
+// and owns the tensor-memory allocation, warps 2-5 drain finished accumulators
+// (tcgen05.ld) to global memory while the next tile is already being
+// multiplied into the second accumulator buffer.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out, the kernel
+// records where in a status word, stops issuing work, waits (bounded) for its
+// own loads in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cakeb200 {
+namespace {
+
+constexpr int BM = 128;          // rows of C per tile = TMEM lanes
+constexpr int BK = 32;           // K per pipeline stage: 32 floats = one 128-byte swizzle row
+constexpr int UMMA_K = 8;        // K of one tcgen05.mma kind::tf32
+constexpr int NUM_THREADS = 192;
+constexpr long long WAIT_LIMIT_NS = 2000000000LL;  // 2 s per wait, far above any legitimate stall
+
+template <int BN>
+struct Cfg {
+    static constexpr int STAGES = (BN == 256) ? 2 : 3;
+    static constexpr int A_BYTES = BM * BK * 4;   // one plane of A per stage
+    static constexpr int B_BYTES = BN * BK * 4;   // one plane of B per stage
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
+// barrier did not flip within WAIT_LIMIT_NS or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_word, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 1023) == 0) {
+            if (*abort_flag) return false;
+            if ((long long) (global_ns() - t0) > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (atomicCAS(status_word, 0, 1) == 0) {
+                    status_word[1] = where;
+                    status_word[2] = (int) blockIdx.x;
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes
+// and 128-byte swizzled: 8-row groups are 1024 bytes apart (stride byte offset),
+// the leading byte offset is unused for swizzled K-major layouts (encoded 1),
+// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t) 1 << 16;                        // leading byte offset (ignored)
+    d |= (uint64_t) (1024 >> 4) << 32;              // stride byte offset
+    d |= (uint64_t) 1 << 46;                        // descriptor version
+    d |= (uint64_t) 2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::tf32: D = F32, A = B = TF32, both K-major,
+// N in units of 8 at bit 17, M in units of 16 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (m >> 4) << 24);
+}
+
+struct Tf32x3Args {
+    float* C;            // output (or split-K partial planes when splits > 1)
+    long long plane;     // elements between split-K partial planes
+    int M, N, K;
+    int ldc;
+    int tiles_m, tiles_n;
+    int splits;          // K is cut into this many ranges, one work unit each
+    int kblocks;         // ceil(K / BK)
+    int order;
+    int accumulate;      // only honoured when splits == 1
+    int* status_word;
+};
+
+// ------------------------------------------------------------------ the kernel
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                    const Tf32x3Args args) {
+    using C_ = Cfg<BN>;
+    constexpr int STAGES = C_::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte alignment
+    uint8_t* tiles = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    uint64_t* bars = (uint64_t*) (tiles + STAGES * C_::STAGE_BYTES);
+    // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
+    uint32_t* tmem_slot = (uint32_t*) (bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor-memory allocation belongs to the MMA warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int units = args.tiles_m * args.tiles_n * args.splits;
+    const int kb_per_split = (args.kblocks + args.splits - 1) / args.splits;
+
+    if (warp == 0) {
+        // ------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const int split = u % args.splits, tile = u / args.splits;
+                int tm, tn;
+                tile_coords(tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
+                const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
+                    if (!ok) break;
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
+                    tma_load_2d(base, &map_a_hi, kb * BK, tm * BM, full_bar(stage));
+                    tma_load_2d(base + C_::A_BYTES, &map_a_lo, kb * BK, tm * BM, full_bar(stage));
+                    tma_load_2d(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, tn * BN, full_bar(stage));
+                    tma_load_2d(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, tn * BN, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Gave up: let the loads already issued land before the CTA goes away.
+                // A stage's loads have landed once its full barrier completed the phase
+                // the producer last armed; poll each briefly (bounded).
+                const unsigned long long t0 = global_ns();
+                for (int s = 0; s < STAGES; s++) {
+                    const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+                    while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, local++) {
+                const int split = u % args.splits;
+                const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
+                    const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
+                    const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
+                    const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
+                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                        accumulate = 1;
+                    }
+                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar(buf));  // accumulator complete
+            }
+        }
+    } else {
+        // ----------------------------------------------------------- epilogue
+        const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        int local = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, local++) {
+            const int split = u % args.splits, tile = u / args.splits;
+            int tm, tn;
+            tile_coords(tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
+            const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int row = tm * BM + quarter * 32 + lane;
+            float* crow = args.C + (long long) split * args.plane + (long long) row * args.ldc;
+            const bool vec_ok = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0) && (args.plane % 4 == 0);
+            const bool empty_range = kb0 >= kb1;  // a split with no K range contributes zeros
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                float v[32];
+                if (!empty_range) {
+                    tmem_ld32(tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN + c * 32), v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = 0.0f;
+                }
+                const int col0 = tn * BN + c * 32;
+                if (row < args.M && col0 < args.N) {
+                    if (vec_ok && col0 + 32 <= args.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (args.accumulate) {
+                                const float4 old = *reinterpret_cast<const float4*>(crow + col0 + j);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(crow + col0 + j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < args.N) crow[col0 + j] = args.accumulate ? crow[col0 + j] + v[j] : v[j];
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------- operand split
+
+__device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) {
+    // round to nearest on the 13 dropped mantissa bits, then the exact remainder, rounded again
+    const uint32_t b = __float_as_uint(v);
+    hi = __uint_as_float((b + 0x1000u) & 0xFFFFE000u);
+    const float r = v - hi;
+    lo = __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
+}
+
+// A (M x K, leading dimension lda) -> hi / lo planes with leading dimension Kp
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const float* __restrict__ A, float* __restrict__ hi, float* __restrict__ lo, int M, int K, int lda, int Kp) {
+    const long long total = (long long) M * Kp;
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long) gridDim.x * blockDim.x) {
+        const int m = (int) (i / Kp), k = (int) (i - (long long) m * Kp);
+        float h = 0.f, l = 0.f;
+        if (k < K) split_tf32(__ldg(A + (long long) m * lda + k), h, l);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+// B (K x N, leading dimension ldb) -> transposed hi / lo planes (N x Kp): 32 x 32 tiles through shared memory
+__global__ void __launch_bounds__(256)
+split_transpose_kernel(const float* __restrict__ B, float* __restrict__ hi, float* __restrict__ lo, int K, int N, int ldb, int Kp) {
+    __shared__ float t[32][33];
+    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int k = k0 + r, n = n0 + tx;
+        t[r][tx] = (k < K && n < N) ? __ldg(B + (long long) k * ldb + n) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int n = n0 + r, k = k0 + tx;
+        if (n < N && k < Kp) {
+            float h, l;
+            split_tf32(t[tx][r], h, l);
+            hi[(long long) n * Kp + k] = h;
+            lo[(long long) n * Kp + k] = l;
+        }
+    }
+}
+
+// sum of split-K partial planes -> C
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ part, long long plane, int splits, float* __restrict__ C, int M, int N, int ldc,
+                     int accumulate) {
+    const long long total = (long long) M * N;
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long) gridDim.x * blockDim.x) {
+        const int m = (int) (i / N), n = (int) (i - (long long) m * N);
+        float s = 0.f;
+        for (int p = 0; p < splits; p++) s += part[(long long) p * plane + i];
+        float* dst = C + (long long) m * ldc + n;
+        *dst = accumulate ? *dst + s : s;
+    }
+}
+
+// ------------------------------------------------------------- host side
+
+typedef CUresult (*encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_fn_t encode_fn() {
+    static encode_fn_t fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (encode_fn_t) p;
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+// rows x K plane (leading dimension Kp floats), boxes of box_rows x 32 floats, 128-byte swizzle, zero fill
+int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int box_rows) {
+    encode_fn_t enc = encode_fn();
+    if (!enc) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return CAKEB200_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t) K, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) Kp * 4};
+    cuuint32_t box[2] = {(cuuint32_t) BK, (cuuint32_t) box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*) base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code %d (rows %d, K %d, Kp %d)", (int) r, rows, K, Kp);
+        return CAKEB200_ERR_CUDA;
+    }
+    return CAKEB200_OK;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
+
+// K ranges per tile so that the machine is filled when there are few tiles
+int choose_splits(long long tiles, int kblocks, int sm_count) {
+    if (tiles * 2 > sm_count) return 1;
+    int s = (int) (sm_count / tiles);
+    s = std::min(s, std::max(kblocks / 8, 1));  // at least 8 k-blocks (256 of K) per range
+    return std::max(1, std::min(s, 32));
+}
+
+template <int BN>
+int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, int splits,
+           int* status_word, int sm_count, cudaStream_t stream) {
+    const int Kp = padded_k(g.K);
+    alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    int rc;
+    if ((rc = make_map(&ma_hi, a_hi, g.M, g.K, Kp, BM))) return rc;
+    if ((rc = make_map(&ma_lo, a_lo, g.M, g.K, Kp, BM))) return rc;
+    if ((rc = make_map(&mb_hi, b_hi, g.N, g.K, Kp, BN))) return rc;
+    if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, BN))) return rc;
+
+    Tf32x3Args a;
+    a.M = g.M; a.N = g.N; a.K = g.K;
+    a.tiles_m = (g.M + BM - 1) / BM;
+    a.tiles_n = (g.N + BN - 1) / BN;
+    a.kblocks = (g.K + BK - 1) / BK;
+    a.splits = splits;
+    a.order = g.order;
+    a.status_word = status_word;
+    if (splits > 1) {
+        a.C = partials; a.plane = (long long) g.M * g.N; a.ldc = g.N; a.accumulate = 0;
+    } else {
+        a.C = g.C; a.plane = 0; a.ldc = g.ldc; a.accumulate = g.accumulate;
+    }
+    const long long units = (long long) a.tiles_m * a.tiles_n * splits;
+    if (units > 0x7fffffffLL) {
+        set_error("sgemm_tf32x3: too many tiles");
+        return CAKEB200_ERR_TOO_LARGE;
+    }
+    CAKE_CUDA_OK(cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+    const int grid = (int) std::min<long long>(units, sm_count);
+    sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
+
+}  // namespace
+
+// scratch = A hi/lo planes + transposed B hi/lo planes + split-K partials (worst case)
+size_t tf32x3_scratch_bytes(int M, int N, int K) {
+    const size_t Kp = (size_t) padded_k(K);
+    const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
+    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + 127) / 128);
+    const size_t part = (tiles * 2 <= 148) ? align_up((size_t) 32 * M * N * 4, 1024) : 0;
+    return 2 * a + 2 * b + part + 1024;
+}
+
+int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word, int sm_count,
+                        cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events) {
+    if (g.batch != 1) {
+        set_error("sgemm_tf32x3: batched products are not supported by this kernel");
+        return CAKEB200_ERR_ARG;
+    }
+    const int Kp = padded_k(g.K);
+    const size_t a_bytes = align_up((size_t) g.M * Kp * 4, 1024), b_bytes = align_up((size_t) g.N * Kp * 4, 1024);
+    char* base = (char*) align_up((size_t) scratch, 1024);
+    float* a_hi = (float*) base;
+    float* a_lo = (float*) (base + a_bytes);
+    float* b_hi = (float*) (base + 2 * a_bytes);
+    float* b_lo = (float*) (base + 2 * a_bytes + b_bytes);
+    float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
+
+    const int bn = (g.N > 128) ? 256 : 128;
+    const long long tiles = (long long) ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
+    const int splits = choose_splits(tiles, (g.K + BK - 1) / BK, sm_count);
+    const size_t need = 2 * a_bytes + 2 * b_bytes + (splits > 1 ? (size_t) splits * g.M * g.N * 4 : 0) + 1024;
+    if (need > scratch_bytes) {
+        set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
+        return CAKEB200_ERR_ARG;
+    }
+
+    if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[0], stream));
+    {
+        const long long total = (long long) g.M * Kp;
+        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
+        split_rows_kernel<<<blocks, 256, 0, stream>>>(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp);
+        dim3 grid((g.N + 31) / 32, (Kp + 31) / 32);
+        if (grid.y > 65535) {
+            set_error("sgemm_tf32x3: K too large for the transpose grid");
+            return CAKEB200_ERR_TOO_LARGE;
+        }
+        split_transpose_kernel<<<grid, 256, 0, stream>>>(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp);
+        CAKE_CUDA_OK(cudaGetLastError());
+    }
+    if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
+
+    int rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream)
+                         : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream);
+    if (rc) return rc;
+    int launches = 3;
+    if (splits > 1) {
+        const long long total = (long long) g.M * g.N;
+        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partials, (long long) g.M * g.N, splits, g.C, g.M, g.N, g.ldc, g.accumulate);
+        CAKE_CUDA_OK(cudaGetLastError());
+        launches++;
+    }
+    if (stats) {
+        stats->launches += launches;
+        stats->tile_m = BM; stats->tile_n = bn; stats->tile_k = BK;
+    }
+    return CAKEB200_OK;
+}
+
+}  // namespace cakeb200

@@ -1,0 +1,185 @@
+// Sparse-A SGEMM: C = A*B with A mostly zero.
+//
+// The reference's sparse microkernel (cake_sp_sgemm_haswell_6x16,
+// src/kernels/haswell/sparse.cpp:7-131) walks the stored columns of an A tile
+// and, for every nonzero a[m,k], issues C[m,:] = fma(a, B[k,:], C[m,:]); zeros
+// issue nothing.  Here A is first compacted on the device into per-row
+// (column, value) lists with warp ballots (each 32-column chunk yields a bitmap
+// whose popcount places the survivors), then a CTA that owns BM rows x BN
+// columns of C streams BK-deep slabs of B through shared memory and lets every
+// warp replay its rows' nonzeros against the slab.  Per C element the FMAs run
+// over k ascending, so the result equals the row-skipping CPU order bit for bit.
+#include "common.cuh"
+
+namespace cakeb200 {
+namespace {
+
+// nonzeros per row; one warp per row, 128-bit loads when the row is aligned
+__global__ void __launch_bounds__(256) row_nnz_kernel(const float* __restrict__ A, int M, int K, int* __restrict__ cnt) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const float* row = A + (long long) warp * K;
+    int n = 0;
+    for (int k = lane; k < K; k += 32) n += (__ldg(row + k) != 0.0f);
+    for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    if (lane == 0) cnt[warp] = n;
+}
+
+// exclusive scan of cnt[0..M) into ptr[0..M]; single CTA, M is at most a few 100k
+__global__ void __launch_bounds__(1024) row_ptr_kernel(const int* __restrict__ cnt, int M, long long* __restrict__ ptr) {
+    __shared__ long long part[1024];
+    const int t = threadIdx.x;
+    const int per = (M + 1023) / 1024;
+    const int lo = min(t * per, M), hi = min(lo + per, M);
+    long long s = 0;
+    for (int i = lo; i < hi; i++) s += cnt[i];
+    part[t] = s;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+        long long v = (t >= o) ? part[t - o] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    long long run = (t == 0) ? 0 : part[t - 1];
+    for (int i = lo; i < hi; i++) {
+        ptr[i] = run;
+        run += cnt[i];
+    }
+    if (t == 1023) ptr[M] = part[1023];
+}
+
+// warp-level compaction: ballot -> bitmap of survivors, popcount of the lower lanes -> slot
+__global__ void __launch_bounds__(256)
+compact_rows_kernel(const float* __restrict__ A, int M, int K, const long long* __restrict__ ptr,
+                    int* __restrict__ cols, float* __restrict__ vals) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const float* row = A + (long long) warp * K;
+    long long base = ptr[warp];
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        const float v = (k < K) ? __ldg(row + k) : 0.0f;
+        const unsigned bitmap = __ballot_sync(0xffffffffu, v != 0.0f);
+        if (v != 0.0f) {
+            const long long slot = base + __popc(bitmap & ((1u << lane) - 1u));
+            cols[slot] = k;
+            vals[slot] = v;
+        }
+        base += __popc(bitmap);
+    }
+}
+
+constexpr int SP_BM = 64, SP_BN = 128, SP_BK = 64, SP_WARPS = 8, SP_ROWS = SP_BM / SP_WARPS;
+
+template <bool VEC>
+__global__ void __launch_bounds__(SP_WARPS * 32)
+spmm_rows_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols, const float* __restrict__ vals,
+                 const float* __restrict__ B, float* __restrict__ C, int M, int N, int K) {
+    __shared__ __align__(16) float Bs[SP_BK][SP_BN];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * SP_BM + warp * SP_ROWS, n0 = blockIdx.x * SP_BN;
+
+    long long cur[SP_ROWS], end[SP_ROWS];
+    float acc[SP_ROWS][4];
+#pragma unroll
+    for (int r = 0; r < SP_ROWS; r++) {
+        const int m = m0 + r;
+        cur[r] = (m < M) ? ptr[m] : 0;
+        end[r] = (m < M) ? ptr[m + 1] : 0;
+        acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+    }
+
+    for (int k0 = 0; k0 < K; k0 += SP_BK) {
+        __syncthreads();  // previous slab fully consumed
+        for (int i = threadIdx.x; i < SP_BK * SP_BN / 4; i += SP_WARPS * 32) {
+            const int r = i / (SP_BN / 4), c = (i % (SP_BN / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + r < K) {
+                const float* src = B + (long long) (k0 + r) * N + n0 + c;
+                if (VEC) {
+                    if (n0 + c < N) v = __ldg(reinterpret_cast<const float4*>(src));
+                } else {
+                    if (n0 + c + 0 < N) v.x = __ldg(src + 0);
+                    if (n0 + c + 1 < N) v.y = __ldg(src + 1);
+                    if (n0 + c + 2 < N) v.z = __ldg(src + 2);
+                    if (n0 + c + 3 < N) v.w = __ldg(src + 3);
+                }
+            }
+            *reinterpret_cast<float4*>(&Bs[r][c]) = v;
+        }
+        __syncthreads();
+        const int k_hi = k0 + SP_BK;
+#pragma unroll
+        for (int r = 0; r < SP_ROWS; r++) {
+            long long c = cur[r];
+            const long long e = end[r];
+            while (c < e) {
+                const int k = __ldg(cols + c);  // same address in every lane: one broadcast load
+                if (k >= k_hi) break;
+                const float a = __ldg(vals + c);
+                const float4 b = *reinterpret_cast<const float4*>(&Bs[k - k0][lane * 4]);
+                acc[r][0] = fmaf(a, b.x, acc[r][0]);
+                acc[r][1] = fmaf(a, b.y, acc[r][1]);
+                acc[r][2] = fmaf(a, b.z, acc[r][2]);
+                acc[r][3] = fmaf(a, b.w, acc[r][3]);
+                c++;
+            }
+            cur[r] = c;
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < SP_ROWS; r++) {
+        const int m = m0 + r, n = n0 + lane * 4;
+        if (m >= M) continue;
+        float* dst = C + (long long) m * N + n;
+        if (VEC) {
+            if (n < N) *reinterpret_cast<float4*>(dst) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (n + j < N) dst[j] = acc[r][j];
+        }
+    }
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+// Scratch layout: [cnt: M ints][ptr: M+1 int64][cols: nnz ints][vals: nnz floats].
+// The compacted lists are sized for the worst case (every entry nonzero) so the
+// whole call needs a single allocation and no device->host round trip.
+size_t sparse_scratch_bytes(int M, int K) {
+    const size_t cells = (size_t) M * K;
+    return align_up((size_t) M * 4, 256) + align_up(((size_t) M + 1) * 8, 256) + align_up(cells * 4, 256) * 2;
+}
+
+int launch_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K, void* scratch,
+                    cudaStream_t stream, int* launches) {
+    char* base = (char*) scratch;
+    int* cnt = (int*) base;
+    base += align_up((size_t) M * 4, 256);
+    long long* ptr = (long long*) base;
+    base += align_up(((size_t) M + 1) * 8, 256);
+    int* cols = (int*) base;
+    base += align_up((size_t) M * K * 4, 256);
+    float* vals = (float*) base;
+
+    const int row_blocks = (M + 7) / 8;  // 8 warps (rows) per 256-thread CTA
+    row_nnz_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, cnt);
+    row_ptr_kernel<<<1, 1024, 0, stream>>>(cnt, M, ptr);
+    compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, ptr, cols, vals);
+    dim3 grid((N + SP_BN - 1) / SP_BN, (M + SP_BM - 1) / SP_BM);
+    const bool vec = (N % 4 == 0) && (((uintptr_t) B | (uintptr_t) C) % 16 == 0);
+    if (vec)
+        spmm_rows_kernel<true><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K);
+    else
+        spmm_rows_kernel<false><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K);
+    CAKE_CUDA_OK(cudaGetLastError());
+    if (launches) *launches += 4;
+    return CAKEB200_OK;
+}
+
+}  // namespace cakeb200

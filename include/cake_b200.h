@@ -1,0 +1,168 @@
+/* cake_b200.h -- the C ABI of the B200 implementation of the CAKE SGEMM path.
+ *
+ * Plain pointers and sizes only.  Every matrix is FP32, row-major, dense, with
+ * the leading dimension equal to its column count (A[m*K+k], B[k*N+n],
+ * C[m*N+n]) exactly as in vnatesh/CAKE_on_CPU (src/util.cpp:183).  Each data
+ * pointer may be a HOST pointer (pageable or pinned) or a DEVICE pointer of the
+ * current CUDA device; host operands are copied to the device and the result is
+ * copied back inside the call.  All entry points return CAKEB200_OK (0) or a
+ * negative status; cakeb200_last_error() gives the text.  Nothing here calls
+ * exit() and no kernel traps: device-side waits are bounded and report through
+ * CAKEB200_ERR_DEVICE_TIMEOUT.
+ *
+ * The C++ API of the reference (include/cake.h of this repository, same
+ * prototypes as the reference's include/cake.h:12-76) is a thin layer over
+ * these functions.
+ */
+#ifndef CAKE_B200_H
+#define CAKE_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    CAKEB200_OK = 0,
+    CAKEB200_ERR_ARG = -1,            /* bad size / null pointer / unknown enum */
+    CAKEB200_ERR_CUDA = -2,           /* a CUDA runtime call failed */
+    CAKEB200_ERR_NO_DEVICE = -3,      /* no usable sm_100 device */
+    CAKEB200_ERR_DEVICE_TIMEOUT = -4, /* a bounded device-side wait gave up */
+    CAKEB200_ERR_TOO_LARGE = -5       /* exceeds a documented fixed limit */
+};
+
+/* Block schedules, same numbering as `enum sched` (reference include/common.h:105). */
+enum { CAKEB200_SCHED_KMN = 0, CAKEB200_SCHED_MKN = 1, CAKEB200_SCHED_NKM = 2, CAKEB200_SCHED_NA = 3 };
+
+/* Which arithmetic kernel computes the contraction. */
+enum {
+    CAKEB200_KERNEL_AUTO = 0,
+    CAKEB200_KERNEL_TF32X3 = 1, /* tcgen05 tensor cores, FP32 split into two TF32 terms, 3 MMAs */
+    CAKEB200_KERNEL_FFMA = 2    /* exact FP32 fused multiply-add on the CUDA cores */
+};
+
+/* Timings of the last call on this thread, milliseconds, from CUDA events. */
+typedef struct cakeb200_stats {
+    float ms_h2d;     /* host -> device copies (0 for device operands) */
+    float ms_prepass; /* operand split / pack kernels */
+    float ms_gemm;    /* the contraction kernel(s) */
+    float ms_d2h;     /* device -> host copy of the result */
+    int kernel;       /* CAKEB200_KERNEL_* that ran */
+    int sched;        /* CAKEB200_SCHED_* that ordered the tiles */
+    int tile_m, tile_n, tile_k;
+    int launches;     /* kernels of this library launched by the call */
+} cakeb200_stats;
+
+/* Machine description the block-sizing formulas consume; mirrors the fields of
+ * cake_cntx_t that the reference reads (reference include/common.h:138-151). */
+typedef struct cakeb200_cntx {
+    double alpha_n;
+    int mr, nr;
+    int L1, L2, L3;
+    int ncores;
+} cakeb200_cntx;
+
+/* Field-for-field the reference's blk_dims_t (reference include/common.h:108-135). */
+typedef struct cakeb200_blk_dims {
+    int m_c, k_c, n_c, m_c1, k_c1, n_c1;
+    int m_c1_last_core, n_c1_last_core, k_c1_last_core;
+    int mr_rem, nr_rem, k_rem;
+    int p_l, pm_l, pn_l, pm, pn;
+    int m_pad, k_pad, n_pad;
+    int Mb, Kb, Nb;
+    int M_padded, N_padded;
+    int sch;
+} cakeb200_blk_dims;
+
+const char* cakeb200_last_error(void);
+void cakeb200_get_stats(cakeb200_stats* out);
+
+/* Number of visible CUDA devices with compute capability 10.x. */
+int cakeb200_device_count(void);
+
+/* Fills a context for the current device: L1 = shared memory per SM,
+ * L2 = device L2 bytes, L3 = min(HBM bytes, INT_MAX), ncores = visible devices,
+ * mr x nr = 128 x 256 (the MMA tile).  Replaces cake_query_cntx()
+ * (reference src/block_sizing.cpp:40-75). */
+int cakeb200_query_cntx(cakeb200_cntx* out);
+
+/* C = A*B (accumulate == 0) or C += A*B (accumulate != 0).
+ * Replaces cake_sgemm() (reference src/cake_sgemm.cpp:9-175; prototype
+ * include/cake.h:12-14).  `sched` orders the output tiles (KMN: K innermost
+ * per tile with a snake over tiles; MKN: M-fastest; NKM: N-fastest; NA: derive
+ * from the shape as derive_schedule does, reference src/block_sizing.cpp:434-462).
+ * `stream` is a cudaStream_t (NULL = the library's own stream); the call
+ * returns after the work on that stream has finished. */
+int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K,
+                   int accumulate, int sched, int kernel, void* stream);
+
+/* Same, but only enqueues on `stream` (device pointers required, no host copies,
+ * no synchronisation).  For callers that time or overlap the work themselves. */
+int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K,
+                         int accumulate, int sched, int kernel, void* stream);
+
+/* `batch` independent products of identical shape, item i at A + i*M*K etc.
+ * Replaces the small-matrix entry points cake_gemm_small / schedule_*_small
+ * (reference include/cake.h:52-72, src/cake_sgemm_small.cpp:7-236), whose live
+ * equivalent in the reference is one cake_sgemm call per item. */
+int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K,
+                           int batch, int kernel, void* stream);
+
+/* C = A*B where A is mostly zero: A is compacted on the device to a per-row
+ * list of (column, value) and only the nonzeros are multiplied.  Replaces the
+ * sparse microkernel cake_sp_sgemm_haswell_6x16 (reference
+ * src/kernels/haswell/sparse.cpp:7-131), which the reference never schedules. */
+int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K,
+                      int kernel, void* stream);
+
+/* NCHW convolution through im2col + SGEMM: out[b][co][ho][wo].  Replaces the
+ * GEMM route of the reference's convolution example (im_2_col + cake_sgemm,
+ * reference examples/cake_conv.cpp:1007-1066,1178-1213), extended with batch,
+ * stride and zero padding. */
+int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch, int cin,
+                    int H, int W, int cout, int hf, int wf, int stride, int pad,
+                    int kernel, void* stream);
+
+/* im2col alone (reference examples/cake_conv.cpp:1178-1213): col[(cin,hf,wf)][(b,ho,wo)]. */
+int cakeb200_im2col(const float* in, float* col, int batch, int cin, int H, int W,
+                    int hf, int wf, int stride, int pad, void* stream);
+
+/* Block sizing: replaces init_block_dims / get_cache_dims / derive_schedule
+ * (reference src/block_sizing.cpp:304-595) and set_schedule
+ * (reference src/cake_sgemm.cpp:768-787).  `cntx->alpha_n` is updated as the
+ * reference does. */
+int cakeb200_init_block_dims(int M, int N, int K, int p, cakeb200_blk_dims* x, cakeb200_cntx* cntx,
+                             int sched, int mcu, int kcu, int ncu);
+int cakeb200_derive_schedule(int M, int N, int K, int p, int mc_ret, const cakeb200_cntx* cntx);
+int cakeb200_set_schedule(int sched, int M, int N, int K);
+
+/* Byte sizes of the packed operands: replaces cake_sgemm_packed_{A,B,C}_size
+ * (reference src/pack_helper.cpp:5-87). */
+size_t cakeb200_packed_A_size(int M, int K, int p, const cakeb200_blk_dims* x, const cakeb200_cntx* cntx, int sched);
+size_t cakeb200_packed_B_size(int K, int N, int p, const cakeb200_blk_dims* x, const cakeb200_cntx* cntx);
+size_t cakeb200_packed_C_size(int M, int N, int p, const cakeb200_blk_dims* x, const cakeb200_cntx* cntx, int sched);
+
+/* Layout-exact packing on the device: the output buffer holds exactly the
+ * bytes the reference's packers produce for the same block dimensions
+ * (padding positions are zero).  Replace pack_A / pack_B / pack_C / unpack_C
+ * (reference src/pack_helper.cpp:92-184 and the routines they dispatch to in
+ * src/pack_{k,m,n}_first.cpp, src/unpack_{k,m,n}_first.cpp, src/pack_ob.cpp). */
+int cakeb200_pack_A(const float* A, float* A_p, int M, int K, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* cntx, void* stream);
+int cakeb200_pack_B(const float* B, float* B_p, int K, int N, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* cntx, void* stream);
+int cakeb200_pack_C(const float* C, float* C_p, int M, int N, int p, const cakeb200_blk_dims* x,
+                    const cakeb200_cntx* cntx, void* stream);
+int cakeb200_unpack_C(float* C, const float* C_p, int M, int N, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* cntx, void* stream);
+/* Inverses of pack_A / pack_B, used when cake_sgemm is handed pre-packed operands. */
+int cakeb200_unpack_A(float* A, const float* A_p, int M, int K, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* cntx, void* stream);
+int cakeb200_unpack_B(float* B, const float* B_p, int K, int N, int p, const cakeb200_blk_dims* x,
+                      const cakeb200_cntx* cntx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

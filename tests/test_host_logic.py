@@ -1,0 +1,96 @@
+"""CPU-only checks of the product's host side: the shared library loads and
+exports every symbol include/cake_b200.h declares, and the host block-sizing
+code agrees with the oracle (no GPU compute is called here)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from _oracle import KMN, MKN, NKM, NA, DEFAULT_CACHES, BLK_FIELDS
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(cake):
+    header = open(os.path.join(ROOT, "include", "cake_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(cakeb200_[a-zA-Z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 20
+    L = ctypes.CDLL(cake.library_path())
+    for name in declared:
+        assert hasattr(L, name), name
+    from cake_on_cpu_b200.api import EXPORTED_SYMBOLS
+    assert set(EXPORTED_SYMBOLS) <= set(declared)
+
+
+def test_cpp_api_symbols_present(cake):
+    # the C++ API keeps the reference's (mangled) names: cake_sgemm, pack_A, init_block_dims, ...
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", "-C", cake.library_path()], capture_output=True, text=True).stdout
+    for name in ["cake_sgemm(", "cake_sgemm_online(", "cake_sgemm_2d(", "schedule_KMN(", "schedule_MKN(", "schedule_NKM(",
+                 "schedule(", "set_schedule(", "cake_query_cntx(", "cake_query_cntx_torch(", "update_mr_nr(",
+                 "derive_schedule(", "get_cache_dims(", "init_block_dims(", "grid_dims_2d(", "pack_A(", "pack_B(",
+                 "pack_C(", "unpack_C(", "cake_sgemm_packed_A_size(", "cake_sgemm_packed_B_size(",
+                 "cake_sgemm_packed_C_size(", "rand_init(", "cake_sgemm_checker(", "mat_equals(", "run_tests(",
+                 "cake_gemm_small("]:
+        assert name in out, name
+
+
+def test_no_gpu_means_loud_failure(cake):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    A = np.zeros((8, 8), np.float32)
+    with pytest.raises(cake.CakeError):
+        cake.cake_sgemm(A, A)
+
+
+@pytest.mark.parametrize("p", [1, 2, 5, 8, 10])
+def test_block_dims_match_oracle(cake, oracle, p):
+    dims = (1, 10, 96, 111, 960, 2111, 8192)
+    for M in dims:
+        for K in dims:
+            for N in dims:
+                for sch in (KMN, MKN, NKM, NA):
+                    cx = cake.Cntx.make(*DEFAULT_CACHES)
+                    x = cake.init_block_dims(M, N, K, p, cx, sch).as_dict()
+                    want = oracle.block_dims(M, N, K, p, sch)
+                    assert {k: x[k] for k in BLK_FIELDS} == {k: want[k] for k in BLK_FIELDS}, (M, K, N, p, sch)
+                    assert cx.alpha_n == want["alpha_n"]
+                    xs = cake.init_block_dims(M, N, K, p, cake.Cntx.make(*DEFAULT_CACHES), sch)
+                    cx2 = cake.Cntx.make(*DEFAULT_CACHES)
+                    got = (cake.cake_sgemm_packed_A_size(M, K, p, xs, cx2, xs.sch),
+                           cake.cake_sgemm_packed_B_size(K, N, p, xs, cx2),
+                           cake.cake_sgemm_packed_C_size(M, N, p, xs, cx2, xs.sch))
+                    assert got == oracle.packed_sizes(M, N, K, p, sch)
+
+
+def test_benchmark_shapes_and_user_blocks(cake, oracle):
+    shapes = [(3000, 3000, 3000), (8192, 8192, 8192), (32768, 32768, 32768), (65536, 1024, 1024), (1024, 1024, 65536),
+              (1024, 262144, 1024), (96, 96, 96), (64, 576, 200704), (512, 2304, 12544)]
+    for (M, K, N) in shapes:
+        for blk in ((0, 0, 0), (48, 64, 96)):
+            x = cake.init_block_dims(M, N, K, 8, cake.Cntx.make(*DEFAULT_CACHES), NA, *blk).as_dict()
+            want = oracle.block_dims(M, N, K, 8, NA, blk=blk)
+            assert {k: x[k] for k in BLK_FIELDS} == {k: want[k] for k in BLK_FIELDS}
+
+
+def test_schedule_helpers(cake, oracle):
+    for M in (1, 100, 1000, 70000):
+        for N in (1, 100, 1000, 70000):
+            for K in (1, 100, 1000, 300000):
+                assert cake.set_schedule(NA, M, N, K) == oracle.set_schedule(NA, M, N, K)
+                assert cake.set_schedule(MKN, M, N, K) == MKN
+                for mc in (6, 96, 492):
+                    cx = cake.Cntx.make(*DEFAULT_CACHES)
+                    cx.alpha_n = 0.84
+                    assert cake.derive_schedule(M, N, K, 8, mc, cx) == oracle.derive_schedule(M, N, K, 8, mc, 0.84)
+
+
+def test_bad_arguments_are_reported_not_fatal(cake):
+    cx = cake.Cntx.make(*DEFAULT_CACHES)
+    with pytest.raises(cake.CakeError):
+        cake.init_block_dims(0, 10, 10, 2, cx, NA)
+    with pytest.raises(cake.CakeError):
+        cake.init_block_dims(10, 10, 10, 2, cx, 7)

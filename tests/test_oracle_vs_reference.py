@@ -1,0 +1,86 @@
+"""Pins the CPU oracle to the unmodified reference, live, wherever the
+reference library could be built (oracle/_ref/).  Everything is compared
+bit for bit on the reference's own grid of awkward sizes
+(src/util.cpp:12-13: 1, 10, 96, 111, 960, 2111)."""
+import numpy as np
+import pytest
+
+from _oracle import KMN, MKN, NKM, NA
+
+DIMS = (1, 10, 96, 111)
+CASES = [(M, K, N) for M in DIMS for K in DIMS for N in DIMS]
+CASES += [(960, 111, 96), (96, 960, 111), (111, 96, 960), (2111, 96, 111), (300, 2111, 50), (37, 53, 2111),
+          (960, 960, 960)]
+
+
+@pytest.mark.parametrize("p", [2, 3, 8])
+def test_sgemm_blockdims_and_packers_bit_exact(oracle, reference, p):
+    rng = np.random.default_rng(p)
+    for (M, K, N) in CASES:
+        A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+        B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+        for sch in (KMN, MKN, NKM, NA):
+            bo, br = oracle.block_dims(M, N, K, p, sch), reference.block_dims(M, N, K, p, sch)
+            assert bo == br, (M, K, N, p, sch)
+            Co, ran = oracle.sgemm(A, B, p, sch)
+            Cr, _ = reference.sgemm(A, B, p, sch)
+            assert np.array_equal(Co, Cr), (M, K, N, p, sch)
+            assert ran == bo["sch"]
+            assert oracle.packed_sizes(M, N, K, p, sch) == reference.packed_sizes(M, N, K, p, sch)
+            # pack_A: every position, padding included
+            assert np.array_equal(oracle.pack(0, A, M, N, K, p, sch), reference.pack(0, A, M, N, K, p, sch))
+            # pack_B: the reference's M-/N-first packers copy whatever follows a row into the pad
+            # columns instead of zero (src/pack_ob.cpp:126-138); compare the positions that hold data
+            po, pr = oracle.pack(1, B, M, N, K, p, sch), reference.pack(1, B, M, N, K, p, sch)
+            if bo["sch"] != KMN:
+                keep = oracle.pack(1, np.ones_like(B), M, N, K, p, sch) != 0
+                po, pr = po[keep], pr[keep]
+            assert np.array_equal(po, pr), (M, K, N, p, sch)
+            # pack_C / unpack_C: the reference's N-first pack_C is only defined for aligned shapes
+            aligned = M % (p * bo["m_c"]) == 0 and N % bo["n_c"] == 0
+            if bo["sch"] != NKM or aligned:
+                Pc = reference.pack(2, Cr, M, N, K, p, sch)
+                assert np.array_equal(oracle.pack(2, Cr, M, N, K, p, sch), Pc)
+                assert np.array_equal(oracle.pack(3, Pc, M, N, K, p, sch), Cr)
+                assert np.array_equal(reference.pack(3, Pc, M, N, K, p, sch), Cr)
+
+
+def test_beta_flag_semantics(oracle, reference):
+    rng = np.random.default_rng(7)
+    M, K, N, p = 111, 96, 211, 4
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    for sch in (KMN, MKN):
+        Co, _ = oracle.sgemm(A, B, p, sch, beta=1.0, C=C0)
+        Cr, _ = reference.sgemm(A, B, p, sch, beta=1.0, C=C0)
+        assert np.array_equal(Co, Cr)
+    plain, _ = reference.sgemm(A, B, p, KMN)
+    kept, _ = reference.sgemm(A, B, p, KMN, beta=1.0, C=C0)
+    assert np.array_equal(plain, kept)  # K-first ignores beta and overwrites
+
+
+def test_user_block_sizes_and_other_drivers(oracle, reference):
+    rng = np.random.default_rng(9)
+    M, K, N, p = 300, 200, 260, 4
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    for sch in (KMN, MKN, NKM):
+        Co, _ = oracle.sgemm(A, B, p, sch, blk=(24, 40, 64))
+        Cr, _ = reference.sgemm(A, B, p, sch, blk=(24, 40, 64))
+        assert np.array_equal(Co, Cr)
+    # the online-packing and 2-D drivers of the reference agree with the float64 product
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    for variant in (1, 2):
+        Cv, _ = reference.sgemm(A, B, p, KMN, variant=variant)
+        assert np.abs(Cv - ref64).max() < 1e-3
+    assert reference.checker(A, B, Cr) == 0
+
+
+def test_rectangular_benchmark_shapes_scaled_down(oracle, reference):
+    # 1/16-scale versions of the M-first / N-first / K-first benchmark shapes
+    for (M, K, N) in [(4096, 64, 64), (64, 64, 4096), (64, 16384, 64)]:
+        A, B = oracle.uniform((M, K), 1), oracle.uniform((K, N), 2)
+        Co, so = oracle.sgemm(A, B, 8, NA)
+        Cr, _ = reference.sgemm(A, B, 8, NA)
+        assert np.array_equal(Co, Cr)
