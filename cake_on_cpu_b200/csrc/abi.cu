@@ -183,7 +183,7 @@ int run_dense(DeviceState* st, GemmProblem& g, int kernel, cudaStream_t s, bool 
         set_error("unknown kernel id %d", kernel);
         return CAKEB200_ERR_ARG;
     }
-    const size_t need = tf32x3_scratch_bytes(g.M, g.N, g.K);
+    const size_t need = tf32x3_scratch_bytes(g.M, g.N, g.K, st->sm_count);
     int rc = ensure_scratch(st, need);
     if (rc) return rc;
     g_stats.ms_prepass = timed ? -1.0f : 0.0f;  // -1: events 4,5 hold the split-pass time

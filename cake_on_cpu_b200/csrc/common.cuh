@@ -54,7 +54,7 @@ int ensure_scratch(DeviceState* st, size_t bytes);
 // exact-FP32 FFMA path (sgemm_ffma.cu)
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);
 // 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
-size_t tf32x3_scratch_bytes(int M, int N, int K);
+size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
                         int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
 

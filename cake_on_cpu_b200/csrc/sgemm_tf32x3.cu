@@ -315,6 +315,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
             if (!ok) break;
             tcgen05_fence_after();
             const int row = tm * BM + quarter * 32 + lane;
@@ -471,12 +472,18 @@ int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int b
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
 
-// K ranges per tile so that the machine is filled when there are few tiles
-int choose_splits(long long tiles, int kblocks, int sm_count) {
-    if (tiles * 2 > sm_count) return 1;
+// Tile width and number of K ranges per tile.  With few output tiles the K
+// dimension is cut so that every SM still gets work (the role K-first blocking
+// plays in the reference when M and N are small, src/block_sizing.cpp:434-462).
+void plan_tiles(int M, int N, int K, int sm_count, int* bn, int* splits) {
+    *bn = (N > 128) ? 256 : 128;
+    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + *bn - 1) / *bn);
+    const int kblocks = (K + BK - 1) / BK;
+    *splits = 1;
+    if (tiles * 2 > sm_count) return;
     int s = (int) (sm_count / tiles);
     s = std::min(s, std::max(kblocks / 8, 1));  // at least 8 k-blocks (256 of K) per range
-    return std::max(1, std::min(s, 32));
+    *splits = std::max(1, std::min(s, 32));
 }
 
 template <int BN>
@@ -518,12 +525,13 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
 }  // namespace
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + split-K partials (worst case)
-size_t tf32x3_scratch_bytes(int M, int N, int K) {
+size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     const size_t Kp = (size_t) padded_k(K);
     const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
-    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + 127) / 128);
-    const size_t part = (tiles * 2 <= 148) ? align_up((size_t) 32 * M * N * 4, 1024) : 0;
-    return 2 * a + 2 * b + part + 1024;
+    int bn, splits;
+    plan_tiles(M, N, K, sm_count, &bn, &splits);
+    const size_t part = splits > 1 ? align_up((size_t) splits * M * N * 4, 1024) : 0;
+    return 2 * a + 2 * b + part + 2048;
 }
 
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word, int sm_count,
@@ -541,9 +549,8 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* b_lo = (float*) (base + 2 * a_bytes + b_bytes);
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
-    const int bn = (g.N > 128) ? 256 : 128;
-    const long long tiles = (long long) ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
-    const int splits = choose_splits(tiles, (g.K + BK - 1) / BK, sm_count);
+    int bn, splits;
+    plan_tiles(g.M, g.N, g.K, sm_count, &bn, &splits);
     const size_t need = 2 * a_bytes + 2 * b_bytes + (splits > 1 ? (size_t) splits * g.M * g.N * 4 : 0) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);

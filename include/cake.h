@@ -16,8 +16,15 @@
  */
 #pragma once
 
+/* the standard headers the reference's common.h makes visible to its callers */
+#include <math.h>
 #include <stdbool.h>
 #include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
 
 #include "cake_b200.h"
 

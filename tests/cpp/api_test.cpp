@@ -1,0 +1,97 @@
+// Drives the C++ API of include/cake.h the way a caller of the reference
+// library would (compare the reference's examples/cake_sgemm_test.cpp:5-90 and
+// the packed-operand calls in examples/cake_conv.cpp:1028-1056).
+// Exit code 0 = every check printed CORRECT.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "cake.h"
+
+static int failures = 0;
+static void expect(bool ok, const char* what) {
+    if (!ok) {
+        printf("FAILED: %s\n", what);
+        failures++;
+    }
+}
+
+int main(int argc, char* argv[]) {
+    int M = 777, K = 515, N = 1030, p = 4;
+    if (argc > 3) { M = atoi(argv[1]); K = atoi(argv[2]); N = atoi(argv[3]); }
+    std::vector<float> A((size_t) M * K), B((size_t) K * N), C((size_t) M * N);
+    srand(1);
+    rand_init(A.data(), M, K);
+    rand_init(B.data(), K, N);
+
+    cake_cntx_t* cntx = cake_query_cntx();
+    printf("context: mr=%d nr=%d L1=%d L2=%d L3=%d ncores=%d\n", cntx->mr, cntx->nr, cntx->L1, cntx->L2, cntx->L3, cntx->ncores);
+    expect(cntx->ncores >= 1 && cntx->L2 > 0, "cake_query_cntx");
+
+    const enum sched all[] = {KMN, MKN, NKM, NA};
+    for (enum sched s : all) {
+        std::fill(C.begin(), C.end(), -7.f);
+        double t = cake_sgemm(A.data(), B.data(), C.data(), M, N, K, p, cntx, NULL, 0, 0, 1, 0, s);
+        expect(t > 0, "cake_sgemm returned a time");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "cake_sgemm result");
+    }
+    // NULL context = query internally
+    expect(cake_sgemm(A.data(), B.data(), C.data(), M, N, K, p, NULL) > 0, "cake_sgemm with NULL context");
+    expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "NULL-context result");
+
+    // pre-packed operands, K-first (examples/cake_conv.cpp:1028-1056)
+    {
+        blk_dims_t x;
+        init_block_dims(M, N, K, p, &x, cntx, KMN, NULL);
+        std::vector<float> A_p(cake_sgemm_packed_A_size(M, K, p, &x, cntx, KMN) / 4);
+        std::vector<float> B_p(cake_sgemm_packed_B_size(K, N, p, &x, cntx) / 4);
+        expect(pack_A(A.data(), A_p.data(), M, K, p, &x, cntx, KMN) >= 0, "pack_A");
+        pack_B(B.data(), B_p.data(), K, N, p, &x, cntx, KMN);
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm(A_p.data(), B_p.data(), C.data(), M, N, K, p, cntx, NULL, 1, 1, 1, 0, KMN) > 0, "packed cake_sgemm");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "packed operands result");
+        std::fill(C.begin(), C.end(), -7.f);
+        schedule_KMN(A_p.data(), B_p.data(), C.data(), NULL, M, N, K, p, cntx, &x);
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN result");
+    }
+    // M-first on packed operands accumulates into packed C; unpack_C brings it back
+    {
+        blk_dims_t x;
+        init_block_dims(M, N, K, p, &x, cntx, MKN, NULL);
+        std::vector<float> A_p(cake_sgemm_packed_A_size(M, K, p, &x, cntx, MKN) / 4);
+        std::vector<float> B_p(cake_sgemm_packed_B_size(K, N, p, &x, cntx) / 4);
+        std::vector<float> C_p(cake_sgemm_packed_C_size(M, N, p, &x, cntx, MKN) / 4, 0.f);
+        pack_A(A.data(), A_p.data(), M, K, p, &x, cntx, MKN);
+        pack_B(B.data(), B_p.data(), K, N, p, &x, cntx, MKN);
+        schedule(A_p.data(), B_p.data(), C_p.data(), M, N, K, p, cntx, &x, MKN, 0, 0);
+        std::fill(C.begin(), C.end(), -7.f);
+        unpack_C(C.data(), C_p.data(), M, N, p, &x, cntx, MKN);
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule(MKN) + unpack_C result");
+    }
+    // beta != 0 with M-first adds to C (the reference's flag semantics)
+    {
+        std::vector<float> C1((size_t) M * N), C2((size_t) M * N, 1.5f);
+        cake_sgemm(A.data(), B.data(), C1.data(), M, N, K, p, cntx, NULL, 0, 0, 1, 0, MKN);
+        cake_sgemm(A.data(), B.data(), C2.data(), M, N, K, p, cntx, NULL, 0, 0, 1, 1, MKN);
+        double worst = 0;
+        for (size_t i = 0; i < C1.size(); i++) worst = std::max(worst, (double) fabsf(C2[i] - C1[i] - 1.5f));
+        expect(worst < 1e-3, "beta flag adds to C");
+    }
+    // small-matrix entry point
+    {
+        const int m = 96;
+        std::vector<float> a(m * m), b(m * m), c(m * m);
+        rand_init(a.data(), m, m);
+        rand_init(b.data(), m, m);
+        blk_dims_t x;
+        expect(cake_gemm_small(a.data(), b.data(), c.data(), m, m, m, p, &x, cntx, NA), "cake_gemm_small took the product");
+        expect(cake_sgemm_checker(a.data(), b.data(), c.data(), m, m, m) == 0, "cake_gemm_small result");
+    }
+    expect(set_schedule(NA, 4000, 100, 100) == MKN && set_schedule(NA, 100, 100, 4000) == KMN &&
+           set_schedule(NA, 100, 4000, 100) == NKM, "set_schedule");
+    free(cntx);
+    printf(failures ? "%d FAILURES\n" : "ALL CORRECT\n", failures);
+    return failures ? 1 : 0;
+}

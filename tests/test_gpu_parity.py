@@ -1,0 +1,227 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Gate (both kernels): max |C - C_ref| / (||A[m,:]||_2 ||B[:,n]||_2) <= 1e-5, where
+C_ref is the oracle's cake_sgemm (= the reference's result bit for bit).  Data
+movement (pack / unpack / im2col) and the sparse product are compared bit-exactly.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from _oracle import KMN, MKN, NKM, NA, DEFAULT_CACHES, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_golden.npz"))
+
+# the reference's own grid of awkward sizes (src/util.cpp:12-13)
+EDGE = (1, 10, 96, 111, 960)
+GRID = [(M, K, N) for M in EDGE for K in EDGE for N in EDGE if (M * K * N) <= 960 * 960 * 111]
+GRID += [(2111, 96, 111), (111, 2111, 96), (96, 111, 2111), (960, 960, 960), (2111, 2111, 10)]
+
+
+def _inputs(oracle, M, K, N):
+    return oracle.uniform((M, K), 1), oracle.uniform((K, N), 2)
+
+
+@pytest.mark.parametrize("kernel_name", ["ffma", "tf32x3"])
+def test_dense_grid_all_schedules(cake, oracle, kernel_name):
+    kernel = {"ffma": cake.KERNEL_FFMA, "tf32x3": cake.KERNEL_TF32X3}[kernel_name]
+    worst = 0.0
+    for i, (M, K, N) in enumerate(GRID):
+        A, B = _inputs(oracle, M, K, N)
+        scheds = (KMN, MKN, NKM, NA) if i % 4 == 0 else ((KMN, MKN, NKM, NA)[i % 4],)
+        for sch in scheds:
+            ref, _ = oracle.sgemm(A, B, 8, sch)
+            C = np.full((M, N), np.nan, np.float32)
+            cake.cake_sgemm(A, B, C, p=8, sch=sch, kernel=kernel)
+            assert cake.last_stats()["kernel"] == kernel
+            err = rel_err(C, ref, A, B)
+            worst = max(worst, err)
+            assert err <= TOL, (kernel_name, M, K, N, sch, err)
+    print("worst normalised error (%s): %.3e" % (kernel_name, worst))
+
+
+@pytest.mark.parametrize("key", sorted(k for k in GOLDEN.files if k.startswith("sgemm_")))
+def test_dense_against_reference_golden(cake, oracle, key):
+    M, K, N, p, sch = (int(v) for v in key.split("_")[1:])
+    A, B = _inputs(oracle, M, K, N)
+    for kernel in (cake.KERNEL_FFMA, cake.KERNEL_TF32X3):
+        C = cake.cake_sgemm(A, B, sch=sch, kernel=kernel)
+        assert rel_err(C, GOLDEN[key], A, B) <= TOL
+
+
+def test_auto_kernel_and_device_pointers(cake, oracle):
+    import torch
+    M, K, N = 777, 515, 1030
+    A, B = _inputs(oracle, M, K, N)
+    ref, _ = oracle.sgemm(A, B, 8, NA)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    for kernel in (cake.KERNEL_AUTO, cake.KERNEL_FFMA, cake.KERNEL_TF32X3):
+        dC = torch.full((M, N), float("nan"), device="cuda")
+        cake.cake_sgemm(dA, dB, dC, kernel=kernel)
+        assert rel_err(dC.cpu().numpy(), ref, A, B) <= TOL
+    assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+    # AUTO picks the tensor-core kernel for this size and FFMA for a tiny one
+    cake.cake_sgemm(dA, dB, dC, kernel=cake.KERNEL_AUTO)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+    cake.cake_sgemm(A[:8], B, kernel=cake.KERNEL_AUTO)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_FFMA
+
+
+def test_beta_flag_matches_reference_semantics(cake, oracle):
+    M, K, N = 300, 200, 260
+    A, B = _inputs(oracle, M, K, N)
+    C0 = oracle.uniform((M, N), 3)
+    for kernel in (cake.KERNEL_FFMA, cake.KERNEL_TF32X3):
+        for sch in (MKN, NKM):
+            ref, _ = oracle.sgemm(A, B, 8, sch, beta=1.0, C=C0)
+            C = C0.copy()
+            cake.cake_sgemm(A, B, C, beta=1.0, sch=sch, kernel=kernel)
+            assert rel_err(C, ref, A, B) <= TOL
+        ref, _ = oracle.sgemm(A, B, 8, KMN, beta=1.0, C=C0)  # K-first overwrites
+        C = C0.copy()
+        cake.cake_sgemm(A, B, C, beta=1.0, sch=KMN, kernel=kernel)
+        assert rel_err(C, ref, A, B) <= TOL
+
+
+def test_skinny_shapes_exercise_each_schedule_and_split_k(cake, oracle):
+    # 1/16-scale versions of the M-first, N-first and K-first benchmark shapes
+    for (M, K, N, want) in [(4096, 64, 64, MKN), (64, 64, 4096, NKM), (256, 16384, 320, KMN)]:
+        A, B = _inputs(oracle, M, K, N)
+        ref, _ = oracle.sgemm(A, B, 8, NA)
+        for kernel in (cake.KERNEL_FFMA, cake.KERNEL_TF32X3):
+            C = cake.cake_sgemm(A, B, kernel=kernel)
+            assert rel_err(C, ref, A, B) <= TOL, (M, K, N, kernel)
+        assert cake.last_stats()["sched"] == want
+
+
+def test_tf32x3_is_fp32_class_against_float64(cake, oracle):
+    M, K, N = 512, 4096, 512
+    A, B = _inputs(oracle, M, K, N)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64)
+    errs = {}
+    for name, kernel in (("ffma", cake.KERNEL_FFMA), ("tf32x3", cake.KERNEL_TF32X3)):
+        C = cake.cake_sgemm(A, B, kernel=kernel)
+        errs[name] = float((np.abs(C - ref64) / bound).max())
+    print("max |C - C64| / sum|a||b|:", errs)
+    assert errs["ffma"] < 2e-6 and errs["tf32x3"] < 2e-6
+
+
+def test_full_size_properties(cake, oracle):
+    """8192^3 (the headline configuration): the oracle would take minutes, so
+    check float64 recomputation of sampled entries, agreement of the two
+    kernels, and linearity C(A, B) + C(A, B') = C(A, B + B') on a slab."""
+    import torch
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(1)
+    A = torch.rand((n, n), device="cuda", generator=g) * 2 - 1
+    B = torch.rand((n, n), device="cuda", generator=g) * 2 - 1
+    C3 = torch.empty((n, n), device="cuda")
+    cake.cake_sgemm(A, B, C3, kernel=cake.KERNEL_TF32X3)
+    rng = np.random.default_rng(0)
+    rows, cols = rng.integers(0, n, 2048), rng.integers(0, n, 2048)
+    r_t, c_t = torch.from_numpy(rows).cuda(), torch.from_numpy(cols).cuda()
+    exact = (A[r_t].double() * B[:, c_t].t().double()).sum(1)
+    norm = A[r_t].double().norm(dim=1) * B[:, c_t].double().norm(dim=0)
+    err = ((C3[r_t, c_t].double() - exact).abs() / norm).max().item()
+    assert err <= TOL, err
+    Cf = torch.empty((1024, n), device="cuda")
+    cake.cake_sgemm(A[:1024].contiguous(), B, Cf, kernel=cake.KERNEL_FFMA)
+    na, nb = A[:1024].double().norm(dim=1), B.double().norm(dim=0)
+    diff = ((Cf - C3[:1024]).double().abs() / (na[:, None] * nb[None, :])).max().item()
+    assert diff <= TOL, diff
+    B2 = torch.rand((n, n), device="cuda", generator=g) * 2 - 1
+    As = A[:1024].contiguous()
+    C1, C2, C12 = (torch.empty((1024, n), device="cuda") for _ in range(3))
+    cake.cake_sgemm(As, B, C1, kernel=cake.KERNEL_TF32X3)
+    cake.cake_sgemm(As, B2, C2, kernel=cake.KERNEL_TF32X3)
+    cake.cake_sgemm(As, B + B2, C12, kernel=cake.KERNEL_TF32X3)
+    nb12 = (B.double().norm(dim=0) + B2.double().norm(dim=0))
+    lin = ((C1 + C2 - C12).double().abs() / (na[:, None] * nb12[None, :])).max().item()
+    assert lin <= TOL, lin
+
+
+def test_pack_unpack_bit_exact(cake, oracle):
+    for (M, K, N, p) in [(111, 96, 77, 4), (10, 960, 20, 5), (960, 10, 7, 8), (2111, 300, 500, 8), (96, 96, 96, 3)]:
+        A, B, C = oracle.uniform((M, K), 1), oracle.uniform((K, N), 2), oracle.uniform((M, N), 3)
+        for sch in (KMN, MKN, NKM, NA):
+            cx = cake.Cntx.make(*DEFAULT_CACHES)
+            x = cake.init_block_dims(M, N, K, p, cx, sch)
+            Ap = cake.pack_A(A, M, K, p, x, cx)
+            Bp = cake.pack_B(B, K, N, p, x, cx)
+            Cp = cake.pack_C(C, M, N, p, x, cx)
+            assert np.array_equal(Ap, oracle.pack(0, A, M, N, K, p, sch)), ("A", M, K, N, p, sch)
+            assert np.array_equal(Bp, oracle.pack(1, B, M, N, K, p, sch)), ("B", M, K, N, p, sch)
+            assert np.array_equal(Cp, oracle.pack(2, C, M, N, K, p, sch)), ("C", M, K, N, p, sch)
+            assert np.array_equal(cake.unpack_C(Cp, M, N, p, x, cx), C)
+            assert np.array_equal(cake.unpack_A(Ap, M, K, p, x, cx), A)
+            assert np.array_equal(cake.unpack_B(Bp, K, N, p, x, cx), B)
+            for which, got in ((0, Ap), (1, Bp), (2, Cp)):
+                key = "pack%s_%d_%d_%d_%d_%d" % ("ABC"[which], M, K, N, p, x.sch)
+                if sch != NA and key in GOLDEN.files:
+                    assert np.array_equal(got, GOLDEN[key]), key
+
+
+def test_pack_on_device_pointers(cake, oracle):
+    import torch
+    M, K, N, p = 500, 300, 700, 8
+    A = oracle.uniform((M, K), 1)
+    cx = cake.Cntx.make(*DEFAULT_CACHES)
+    x = cake.init_block_dims(M, N, K, p, cx, KMN)
+    Ap = cake.pack_A(torch.from_numpy(A).cuda(), M, K, p, x, cx)
+    assert Ap.is_cuda
+    assert np.array_equal(Ap.cpu().numpy(), oracle.pack(0, A, M, N, K, p, KMN))
+
+
+def test_sparse_product_bit_exact_and_against_dense_reference(cake, oracle):
+    for (M, K, N, d) in [(300, 257, 130, 0.5), (513, 1000, 260, 0.1), (1024, 2048, 515, 0.01), (7, 5, 3, 0.5)]:
+        A = oracle.sparse((M, K), 1, 3, d)
+        B = oracle.uniform((K, N), 2)
+        C = cake.cake_sp_sgemm(A, B)
+        assert np.array_equal(C, oracle.sp_sgemm(A, B)), (M, K, N, d)
+        dense_ref, _ = oracle.sgemm(A, B, 8, NA)  # the reference's dense path on the densified operand
+        assert rel_err(C, dense_ref, A, B) <= TOL
+        C3 = cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_TF32X3)
+        assert rel_err(C3, dense_ref, A, B) <= TOL
+
+
+def test_im2col_and_conv(cake, oracle):
+    for (b, cin, H, W, cout, hf, stride, pad) in [(2, 3, 7, 6, 5, 3, 1, 1), (3, 8, 14, 14, 16, 3, 1, 1),
+                                                 (1, 4, 9, 9, 6, 3, 2, 0), (2, 16, 12, 12, 32, 1, 1, 0)]:
+        x = oracle.normal((b, cin, H, W), 4, 0.1)
+        w = oracle.normal((cout, cin, hf, hf), 5, 0.1)
+        assert np.array_equal(cake.im2col(x, hf, hf, stride, pad), oracle.im2col(x, hf, hf, stride, pad))
+        out = cake.cake_conv2d(x, w, stride, pad)
+        ref = oracle.conv2d(x, w, stride, pad, 8)
+        col = oracle.im2col(x, hf, hf, stride, pad)
+        Ho, Wo = out.shape[2:]
+        got = out.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+        want = ref.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+        assert rel_err(got, want, w.reshape(cout, -1), col) <= TOL
+
+
+def test_batched_small(cake, oracle):
+    for (batch, M, K, N) in [(64, 96, 96, 96), (5, 33, 17, 70), (3, 130, 40, 129)]:
+        A, B = oracle.uniform((batch, M, K), 1), oracle.uniform((batch, K, N), 2)
+        C = cake.cake_sgemm_batched(A, B)
+        ref = oracle.sgemm_batched(A, B, 8)
+        for i in range(batch):
+            assert rel_err(C[i], ref[i], A[i], B[i]) <= TOL
+
+
+def test_errors_are_status_codes(cake):
+    A = np.zeros((4, 4), np.float32)
+    with pytest.raises(ValueError):
+        cake.cake_sgemm(A, np.zeros((5, 4), np.float32))
+    with pytest.raises(cake.CakeError):
+        cake.cake_sgemm(A, A, sch=9)
+    with pytest.raises(cake.CakeError):
+        cake.cake_sgemm(A, A, kernel=17)
+    with pytest.raises(cake.CakeError):
+        cake.cake_sgemm_async(0, 0, 0, 4, 4, 4)
+    # the library is still usable afterwards
+    C = cake.cake_sgemm(np.eye(4, dtype=np.float32), np.eye(4, dtype=np.float32))
+    assert np.array_equal(C, np.eye(4, dtype=np.float32))
