@@ -37,7 +37,7 @@ UNIT = "TFLOP/s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cake_b200", choices=["cake_b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = K = N (default: the headline 8192)")
