@@ -1,0 +1,71 @@
+"""``cake_linear`` on CUDA tensors.
+
+Mirrors the reference's PyTorch binding: the autograd function and module of
+python/cake.py:18-49 and the three products of src/linear.cpp (forward
+y = x W^T + b at :12-49; backward dX = dY W and dW = dY^T X at :52-102), each
+product being one cake_sgemm call.  Tensors stay on the GPU: the library is
+handed device pointers.
+"""
+import torch
+from torch import nn
+from torch.nn import Parameter
+
+from . import api
+
+
+def _sgemm(a, b):
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=torch.float32, device=a.device)
+    return api.cake_sgemm(a, b, out)
+
+
+def linear_forward(input, weight, bias=None):
+    """y = input @ weight.T (+ bias), as linear_forward in src/linear.cpp:12-49."""
+    x = input.reshape(-1, input.shape[-1])
+    out = _sgemm(x, weight.t())
+    if bias is not None:
+        out.add_(bias)
+    return out.reshape(*input.shape[:-1], weight.shape[0])
+
+
+def linear_backward(grad_output, input, weight, bias=None):
+    """(grad_input, grad_weight, grad_bias), as linear_backward in src/linear.cpp:52-102."""
+    dy = grad_output.reshape(-1, grad_output.shape[-1])
+    x = input.reshape(-1, input.shape[-1])
+    grad_input = _sgemm(dy, weight).reshape(input.shape)
+    grad_weight = _sgemm(dy.t(), x)
+    grad_bias = dy.sum(0) if bias is not None else None
+    return grad_input, grad_weight, grad_bias
+
+
+class cake_linear_function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, data, weight, bias=None):
+        output = linear_forward(data, weight, bias)
+        ctx.save_for_backward(data, weight, bias)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        data, weight, bias = ctx.saved_tensors
+        return linear_backward(grad_output, data, weight, bias)
+
+
+class cake_linear(nn.Module):
+    """Drop-in for the reference's ``cake_linear`` module (python/cake.py:33-49)."""
+
+    def __init__(self, input_features, output_features, bias=True):
+        super().__init__()
+        self.input_features = input_features
+        self.output_features = output_features
+        self.weight = Parameter(torch.empty(output_features, input_features))
+        if bias:
+            self.bias = Parameter(torch.empty(output_features))
+        else:
+            self.register_parameter("bias", None)
+        self.weight.data.uniform_(-0.1, 0.1)
+        if bias:
+            self.bias.data.uniform_(-0.1, 0.1)
+
+    def forward(self, data):
+        return cake_linear_function.apply(data, self.weight, self.bias)
