@@ -78,6 +78,8 @@ _SIGNATURES = {
 for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
     _SIGNATURES["cakeb200_" + _n] = (_i, [_vp, _vp, _i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _vp])
 
+_SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
+
 EXPORTED_SYMBOLS = sorted(_SIGNATURES)
 
 
@@ -316,3 +318,26 @@ def unpack_B(B_p, K, N, p, x, cake_cntx, B=None, stream=None):
         B = _empty_like_kind(B_p, (K, N))
     _pack("unpack_B", B, B_p, K, N, p, x, cake_cntx, stream)
     return B
+
+
+NOALLOC_SCRATCH_BYTES = 17 << 20
+
+
+def cake_sgemm_noalloc(A, B, C=None, stream=None):
+    """C = A @ B for callers that must not allocate device memory (embedded in
+    another framework's memory pool, fixed memory budget, plug-ins that are only
+    handed buffers).  CUDA tensors only; the scratch is a fixed 17 MiB array in
+    the library, so shapes are limited (1024 x 1024 x 1024 fits) and calls that
+    overlap on the GPU race on it.  The first call on a device should happen
+    outside any stream capture.  Pass ``C`` to keep the call itself free of
+    allocations on the Python side as well."""
+    if not (_is_torch(A) and A.is_cuda and _is_torch(B) and B.is_cuda):
+        raise TypeError("cake_sgemm_noalloc takes CUDA tensors")
+    M, K = A.shape
+    K2, N = B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if C is None:
+        C = _empty_like_kind(A, (M, N))
+    _check(lib().cakeb200_sgemm_noalloc(_ptr(A), _ptr(B), _ptr(C), M, N, K, _stream_of(C, stream)))
+    return C

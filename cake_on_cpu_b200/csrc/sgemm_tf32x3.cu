@@ -591,3 +591,129 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 }
 
 }  // namespace cakeb200
+
+// ------------------------------------------------- entry point that allocates nothing
+//
+// Some callers may not allocate device memory at the moment they need a product:
+// code that runs inside another framework's memory pool and must not disturb it, a
+// real-time loop whose memory budget was fixed at start-up, a library that is handed
+// a stream and buffers and told to stay off the allocator.  cakeb200_sgemm grows a
+// scratch arena with cudaMalloc on first use and again whenever a larger shape shows
+// up, so those callers cannot use it.  This variant runs the same 3xTF32 kernels with
+// the split operand planes in a fixed array that is part of the library image.
+//
+// The array costs CAKEB200_NOALLOC_SCRATCH_BYTES of device memory on every GPU that
+// loads the library, from load until the process exits.
+namespace {
+
+constexpr size_t NOALLOC_HEADER = 1024;  // status word, then padding up to the plane alignment
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CAKEB200_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device
+// address; the address is looked up once per device, with that device current.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mutex;
+
+int noalloc_scratch(unsigned char** out) {
+    int dev = -1;
+    CAKE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        cakeb200::set_error("device index %d out of range", dev);
+        return CAKEB200_ERR_NO_DEVICE;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_addr[dev]) {
+        void* p = nullptr;
+        CAKE_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_addr[dev] = (unsigned char*) p;
+    }
+    *out = g_noalloc_addr[dev];
+    return CAKEB200_OK;
+}
+
+bool noalloc_on_device(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+}  // namespace
+
+// bytes of the built-in array a shape uses: header + two planes of A + two planes of B
+static size_t noalloc_scratch_need(int M, int N, int K) {
+    const size_t Kp = (size_t) cakeb200::padded_k(K);
+    return NOALLOC_HEADER + 2 * cakeb200::align_up((size_t) M * Kp * 4, 1024) + 2 * cakeb200::align_up((size_t) N * Kp * 4, 1024);
+}
+
+extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+    using namespace cakeb200;
+    if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) {
+        set_error("cakeb200_sgemm_noalloc: null pointer or non-positive dimension");
+        return CAKEB200_ERR_ARG;
+    }
+    if (!noalloc_on_device(A) || !noalloc_on_device(B) || !noalloc_on_device(C)) {
+        set_error("cakeb200_sgemm_noalloc: A, B and C must be device pointers (staging a host operand would allocate)");
+        return CAKEB200_ERR_ARG;
+    }
+    const size_t need = noalloc_scratch_need(M, N, K);
+    if (need > (size_t) CAKEB200_NOALLOC_SCRATCH_BYTES) {
+        set_error("cakeb200_sgemm_noalloc: M=%d N=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu; "
+                  "use cakeb200_sgemm for this shape",
+                  M, N, K, need, (size_t) CAKEB200_NOALLOC_SCRATCH_BYTES);
+        return CAKEB200_ERR_TOO_LARGE;
+    }
+    unsigned char* base = nullptr;
+    int rc = noalloc_scratch(&base);
+    if (rc) return rc;
+    int dev = 0, sm_count = 0;
+    CAKE_CUDA_OK(cudaGetDevice(&dev));
+    CAKE_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    cudaStream_t s = (cudaStream_t) stream;
+
+    const int Kp = padded_k(K);
+    const size_t a_bytes = align_up((size_t) M * Kp * 4, 1024), b_bytes = align_up((size_t) N * Kp * 4, 1024);
+    int* status_word = (int*) base;
+    float* a_hi = (float*) (base + NOALLOC_HEADER);
+    float* a_lo = (float*) (base + NOALLOC_HEADER + a_bytes);
+    float* b_hi = (float*) (base + NOALLOC_HEADER + 2 * a_bytes);
+    float* b_lo = (float*) (base + NOALLOC_HEADER + 2 * a_bytes + b_bytes);
+
+    // The array keeps whatever the previous call left.  The status word must start
+    // at zero; the planes need no clearing because the split pass rewrites every
+    // element this shape will read, padding columns included.
+    CAKE_CUDA_OK(cudaMemsetAsync(status_word, 0, 256, s));
+    {
+        const long long total = (long long) M * Kp;
+        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
+        split_rows_kernel<<<blocks, 256, 0, s>>>(A, a_hi, a_lo, M, K, K, Kp);
+        dim3 grid((N + 31) / 32, (Kp + 31) / 32);
+        if (grid.y > 65535) {
+            set_error("cakeb200_sgemm_noalloc: K too large");
+            return CAKEB200_ERR_TOO_LARGE;
+        }
+        split_transpose_kernel<<<grid, 256, 0, s>>>(B, b_hi, b_lo, K, N, N, Kp);
+        CAKE_CUDA_OK(cudaGetLastError());
+    }
+    GemmProblem g = {};
+    g.A = A; g.B = B; g.C = C;
+    g.M = M; g.N = N; g.K = K;
+    g.lda = K; g.ldb = N; g.ldc = N;
+    g.batch = 1;
+    g.order = CAKEB200_SCHED_KMN;
+    // one K range per tile: split-K would need partial planes, i.e. more scratch
+    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, 1, status_word, sm_count, s)
+                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, 1, status_word, sm_count, s);
+    if (rc) return rc;
+    int word[4] = {0, 0, 0, 0};
+    CAKE_CUDA_OK(cudaMemcpyAsync(word, status_word, sizeof(word), cudaMemcpyDeviceToHost, s));
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    if (word[0] != 0) {
+        set_error("cakeb200_sgemm_noalloc: device-side wait gave up (where %d, block %d)", word[1], word[2]);
+        return CAKEB200_ERR_DEVICE_TIMEOUT;
+    }
+    return CAKEB200_OK;
+}

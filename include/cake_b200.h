@@ -162,6 +162,35 @@ int cakeb200_unpack_A(float* A, const float* A_p, int M, int K, int p, const cak
 int cakeb200_unpack_B(float* B, const float* B_p, int K, int N, int p, const cakeb200_blk_dims* x,
                       const cakeb200_cntx* cntx, void* stream);
 
+/* C = A*B for callers that must not allocate device memory.  This entry point has
+ * no counterpart in the reference; it exists for hosts of this library that are
+ * not allowed to touch the allocator when they need a product: code living inside
+ * another framework's memory pool, a loop whose memory was budgeted at start-up, a
+ * plug-in that is given a stream and buffers and nothing else.  cakeb200_sgemm
+ * cannot serve them because it grows its scratch arena with cudaMalloc the first
+ * time a larger shape arrives.
+ *
+ * Same kernels as cakeb200_sgemm with CAKEB200_KERNEL_TF32X3, but the split operand
+ * planes live in a fixed device array inside the library image.  The call makes no
+ * cudaMalloc, cudaFree or other allocating call.
+ *   - A, B, C must be DEVICE pointers (copying a host operand would need a buffer).
+ *   - Limit: 1024 + 2*roundup1024(4*M*ceil4(K)) + 2*roundup1024(4*N*ceil4(K)) bytes
+ *     must fit in CAKEB200_NOALLOC_SCRATCH_BYTES (17 MiB: 1024 x 1024 x 1024 fits;
+ *     so does 2048 x 512 x 1024).  Larger shapes return CAKEB200_ERR_TOO_LARGE and
+ *     compute nothing.
+ *   - The array occupies that much memory on every GPU that loads the library,
+ *     until the process exits.
+ *   - The first call on a device looks up the array's device address; make that
+ *     first call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls whose work overlaps on
+ *     the GPU (different streams, or different threads) race on it.  Issue them
+ *     one after the other.  Each call clears the state it needs at its start, so
+ *     what an earlier call left behind does not matter.
+ *   - `stream` is a cudaStream_t (NULL = the default stream).  The call returns
+ *     after the work has finished and the device-side status has been read. */
+#define CAKEB200_NOALLOC_SCRATCH_BYTES (17u << 20)
+int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, int M, int N, int K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
