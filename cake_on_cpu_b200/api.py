@@ -78,6 +78,8 @@ _SIGNATURES = {
 for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
     _SIGNATURES["cakeb200_" + _n] = (_i, [_vp, _vp, _i, _i, _i, ctypes.POINTER(BlkDims), ctypes.POINTER(Cntx), _vp])
 
+_SIGNATURES["cakeb200_profile_begin"] = (_i, [])
+_SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i)])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
 EXPORTED_SYMBOLS = sorted(_SIGNATURES)
@@ -341,3 +343,15 @@ def cake_sgemm_noalloc(A, B, C=None, stream=None):
         C = _empty_like_kind(A, (M, N))
     _check(lib().cakeb200_sgemm_noalloc(_ptr(A), _ptr(B), _ptr(C), M, N, K, _stream_of(C, stream)))
     return C
+
+
+def profile_begin():
+    """Start device-side timing of the asynchronous products that follow (see cakeb200_profile_begin)."""
+    _check(lib().cakeb200_profile_begin())
+
+
+def profile_end():
+    """(ms_prepass, ms_kernel, calls) summed over the products since profile_begin()."""
+    pre, ker, n = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+    _check(lib().cakeb200_profile_end(ctypes.byref(pre), ctypes.byref(ker), ctypes.byref(n)))
+    return pre.value, ker.value, n.value

@@ -4,7 +4,9 @@
 #include <algorithm>
 #include <climits>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
+#include <ctime>
 #include <mutex>
 
 #include "common.cuh"
@@ -15,7 +17,7 @@ int pack_A_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, co
 int pack_B_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
 int pack_C_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
 size_t sparse_scratch_bytes(int M, int K);
-int launch_sp_sgemm(const float*, const float*, float*, int, int, int, void*, cudaStream_t, int*);
+int launch_sp_sgemm(const float*, const float*, float*, int, int, int, void*, int*, cudaStream_t, int*);
 int launch_im2col(const float*, float*, int, int, int, int, int, int, int, int, cudaStream_t);
 
 namespace {
@@ -135,20 +137,30 @@ int check_status_word(DeviceState* st, cudaStream_t s) {
     return CAKEB200_OK;
 }
 
+// Queried once per device: the property calls cost milliseconds, far too much per product.
 void b200_cntx(DeviceState* st, cakeb200_cntx* c) {
-    cudaDeviceProp prop;
-    cudaGetDeviceProperties(&prop, st->device);
-    size_t free_b = 0, total_b = 0;
-    cudaMemGetInfo(&free_b, &total_b);
-    int ndev = 0;
-    cudaGetDeviceCount(&ndev);
-    c->alpha_n = 1.0;
-    c->mr = 128;
-    c->nr = 256;
-    c->L1 = (int) prop.sharedMemPerMultiprocessor;
-    c->L2 = prop.l2CacheSize;
-    c->L3 = (int) std::min<size_t>(total_b, (size_t) INT_MAX);
-    c->ncores = ndev;
+    static std::mutex m;
+    static cakeb200_cntx cached[MAX_DEVICES];
+    static bool have[MAX_DEVICES] = {};
+    std::lock_guard<std::mutex> lock(m);
+    if (!have[st->device]) {
+        cudaDeviceProp prop;
+        cudaGetDeviceProperties(&prop, st->device);
+        size_t free_b = 0, total_b = 0;
+        cudaMemGetInfo(&free_b, &total_b);
+        int ndev = 0;
+        cudaGetDeviceCount(&ndev);
+        cakeb200_cntx& k = cached[st->device];
+        k.alpha_n = 1.0;
+        k.mr = 128;
+        k.nr = 256;
+        k.L1 = (int) prop.sharedMemPerMultiprocessor;
+        k.L2 = prop.l2CacheSize;
+        k.L3 = (int) std::min<size_t>(total_b, (size_t) INT_MAX);
+        k.ncores = ndev;
+        have[st->device] = true;
+    }
+    *c = cached[st->device];
 }
 
 // Tile order for a shape when the caller leaves the schedule open: the same
@@ -205,6 +217,112 @@ float elapsed(cudaEvent_t a, cudaEvent_t b) {
     return ms;
 }
 
+int ensure_pipeline(DeviceState* st) {
+    if (st->copy_in) return CAKEB200_OK;
+    CAKE_CUDA_OK(cudaStreamCreateWithFlags(&st->copy_in, cudaStreamNonBlocking));
+    CAKE_CUDA_OK(cudaStreamCreateWithFlags(&st->copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < DeviceState::MAX_BANDS; i++) {
+        CAKE_CUDA_OK(cudaEventCreateWithFlags(&st->band_in[i], cudaEventDisableTiming));
+        CAKE_CUDA_OK(cudaEventCreateWithFlags(&st->band_done[i], cudaEventDisableTiming));
+    }
+    for (int i = 0; i < 3; i++) CAKE_CUDA_OK(cudaEventCreateWithFlags(&st->fence[i], cudaEventDisableTiming));
+    return CAKEB200_OK;
+}
+
+// Host operands, large M: the product is cut into bands of rows.  While band i is
+// multiplied, the rows of band i+1 are still arriving over PCIe and the result rows
+// of band i-1 are already leaving; only B has to be complete before the first band.
+// This is the GPU form of the reference's on-the-fly packing driver, which packs
+// block i+1 while block i is multiplied (src/cake_sgemm_k_first.cpp:633-813).
+int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float* C, GemmProblem g, int kernel,
+                         cudaStream_t s) {
+    const int M = g.M, N = g.N, K = g.K;
+    int rc;
+    static const bool debug_timing = getenv("CAKEB200_DEBUG_TIMING") != nullptr;
+    timespec h0, h1, h2;
+    clock_gettime(CLOCK_MONOTONIC, &h0);
+    if ((rc = ensure_pipeline(st))) return rc;
+    kernel = resolve_kernel(kernel, M, N, K, 1);
+    g_stats.kernel = kernel;
+    const bool b_host = !on_device(B);
+    if ((rc = grow(&st->staging[0], &st->staging_bytes[0], (size_t) M * K * 4))) return rc;
+    if (b_host && (rc = grow(&st->staging[1], &st->staging_bytes[1], (size_t) K * N * 4))) return rc;
+    if ((rc = grow(&st->staging[2], &st->staging_bytes[2], (size_t) M * N * 4))) return rc;
+    float* dA = (float*) st->staging[0];
+    const float* dB = b_host ? (const float*) st->staging[1] : B;
+    float* dC = (float*) st->staging[2];
+    Tf32x3Planes planes = {};
+    if (kernel == CAKEB200_KERNEL_TF32X3) {
+        if ((rc = ensure_scratch(st, tf32x3_plane_bytes(M, N, K)))) return rc;
+        if ((rc = tf32x3_planes(M, N, K, st->scratch, st->scratch_bytes, &planes))) return rc;
+    }
+
+    // bands of whole 128-row tiles; enough of them that the first and last are short
+    const int tiles = (M + 127) / 128;
+    const int bands = std::max(1, std::min(std::min(DeviceState::MAX_BANDS, 16), tiles / 2));
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    CAKE_CUDA_OK(cudaEventRecord(st->fence[0], s));
+    CAKE_CUDA_OK(cudaStreamWaitEvent(st->copy_in, st->fence[0], 0));
+    CAKE_CUDA_OK(cudaStreamWaitEvent(st->copy_out, st->fence[0], 0));
+    if (b_host) {
+        CAKE_CUDA_OK(cudaMemcpyAsync(st->staging[1], B, (size_t) K * N * 4, cudaMemcpyHostToDevice, st->copy_in));
+        CAKE_CUDA_OK(cudaEventRecord(st->fence[1], st->copy_in));
+        CAKE_CUDA_OK(cudaStreamWaitEvent(s, st->fence[1], 0));
+    }
+    if (kernel == CAKEB200_KERNEL_TF32X3) {
+        if ((rc = tf32x3_split_B(dB, N, K, N, planes, s))) return rc;
+        g_stats.launches++;
+        g_stats.tile_m = 128; g_stats.tile_n = N > 128 ? 256 : 128; g_stats.tile_k = 32;
+    }
+    for (int b = 0; b < bands; b++) {
+        const int r0 = (int) ((long long) tiles * b / bands) * 128;
+        const int r1 = (b == bands - 1) ? M : (int) ((long long) tiles * (b + 1) / bands) * 128;
+        const int rows = r1 - r0;
+        if (rows <= 0) continue;
+        CAKE_CUDA_OK(cudaMemcpyAsync(dA + (size_t) r0 * K, A + (size_t) r0 * K, (size_t) rows * K * 4,
+                                     cudaMemcpyHostToDevice, st->copy_in));
+        if (g.accumulate)
+            CAKE_CUDA_OK(cudaMemcpyAsync(dC + (size_t) r0 * N, C + (size_t) r0 * N, (size_t) rows * N * 4,
+                                         cudaMemcpyHostToDevice, st->copy_in));
+        CAKE_CUDA_OK(cudaEventRecord(st->band_in[b], st->copy_in));
+        if (b == bands - 1) CAKE_CUDA_OK(cudaEventRecord(st->ev[1], st->copy_in));
+        CAKE_CUDA_OK(cudaStreamWaitEvent(s, st->band_in[b], 0));
+        if (kernel == CAKEB200_KERNEL_TF32X3) {
+            if ((rc = tf32x3_split_A_rows(dA, K, r0, rows, K, planes, st->sm_count, s))) return rc;
+            if ((rc = tf32x3_multiply_rows(planes, dC, N, r0, rows, N, K, g.order, g.accumulate, st->status_word,
+                                           st->sm_count, s)))
+                return rc;
+            g_stats.launches += 2;
+        } else {
+            GemmProblem band = g;
+            band.A = dA + (size_t) r0 * K; band.B = dB; band.C = dC + (size_t) r0 * N;
+            band.M = rows;
+            if ((rc = launch_sgemm_ffma(band, s))) return rc;
+            g_stats.launches += 1;
+        }
+        CAKE_CUDA_OK(cudaEventRecord(st->band_done[b], s));
+        if (b == bands - 1) CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+        CAKE_CUDA_OK(cudaStreamWaitEvent(st->copy_out, st->band_done[b], 0));
+        CAKE_CUDA_OK(cudaMemcpyAsync(C + (size_t) r0 * N, dC + (size_t) r0 * N, (size_t) rows * N * 4,
+                                     cudaMemcpyDeviceToHost, st->copy_out));
+    }
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], st->copy_out));
+    CAKE_CUDA_OK(cudaEventRecord(st->fence[2], st->copy_out));
+    CAKE_CUDA_OK(cudaStreamWaitEvent(s, st->fence[2], 0));
+    clock_gettime(CLOCK_MONOTONIC, &h1);
+    if ((rc = check_status_word(st, s))) return rc;
+    clock_gettime(CLOCK_MONOTONIC, &h2);
+    if (debug_timing)
+        fprintf(stderr, "cakeb200 pipelined: %d bands, host enqueue %.3f ms, wait %.3f ms\n", bands,
+                (h1.tv_sec - h0.tv_sec) * 1e3 + (h1.tv_nsec - h0.tv_nsec) * 1e-6,
+                (h2.tv_sec - h1.tv_sec) * 1e3 + (h2.tv_nsec - h1.tv_nsec) * 1e-6);
+    // the phases overlap; report the spans that do not: start -> last row arrived -> last band multiplied -> last row back
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
 int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
                int kernel, void* stream, bool blocking) {
     g_stats = cakeb200_stats();
@@ -219,7 +337,7 @@ int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, in
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
 
     GemmProblem g = {};
     g.M = M; g.N = N; g.K = K;
@@ -235,8 +353,29 @@ int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, in
             return CAKEB200_ERR_ARG;
         }
         g.A = A; g.B = B; g.C = C;
+        if (st->profiling && st->profile_count < DeviceState::MAX_PROFILE) {
+            cudaEvent_t* e = &st->profile_ev[3 * st->profile_count];
+            const bool tensor = resolve_kernel(kernel, M, N, K, 1) == CAKEB200_KERNEL_TF32X3;
+            int rc = CAKEB200_OK;
+            if (tensor) {
+                const size_t need = tf32x3_scratch_bytes(M, N, K, st->sm_count);
+                if ((rc = ensure_scratch(st, need))) return rc;
+                g_stats.kernel = CAKEB200_KERNEL_TF32X3;
+                rc = launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats, e);
+            } else {
+                CAKE_CUDA_OK(cudaEventRecord(e[0], s));
+                CAKE_CUDA_OK(cudaEventRecord(e[1], s));
+                rc = run_dense(st, g, kernel, s, false);
+            }
+            if (rc) return rc;
+            CAKE_CUDA_OK(cudaEventRecord(e[2], s));
+            st->profile_count++;
+            return CAKEB200_OK;
+        }
         return run_dense(st, g, kernel, s, false);
     }
+
+    if (!on_device(A) && !on_device(C) && M >= 1024) return sgemm_host_pipelined(st, A, B, C, g, kernel, s);
 
     Operand oa, ob, oc;
     int rc;
@@ -271,7 +410,7 @@ int pack_impl(pack_fn fn, const float* mat, size_t mat_bytes, float* packed, siz
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     Operand om, op;
     int rc;
     // unpack leaves matrix cells outside the packed image untouched, so the matrix is always copied in
@@ -318,6 +457,34 @@ int cakeb200_query_cntx(cakeb200_cntx* out) {
     return CAKEB200_OK;
 }
 
+int cakeb200_profile_begin(void) {
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    for (int i = 0; i < 3 * DeviceState::MAX_PROFILE; i++)
+        if (!st->profile_ev[i]) CAKE_CUDA_OK(cudaEventCreate(&st->profile_ev[i]));
+    st->profile_count = 0;
+    st->profiling = true;
+    return CAKEB200_OK;
+}
+
+int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls) {
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    st->profiling = false;
+    double pre = 0, ker = 0;
+    for (int i = 0; i < st->profile_count; i++) {
+        cudaEvent_t* e = &st->profile_ev[3 * i];
+        CAKE_CUDA_OK(cudaEventSynchronize(e[2]));
+        pre += elapsed(e[0], e[1]);
+        ker += elapsed(e[1], e[2]);
+    }
+    if (ms_prepass) *ms_prepass = (float) pre;
+    if (ms_kernel) *ms_kernel = (float) ker;
+    if (calls) *calls = st->profile_count;
+    st->profile_count = 0;
+    return CAKEB200_OK;
+}
+
 int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
                    int kernel, void* stream) {
     return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, true);
@@ -342,7 +509,7 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     Operand oa, ob, oc;
     int rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
@@ -385,7 +552,7 @@ int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, in
     if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     Operand oa, ob, oc;
     int rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
@@ -402,8 +569,8 @@ int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, in
         if ((rc = run_dense(st, g, CAKEB200_KERNEL_TF32X3, s, false))) return rc;
     } else {
         if ((rc = ensure_scratch(st, sparse_scratch_bytes(M, K)))) return rc;
-        if ((rc = launch_sp_sgemm((const float*) oa.dev, (const float*) ob.dev, (float*) oc.dev, M, N, K, st->scratch, s,
-                                  &g_stats.launches)))
+        if ((rc = launch_sp_sgemm((const float*) oa.dev, (const float*) ob.dev, (float*) oc.dev, M, N, K, st->scratch,
+                                  st->status_word, s, &g_stats.launches)))
             return rc;
         g_stats.kernel = CAKEB200_KERNEL_FFMA;
     }
@@ -427,7 +594,7 @@ int cakeb200_im2col(const float* in, float* col, int batch, int cin, int H, int 
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
     Operand oi, oc;
     int rc;
@@ -450,7 +617,7 @@ int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    cudaStream_t s = stream ? (cudaStream_t) stream : st->stream;
+    cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
     const int Kg = cin * hf * wf;
     const long long plane = (long long) Ho * Wo, Ng = plane * batch;

@@ -47,6 +47,15 @@ struct DeviceState {
     int* status_word = nullptr;  // device-side error flag written by bounded waits
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // 4,5 bracket the operand-split pass
+    // host-operand pipeline: copies in and out run on their own streams, ordered by per-band events
+    static constexpr int MAX_BANDS = 32;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t band_in[MAX_BANDS] = {}, band_done[MAX_BANDS] = {}, fence[3] = {};
+    // optional device-side timing of the asynchronous entry point (cakeb200_profile_begin / _end)
+    static constexpr int MAX_PROFILE = 256;
+    bool profiling = false;
+    int profile_count = 0;
+    cudaEvent_t profile_ev[3 * MAX_PROFILE] = {};
 };
 DeviceState* device_state();  // state of the current device (created on first use)
 int ensure_scratch(DeviceState* st, size_t bytes);
@@ -55,6 +64,18 @@ int ensure_scratch(DeviceState* st, size_t bytes);
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);
 // 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
+// row-band interface of the 3xTF32 path (operand planes laid out once, rows multiplied band by band)
+struct Tf32x3Planes {
+    float *a_hi, *a_lo, *b_hi, *b_lo;
+    int Kp;
+};
+size_t tf32x3_plane_bytes(int M, int N, int K);
+int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out);
+int tf32x3_split_B(const float* B, int ldb, int K, int N, const Tf32x3Planes& p, cudaStream_t stream);
+int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const Tf32x3Planes& p, int sm_count,
+                        cudaStream_t stream);
+int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int rows, int N, int K, int order,
+                         int accumulate, int* status_word, int sm_count, cudaStream_t stream);
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
                         int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
 

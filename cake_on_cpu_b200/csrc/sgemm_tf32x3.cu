@@ -389,6 +389,23 @@ split_rows_kernel(const float* __restrict__ A, float* __restrict__ hi, float* __
     }
 }
 
+// Same split, four elements per thread: needs K % 4 == 0 (then Kp == K), lda % 4 == 0 and a 16-byte aligned A.
+__global__ void __launch_bounds__(256)
+split_rows_vec4_kernel(const float4* __restrict__ A, float4* __restrict__ hi, float4* __restrict__ lo, int M, int K4, int lda4) {
+    const long long total = (long long) M * K4;
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long) gridDim.x * blockDim.x) {
+        const int m = (int) (i / K4), k = (int) (i - (long long) m * K4);
+        const float4 v = __ldg(A + (long long) m * lda4 + k);
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
 // B (K x N, leading dimension ldb) -> transposed hi / lo planes (N x Kp): 32 x 32 tiles through shared memory
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ B, float* __restrict__ hi, float* __restrict__ lo, int K, int N, int ldb, int Kp) {
@@ -522,7 +539,85 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     return CAKEB200_OK;
 }
 
+// rows [0, M) of A (leading dimension lda) -> hi / lo planes
+int run_split_rows(const float* A, float* hi, float* lo, int M, int K, int lda, int Kp, int sm_count, cudaStream_t stream) {
+    if (M <= 0) return CAKEB200_OK;
+    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (((uintptr_t) A | (uintptr_t) hi | (uintptr_t) lo) % 16 == 0);
+    if (vec) {
+        const long long total = (long long) M * (K / 4);
+        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
+        split_rows_vec4_kernel<<<blocks, 256, 0, stream>>>((const float4*) A, (float4*) hi, (float4*) lo, M, K / 4, lda / 4);
+    } else {
+        const long long total = (long long) M * Kp;
+        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
+        split_rows_kernel<<<blocks, 256, 0, stream>>>(A, hi, lo, M, K, lda, Kp);
+    }
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
+
+int run_split_transpose(const float* B, float* hi, float* lo, int K, int N, int ldb, int Kp, cudaStream_t stream) {
+    dim3 grid((N + 31) / 32, (Kp + 31) / 32);
+    if (grid.y > 65535) {
+        set_error("sgemm_tf32x3: K too large for the transpose grid");
+        return CAKEB200_ERR_TOO_LARGE;
+    }
+    split_transpose_kernel<<<grid, 256, 0, stream>>>(B, hi, lo, K, N, ldb, Kp);
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
+
 }  // namespace
+
+// ---- row-band interface: lets the host-pointer driver overlap copies with compute.
+// Planes for the whole product are laid out once; B is split once; then each band of
+// rows is split and multiplied as soon as its rows have arrived.
+
+size_t tf32x3_plane_bytes(int M, int N, int K) {
+    const size_t Kp = (size_t) padded_k(K);
+    return 2 * align_up((size_t) M * Kp * 4, 1024) + 2 * align_up((size_t) N * Kp * 4, 1024) + 2048;
+}
+
+int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out) {
+    if (tf32x3_plane_bytes(M, N, K) > scratch_bytes) {
+        set_error("sgemm_tf32x3: scratch too small for the operand planes");
+        return CAKEB200_ERR_ARG;
+    }
+    const int Kp = padded_k(K);
+    const size_t a_bytes = align_up((size_t) M * Kp * 4, 1024), b_bytes = align_up((size_t) N * Kp * 4, 1024);
+    char* base = (char*) align_up((size_t) scratch, 1024);
+    out->a_hi = (float*) base;
+    out->a_lo = (float*) (base + a_bytes);
+    out->b_hi = (float*) (base + 2 * a_bytes);
+    out->b_lo = (float*) (base + 2 * a_bytes + b_bytes);
+    out->Kp = Kp;
+    return CAKEB200_OK;
+}
+
+int tf32x3_split_B(const float* B, int ldb, int K, int N, const Tf32x3Planes& p, cudaStream_t stream) {
+    return run_split_transpose(B, p.b_hi, p.b_lo, K, N, ldb, p.Kp, stream);
+}
+
+int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const Tf32x3Planes& p, int sm_count,
+                        cudaStream_t stream) {
+    return run_split_rows(A + (size_t) r0 * lda, p.a_hi + (size_t) r0 * p.Kp, p.a_lo + (size_t) r0 * p.Kp, rows, K, lda,
+                          p.Kp, sm_count, stream);
+}
+
+int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int rows, int N, int K, int order,
+                         int accumulate, int* status_word, int sm_count, cudaStream_t stream) {
+    GemmProblem g = {};
+    g.C = C + (size_t) r0 * ldc;
+    g.M = rows; g.N = N; g.K = K;
+    g.ldc = ldc;
+    g.batch = 1;
+    g.order = order;
+    g.accumulate = accumulate;
+    float* a_hi = p.a_hi + (size_t) r0 * p.Kp;
+    float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
+    return (N > 128) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, nullptr, 1, status_word, sm_count, stream)
+                     : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, nullptr, 1, status_word, sm_count, stream);
+}
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + split-K partials (worst case)
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
@@ -558,21 +653,12 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     }
 
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[0], stream));
-    {
-        const long long total = (long long) g.M * Kp;
-        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
-        split_rows_kernel<<<blocks, 256, 0, stream>>>(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp);
-        dim3 grid((g.N + 31) / 32, (Kp + 31) / 32);
-        if (grid.y > 65535) {
-            set_error("sgemm_tf32x3: K too large for the transpose grid");
-            return CAKEB200_ERR_TOO_LARGE;
-        }
-        split_transpose_kernel<<<grid, 256, 0, stream>>>(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp);
-        CAKE_CUDA_OK(cudaGetLastError());
-    }
+    int rc;
+    if ((rc = run_split_rows(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp, sm_count, stream))) return rc;
+    if ((rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream))) return rc;
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
-    int rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream)
+    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream)
                          : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream);
     if (rc) return rc;
     int launches = 3;

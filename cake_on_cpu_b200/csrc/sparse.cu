@@ -9,6 +9,8 @@
 // columns of C streams BK-deep slabs of B through shared memory and lets every
 // warp replay its rows' nonzeros against the slab.  Per C element the FMAs run
 // over k ascending, so the result equals the row-skipping CPU order bit for bit.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cakeb200 {
@@ -52,19 +54,24 @@ __global__ void __launch_bounds__(1024) row_ptr_kernel(const int* __restrict__ c
 // warp-level compaction: ballot -> bitmap of survivors, popcount of the lower lanes -> slot
 __global__ void __launch_bounds__(256)
 compact_rows_kernel(const float* __restrict__ A, int M, int K, const long long* __restrict__ ptr,
-                    int* __restrict__ cols, float* __restrict__ vals) {
+                    int* __restrict__ cols, float* __restrict__ vals, int* status) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= M) return;
     const float* row = A + (long long) warp * K;
     long long base = ptr[warp];
+    const long long limit = ptr[warp + 1];
     for (int k0 = 0; k0 < K; k0 += 32) {
         const int k = k0 + lane;
         const float v = (k < K) ? __ldg(row + k) : 0.0f;
         const unsigned bitmap = __ballot_sync(0xffffffffu, v != 0.0f);
         if (v != 0.0f) {
             const long long slot = base + __popc(bitmap & ((1u << lane) - 1u));
-            cols[slot] = k;
-            vals[slot] = v;
+            if (slot >= limit || slot < 0) {  // the row holds more nonzeros than were counted: record, do not write
+                if (atomicCAS(status, 0, 2) == 0) { status[1] = 11; status[2] = warp; }
+            } else {
+                cols[slot] = k;
+                vals[slot] = v;
+            }
         }
         base += __popc(bitmap);
     }
@@ -75,7 +82,7 @@ constexpr int SP_BM = 64, SP_BN = 128, SP_BK = 64, SP_WARPS = 8, SP_ROWS = SP_BM
 template <bool VEC>
 __global__ void __launch_bounds__(SP_WARPS * 32)
 spmm_rows_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols, const float* __restrict__ vals,
-                 const float* __restrict__ B, float* __restrict__ C, int M, int N, int K) {
+                 const float* __restrict__ B, float* __restrict__ C, int M, int N, int K, int* status) {
     __shared__ __align__(16) float Bs[SP_BK][SP_BN];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * SP_BM + warp * SP_ROWS, n0 = blockIdx.x * SP_BN;
@@ -87,6 +94,10 @@ spmm_rows_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols
         const int m = m0 + r;
         cur[r] = (m < M) ? ptr[m] : 0;
         end[r] = (m < M) ? ptr[m + 1] : 0;
+        if (cur[r] < 0 || end[r] < cur[r] || end[r] > (long long) M * K) {  // corrupt row list: record, skip the row
+            if (lane == 0 && atomicCAS(status, 0, 2) == 0) { status[1] = 13; status[2] = m; }
+            cur[r] = end[r] = 0;
+        }
         acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
     }
 
@@ -117,6 +128,11 @@ spmm_rows_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols
             while (c < e) {
                 const int k = __ldg(cols + c);  // same address in every lane: one broadcast load
                 if (k >= k_hi) break;
+                if (k < k0) {  // list not ascending: record and drop the rest of the row
+                    if (lane == 0 && atomicCAS(status, 0, 2) == 0) { status[1] = 12; status[2] = m0 + r; }
+                    c = e;
+                    break;
+                }
                 const float a = __ldg(vals + c);
                 const float4 b = *reinterpret_cast<const float4*>(&Bs[k - k0][lane * 4]);
                 acc[r][0] = fmaf(a, b.x, acc[r][0]);
@@ -157,7 +173,20 @@ size_t sparse_scratch_bytes(int M, int K) {
 }
 
 int launch_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K, void* scratch,
-                    cudaStream_t stream, int* launches) {
+                    int* status_word, cudaStream_t stream, int* launches) {
+    // CAKEB200_DEBUG_SYNC=1: wait after every kernel and name the one that failed
+    static const bool debug_sync = getenv("CAKEB200_DEBUG_SYNC") != nullptr;
+    auto after = [&](const char* what) -> int {
+        if (!debug_sync) return CAKEB200_OK;
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            set_error("sparse: %s failed: %s", what, cudaGetErrorString(e));
+            return CAKEB200_ERR_CUDA;
+        }
+        return CAKEB200_OK;
+    };
+    int rc;
     char* base = (char*) scratch;
     int* cnt = (int*) base;
     base += align_up((size_t) M * 4, 256);
@@ -169,15 +198,19 @@ int launch_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int 
 
     const int row_blocks = (M + 7) / 8;  // 8 warps (rows) per 256-thread CTA
     row_nnz_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, cnt);
+    if ((rc = after("row_nnz_kernel"))) return rc;
     row_ptr_kernel<<<1, 1024, 0, stream>>>(cnt, M, ptr);
-    compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, ptr, cols, vals);
+    if ((rc = after("row_ptr_kernel"))) return rc;
+    compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, ptr, cols, vals, status_word);
+    if ((rc = after("compact_rows_kernel"))) return rc;
     dim3 grid((N + SP_BN - 1) / SP_BN, (M + SP_BM - 1) / SP_BM);
     const bool vec = (N % 4 == 0) && (((uintptr_t) B | (uintptr_t) C) % 16 == 0);
     if (vec)
-        spmm_rows_kernel<true><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K);
+        spmm_rows_kernel<true><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K, status_word);
     else
-        spmm_rows_kernel<false><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K);
+        spmm_rows_kernel<false><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K, status_word);
     CAKE_CUDA_OK(cudaGetLastError());
+    if ((rc = after("spmm_rows_kernel"))) return rc;
     if (launches) *launches += 4;
     return CAKEB200_OK;
 }

@@ -92,8 +92,11 @@ int cakeb200_query_cntx(cakeb200_cntx* out);
  * include/cake.h:12-14).  `sched` orders the output tiles (KMN: K innermost
  * per tile with a snake over tiles; MKN: M-fastest; NKM: N-fastest; NA: derive
  * from the shape as derive_schedule does, reference src/block_sizing.cpp:434-462).
- * `stream` is a cudaStream_t (NULL = the library's own stream); the call
- * returns after the work on that stream has finished. */
+ * `stream` is a cudaStream_t (NULL = the CUDA default stream, as in the CUDA
+ * runtime); work is ordered after what the caller queued on that stream before
+ * the call, and the call returns after its own work has finished.  Host
+ * operands with many rows are streamed in bands of rows: band i is multiplied
+ * while band i+1 is still being copied in and band i-1 is being copied out. */
 int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K,
                    int accumulate, int sched, int kernel, void* stream);
 
@@ -101,6 +104,15 @@ int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K
  * no synchronisation).  For callers that time or overlap the work themselves. */
 int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K,
                          int accumulate, int sched, int kernel, void* stream);
+
+/* Device-side timing of cakeb200_sgemm_async without synchronising: between
+ * _begin and _end every asynchronous product (up to 256) records CUDA events on
+ * its stream before the operand-split pass, after it and after the contraction
+ * kernel(s); _end waits for the last one and returns the summed durations in
+ * milliseconds.  Replaces the reference's DEBUG timing printouts around pack /
+ * GEMM / unpack (reference src/cake_sgemm.cpp:32-168). */
+int cakeb200_profile_begin(void);
+int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls);
 
 /* `batch` independent products of identical shape, item i at A + i*M*K etc.
  * Replaces the small-matrix entry points cake_gemm_small / schedule_*_small

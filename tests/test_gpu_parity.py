@@ -86,6 +86,44 @@ def test_beta_flag_matches_reference_semantics(cake, oracle):
         assert rel_err(C, ref, A, B) <= TOL
 
 
+def test_host_operands_banded_copy_compute_overlap(cake, oracle):
+    """Host arrays with many rows take the banded path (copies overlapped with compute);
+    it must give what the single-shot path gives for device operands."""
+    import torch
+    for (M, K, N) in [(2600, 300, 520), (1024, 64, 1000), (4099, 129, 257)]:
+        A, B = _inputs(oracle, M, K, N)
+        C0 = oracle.uniform((M, N), 3)
+        ref, _ = oracle.sgemm(A, B, 8, NA)
+        for kernel in (cake.KERNEL_FFMA, cake.KERNEL_TF32X3):
+            C = cake.cake_sgemm(A, B, kernel=kernel)
+            assert rel_err(C, ref, A, B) <= TOL, (M, K, N, kernel)
+            dC = cake.cake_sgemm(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), kernel=kernel)
+            assert np.array_equal(C, dC.cpu().numpy()), (M, K, N, kernel)
+            # host A and C, device B
+            C2 = np.full((M, N), np.nan, np.float32)
+            cake.cake_sgemm(A, torch.from_numpy(B).cuda(), C2, kernel=kernel)
+            assert np.array_equal(C, C2), (M, K, N, kernel)
+        refb, _ = oracle.sgemm(A, B, 8, MKN, beta=1.0, C=C0)
+        Cb = C0.copy()
+        cake.cake_sgemm(A, B, Cb, beta=1.0, sch=MKN, kernel=cake.KERNEL_TF32X3)
+        assert rel_err(Cb, refb, A, B) <= TOL
+
+
+def test_profile_events_of_async_products(cake):
+    import torch
+    n = 1024
+    A, B, C = (torch.rand((n, n), device="cuda") for _ in range(3))
+    s = torch.cuda.current_stream().cuda_stream
+    cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+    cake.profile_begin()
+    for _ in range(4):
+        cake.cake_sgemm_async(A.data_ptr(), B.data_ptr(), C.data_ptr(), n, n, n, 0, cake.NA, cake.KERNEL_TF32X3, s)
+    pre, ker, calls = cake.profile_end()
+    assert calls == 4 and pre > 0 and ker > 0
+    ref = A.double() @ B.double()
+    assert (C.double() - ref).abs().max().item() < 1e-2
+
+
 def test_skinny_shapes_exercise_each_schedule_and_split_k(cake, oracle):
     # 1/16-scale versions of the M-first, N-first and K-first benchmark shapes
     for (M, K, N, want) in [(4096, 64, 64, MKN), (64, 64, 4096, NKM), (256, 16384, 320, KMN)]:
