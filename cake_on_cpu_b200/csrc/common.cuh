@@ -34,6 +34,10 @@ struct GemmProblem {
     int batch;
     int accumulate;  // 0: C = A*B, 1: C += A*B (the reference's beta != 0 behaviour)
     int order;       // tile rasterisation: CAKEB200_SCHED_*
+    // 3xTF32 path only: when out_p > 0 the N axis is (image, position) with out_p positions per image and
+    // element (m, n) is stored at C[(n / out_p) * out_image_stride + m * out_p + n % out_p] (NCHW convolution output)
+    int out_p;
+    long long out_image_stride;
 };
 
 // Per-device state: scratch arena that grows on demand and is reused between calls.
@@ -74,8 +78,11 @@ int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32
 int tf32x3_split_B(const float* B, int ldb, int K, int N, const Tf32x3Planes& p, cudaStream_t stream);
 int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const Tf32x3Planes& p, int sm_count,
                         cudaStream_t stream);
+int tf32x3_split_im2col(const float* in, int batch, int cin, int H, int W, int hf, int wf, int stride, int pad,
+                        const Tf32x3Planes& p, int sm_count, cudaStream_t stream);
 int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int rows, int N, int K, int order,
-                         int accumulate, int* status_word, int sm_count, cudaStream_t stream);
+                         int accumulate, int* status_word, int sm_count, cudaStream_t stream, int out_p = 0,
+                         long long out_image_stride = 0);
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
                         int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
 

@@ -202,8 +202,21 @@ int launch_cfg(const GemmProblem& g, cudaStream_t stream) {
 // src/block_sizing.cpp:304-429): big tiles when the grid still fills the SMs.
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream) {
     if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return CAKEB200_OK;
-    const long long big_tiles = (long long) ((g.M + 127) / 128) * ((g.N + 127) / 128) * g.batch;
-    if (big_tiles >= 120 && g.M > 64 && g.N > 64) return launch_cfg<128, 128, 16, 8, 8>(g, stream);
+    // padded work of each tile size, weighted by how efficient that tile's inner loop is;
+    // a large tile is penalised when it leaves most SMs without a CTA
+    const int sizes[3] = {128, 96, 64};
+    const double weight[3] = {1.0, 1.1, 1.35};
+    int best = 2;
+    double best_cost = 0;
+    for (int i = 0; i < 3; i++) {
+        const int t = sizes[i];
+        const double tiles = (double) ((g.M + t - 1) / t) * ((g.N + t - 1) / t) * g.batch;
+        double cost = tiles * t * t * weight[i];
+        if (tiles < 120) cost *= 120.0 / tiles;
+        if (i == 0 || cost < best_cost) { best = i; best_cost = cost; }
+    }
+    if (best == 0) return launch_cfg<128, 128, 16, 8, 8>(g, stream);
+    if (best == 1) return launch_cfg<96, 96, 16, 8, 8>(g, stream);
     return launch_cfg<64, 64, 16, 4, 4>(g, stream);
 }
 

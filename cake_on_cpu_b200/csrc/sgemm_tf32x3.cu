@@ -172,6 +172,8 @@ struct Tf32x3Args {
     int kblocks;         // ceil(K / BK)
     int order;
     int accumulate;      // only honoured when splits == 1
+    int out_p;           // > 0: N axis is (image, position), see GemmProblem::out_p
+    long long out_image_stride;
     int* status_word;
 };
 
@@ -333,7 +335,28 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                     for (int j = 0; j < 32; j++) v[j] = 0.0f;
                 }
                 const int col0 = tn * BN + c * 32;
-                if (row < args.M && col0 < args.N) {
+                if (args.out_p > 0) {
+                    // convolution output: columns are (image, position); rows are output channels
+                    if (row < args.M && col0 < args.N) {
+                        const int img = col0 / args.out_p, pos = col0 - img * args.out_p;
+                        float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
+                        if (pos + 32 <= args.out_p && col0 + 32 <= args.N && (args.out_p % 4 == 0) &&
+                            (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int col = col0 + j;
+                                if (col < args.N) {
+                                    const int im = col / args.out_p, ps = col - im * args.out_p;
+                                    args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = v[j];
+                                }
+                            }
+                        }
+                    }
+                } else if (row < args.M && col0 < args.N) {
                     if (vec_ok && col0 + 32 <= args.N) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
@@ -430,6 +453,64 @@ split_transpose_kernel(const float* __restrict__ B, float* __restrict__ hi, floa
     }
 }
 
+// im2col fused with the operand split: the K x N matrix of the convolution-as-GEMM
+// route (reference examples/cake_conv.cpp:1178-1213; row k = (cin, hf, wf), column
+// n = (image, ho, wo), zero padding) is never materialised; its transposed hi / lo
+// planes (N x Kp, k fastest) are written straight from the NCHW input.
+__global__ void __launch_bounds__(256)
+im2col_split_kernel(const float* __restrict__ in, float* __restrict__ hi, float* __restrict__ lo, int batch, int cin,
+                    int H, int W, int hf, int wf, int stride, int pad, int Ho, int Wo, int Kg, int Kp) {
+    const long long total = (long long) batch * Ho * Wo * Kp;
+    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long) gridDim.x * blockDim.x) {
+        const long long n = i / Kp;
+        const int k = (int) (i - n * Kp);
+        float h = 0.f, l = 0.f;
+        if (k < Kg) {
+            const int fw = k % wf, fh = (k / wf) % hf, ci = k / (wf * hf);
+            const int wo = (int) (n % Wo), ho = (int) ((n / Wo) % Ho), b = (int) (n / ((long long) Wo * Ho));
+            const int y = ho * stride - pad + fh, x = wo * stride - pad + fw;
+            if (y >= 0 && y < H && x >= 0 && x < W)
+                split_tf32(__ldg(in + (((long long) b * cin + ci) * H + y) * W + x), h, l);
+        }
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+// Same planes, one CTA per output row (image b, row ho): the hf input rows of every
+// channel that this output row touches are staged in shared memory once (coalesced
+// reads), then each thread owns a few k = (cin, hf, wf) and walks along wo, so the
+// (cin, hf, wf) decode happens once per k and the plane writes are coalesced along k.
+__global__ void __launch_bounds__(256)
+im2col_split_rows_kernel(const float* __restrict__ in, float* __restrict__ hi, float* __restrict__ lo, int cin, int H, int W,
+                         int hf, int wf, int stride, int pad, int Ho, int Wo, int Kg, int Kp) {
+    extern __shared__ float patch[];  // [cin][hf][W]
+    const int b = blockIdx.x / Ho, ho = blockIdx.x - b * Ho;
+    const int rows = cin * hf;
+    for (int e = threadIdx.x; e < rows * W; e += blockDim.x) {
+        const int r = e / W, x = e - r * W;
+        const int ci = r / hf, fh = r - ci * hf;
+        const int y = ho * stride - pad + fh;
+        patch[e] = (y >= 0 && y < H) ? __ldg(in + (((long long) b * cin + ci) * H + y) * W + x) : 0.0f;
+    }
+    __syncthreads();
+    const long long row_base = ((long long) b * Ho + ho) * Wo;
+    for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+        const bool real = k < Kg;
+        const int ci = k / (hf * wf), r = k - ci * (hf * wf);
+        const int fh = r / wf, fw = r - fh * wf;
+        const float* src = patch + (ci * hf + fh) * W;
+        for (int wo = 0; wo < Wo; wo++) {
+            const int x = wo * stride - pad + fw;
+            float h = 0.f, l = 0.f;
+            if (real && x >= 0 && x < W) split_tf32(src[x], h, l);
+            const long long o = (row_base + wo) * Kp + k;
+            hi[o] = h;
+            lo[o] = l;
+        }
+    }
+}
+
 // sum of split-K partial planes -> C
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ part, long long plane, int splits, float* __restrict__ C, int M, int N, int ldc,
@@ -521,6 +602,8 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.kblocks = (g.K + BK - 1) / BK;
     a.splits = splits;
     a.order = g.order;
+    a.out_p = (splits > 1) ? 0 : g.out_p;
+    a.out_image_stride = g.out_image_stride;
     a.status_word = status_word;
     if (splits > 1) {
         a.C = partials; a.plane = (long long) g.M * g.N; a.ldc = g.N; a.accumulate = 0;
@@ -598,6 +681,27 @@ int tf32x3_split_B(const float* B, int ldb, int K, int N, const Tf32x3Planes& p,
     return run_split_transpose(B, p.b_hi, p.b_lo, K, N, ldb, p.Kp, stream);
 }
 
+// B planes of a convolution: n = (image, ho, wo) rows, k = (cin, hf, wf) columns
+int tf32x3_split_im2col(const float* in, int batch, int cin, int H, int W, int hf, int wf, int stride, int pad,
+                        const Tf32x3Planes& p, int sm_count, cudaStream_t stream) {
+    const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
+    const long long total = (long long) batch * Ho * Wo * p.Kp;
+    if (total <= 0) return CAKEB200_OK;
+    const size_t patch_bytes = (size_t) cin * hf * W * sizeof(float);
+    if (patch_bytes <= 200 * 1024 && (long long) batch * Ho <= 0x7fffffffLL) {
+        CAKE_CUDA_OK(cudaFuncSetAttribute(im2col_split_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) patch_bytes));
+        im2col_split_rows_kernel<<<batch * Ho, 256, patch_bytes, stream>>>(in, p.b_hi, p.b_lo, cin, H, W, hf, wf, stride, pad,
+                                                                          Ho, Wo, cin * hf * wf, p.Kp);
+        CAKE_CUDA_OK(cudaGetLastError());
+        return CAKEB200_OK;
+    }
+    const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 32);
+    im2col_split_kernel<<<blocks, 256, 0, stream>>>(in, p.b_hi, p.b_lo, batch, cin, H, W, hf, wf, stride, pad, Ho, Wo,
+                                                    cin * hf * wf, p.Kp);
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
+
 int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const Tf32x3Planes& p, int sm_count,
                         cudaStream_t stream) {
     return run_split_rows(A + (size_t) r0 * lda, p.a_hi + (size_t) r0 * p.Kp, p.a_lo + (size_t) r0 * p.Kp, rows, K, lda,
@@ -605,7 +709,8 @@ int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const 
 }
 
 int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int rows, int N, int K, int order,
-                         int accumulate, int* status_word, int sm_count, cudaStream_t stream) {
+                         int accumulate, int* status_word, int sm_count, cudaStream_t stream, int out_p,
+                         long long out_image_stride) {
     GemmProblem g = {};
     g.C = C + (size_t) r0 * ldc;
     g.M = rows; g.N = N; g.K = K;
@@ -613,6 +718,8 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     g.batch = 1;
     g.order = order;
     g.accumulate = accumulate;
+    g.out_p = out_p;
+    g.out_image_stride = out_image_stride;
     float* a_hi = p.a_hi + (size_t) r0 * p.Kp;
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
     return (N > 128) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, nullptr, 1, status_word, sm_count, stream)

@@ -77,6 +77,57 @@ compact_rows_kernel(const float* __restrict__ A, int M, int K, const long long* 
     }
 }
 
+// 128-bit variants for rows that are 16-byte aligned (K % 4 == 0): a warp step covers 128 columns.
+__global__ void __launch_bounds__(256) row_nnz_vec4_kernel(const float4* __restrict__ A, int M, int K4, int* __restrict__ cnt) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const float4* row = A + (long long) warp * K4;
+    int n = 0;
+    for (int k = lane; k < K4; k += 32) {
+        const float4 v = __ldg(row + k);
+        n += (v.x != 0.0f) + (v.y != 0.0f) + (v.z != 0.0f) + (v.w != 0.0f);
+    }
+    for (int o = 16; o; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    if (lane == 0) cnt[warp] = n;
+}
+
+__global__ void __launch_bounds__(256)
+compact_rows_vec4_kernel(const float4* __restrict__ A, int M, int K4, const long long* __restrict__ ptr,
+                         int* __restrict__ cols, float* __restrict__ vals, int* status) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const float4* row = A + (long long) warp * K4;
+    long long base = ptr[warp];
+    const long long limit = ptr[warp + 1];
+    for (int k0 = 0; k0 < K4; k0 += 32) {
+        const int k4 = k0 + lane;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k4 < K4) v = __ldg(row + k4);
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        // survivors of this lane, then an exclusive prefix over the lanes: ascending column order is kept
+        const int mine = (e[0] != 0.0f) + (e[1] != 0.0f) + (e[2] != 0.0f) + (e[3] != 0.0f);
+        int incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        long long slot = base + incl - mine;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (e[j] != 0.0f) {
+                if (slot >= limit || slot < 0) {  // more nonzeros than were counted: record, do not write
+                    if (atomicCAS(status, 0, 2) == 0) { status[1] = 11; status[2] = warp; }
+                } else {
+                    cols[slot] = k4 * 4 + j;
+                    vals[slot] = e[j];
+                }
+                slot++;
+            }
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+
 constexpr int SP_BM = 64, SP_BN = 128, SP_BK = 64, SP_WARPS = 8, SP_ROWS = SP_BM / SP_WARPS;
 
 template <bool VEC>
@@ -160,7 +211,109 @@ spmm_rows_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols
     }
 }
 
+// Very sparse A: each 64-deep slab of B would be staged for a handful of nonzeros, so
+// the slab staging is dropped.  One warp owns one row of A and a 512-column slab of C;
+// it loads 32 (column, value) pairs at a time, broadcasts them with shuffles and, for
+// each nonzero, reads the matching piece of row k of B straight from L2 (four
+// independent 128-bit loads per lane).  Same FMA order per element as the staged kernel.
+constexpr int SG_BN = 512;
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+spmm_gather_kernel(const long long* __restrict__ ptr, const int* __restrict__ cols, const float* __restrict__ vals,
+                   const float* __restrict__ B, float* __restrict__ C, int M, int N, int K, int* status) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.y * 8 + warp, n0 = blockIdx.x * SG_BN;
+    if (m >= M) return;
+    long long c = ptr[m], e = ptr[m + 1];
+    if (c < 0 || e < c || e > (long long) M * K) {  // corrupt row list: record, produce zeros
+        if (lane == 0 && atomicCAS(status, 0, 2) == 0) { status[1] = 13; status[2] = m; }
+        c = e = 0;
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+
+    for (; c < e; c += 32) {
+        const long long mine = c + lane;
+        const int my_k = (mine < e) ? __ldg(cols + mine) : 0;
+        const float my_a = (mine < e) ? __ldg(vals + mine) : 0.0f;
+        const int cnt = (int) min((long long) 32, e - c);
+#pragma unroll 4
+        for (int t = 0; t < cnt; t++) {
+            int k = __shfl_sync(0xffffffffu, my_k, t);
+            const float a = __shfl_sync(0xffffffffu, my_a, t);
+            if ((unsigned) k >= (unsigned) K) {  // never for a list built by compact_rows_kernel
+                if (lane == 0 && atomicCAS(status, 0, 2) == 0) { status[1] = 14; status[2] = m; }
+                continue;
+            }
+            const float* brow = B + (long long) k * N + n0 + lane * 4;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int col = n0 + j * 128 + lane * 4;
+                float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (VEC) {
+                    if (col < N) b = __ldg(reinterpret_cast<const float4*>(brow + j * 128));
+                } else {
+                    if (col + 0 < N) b.x = __ldg(brow + j * 128 + 0);
+                    if (col + 1 < N) b.y = __ldg(brow + j * 128 + 1);
+                    if (col + 2 < N) b.z = __ldg(brow + j * 128 + 2);
+                    if (col + 3 < N) b.w = __ldg(brow + j * 128 + 3);
+                }
+                acc[j][0] = fmaf(a, b.x, acc[j][0]);
+                acc[j][1] = fmaf(a, b.y, acc[j][1]);
+                acc[j][2] = fmaf(a, b.z, acc[j][2]);
+                acc[j][3] = fmaf(a, b.w, acc[j][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int col = n0 + j * 128 + lane * 4;
+        float* dst = C + (long long) m * N + col;
+        if (VEC) {
+            if (col < N) *reinterpret_cast<float4*>(dst) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                if (col + q < N) dst[q] = acc[j][q];
+        }
+    }
+}
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct SparseLayout {
+    int* cnt;
+    long long* ptr;
+    int* cols;
+    float* vals;
+};
+SparseLayout layout_of(void* scratch, int M, int K) {
+    SparseLayout l;
+    char* base = (char*) scratch;
+    l.cnt = (int*) base;
+    base += align_up((size_t) M * 4, 256);
+    l.ptr = (long long*) base;
+    base += align_up(((size_t) M + 1) * 8, 256);
+    l.cols = (int*) base;
+    base += align_up((size_t) M * K * 4, 256);
+    l.vals = (float*) base;
+    return l;
+}
+
+// CAKEB200_DEBUG_SYNC=1: wait after every kernel and name the one that failed
+int after_kernel(const char* what, cudaStream_t stream) {
+    static const bool debug_sync = getenv("CAKEB200_DEBUG_SYNC") != nullptr;
+    if (!debug_sync) return CAKEB200_OK;
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("sparse: %s failed: %s", what, cudaGetErrorString(e));
+        return CAKEB200_ERR_CUDA;
+    }
+    return CAKEB200_OK;
+}
 
 }  // namespace
 
@@ -172,46 +325,59 @@ size_t sparse_scratch_bytes(int M, int K) {
     return align_up((size_t) M * 4, 256) + align_up(((size_t) M + 1) * 8, 256) + align_up(cells * 4, 256) * 2;
 }
 
-int launch_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K, void* scratch,
-                    int* status_word, cudaStream_t stream, int* launches) {
-    // CAKEB200_DEBUG_SYNC=1: wait after every kernel and name the one that failed
-    static const bool debug_sync = getenv("CAKEB200_DEBUG_SYNC") != nullptr;
-    auto after = [&](const char* what) -> int {
-        if (!debug_sync) return CAKEB200_OK;
-        cudaError_t e = cudaStreamSynchronize(stream);
-        if (e == cudaSuccess) e = cudaGetLastError();
-        if (e != cudaSuccess) {
-            set_error("sparse: %s failed: %s", what, cudaGetErrorString(e));
-            return CAKEB200_ERR_CUDA;
-        }
-        return CAKEB200_OK;
-    };
+// Step 1: count, scan, compact.  Returns the number of nonzeros (one 8-byte read-back:
+// the caller picks the multiply kernel, or the dense tensor-core product, from the density).
+int sp_compact(const float* A, int M, int K, void* scratch, int* status_word, cudaStream_t stream,
+               long long* nnz, int* launches) {
+    const SparseLayout l = layout_of(scratch, M, K);
     int rc;
-    char* base = (char*) scratch;
-    int* cnt = (int*) base;
-    base += align_up((size_t) M * 4, 256);
-    long long* ptr = (long long*) base;
-    base += align_up(((size_t) M + 1) * 8, 256);
-    int* cols = (int*) base;
-    base += align_up((size_t) M * K * 4, 256);
-    float* vals = (float*) base;
-
     const int row_blocks = (M + 7) / 8;  // 8 warps (rows) per 256-thread CTA
-    row_nnz_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, cnt);
-    if ((rc = after("row_nnz_kernel"))) return rc;
-    row_ptr_kernel<<<1, 1024, 0, stream>>>(cnt, M, ptr);
-    if ((rc = after("row_ptr_kernel"))) return rc;
-    compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, ptr, cols, vals, status_word);
-    if ((rc = after("compact_rows_kernel"))) return rc;
-    dim3 grid((N + SP_BN - 1) / SP_BN, (M + SP_BM - 1) / SP_BM);
-    const bool vec = (N % 4 == 0) && (((uintptr_t) B | (uintptr_t) C) % 16 == 0);
+    const bool vec = (K % 4 == 0) && ((uintptr_t) A % 16 == 0);
     if (vec)
-        spmm_rows_kernel<true><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K, status_word);
+        row_nnz_vec4_kernel<<<row_blocks, 256, 0, stream>>>((const float4*) A, M, K / 4, l.cnt);
     else
-        spmm_rows_kernel<false><<<grid, SP_WARPS * 32, 0, stream>>>(ptr, cols, vals, B, C, M, N, K, status_word);
+        row_nnz_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, l.cnt);
+    if ((rc = after_kernel("row_nnz_kernel", stream))) return rc;
+    row_ptr_kernel<<<1, 1024, 0, stream>>>(l.cnt, M, l.ptr);
+    if ((rc = after_kernel("row_ptr_kernel", stream))) return rc;
+    if (vec)
+        compact_rows_vec4_kernel<<<row_blocks, 256, 0, stream>>>((const float4*) A, M, K / 4, l.ptr, l.cols, l.vals, status_word);
+    else
+        compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, l.ptr, l.cols, l.vals, status_word);
     CAKE_CUDA_OK(cudaGetLastError());
-    if ((rc = after("spmm_rows_kernel"))) return rc;
-    if (launches) *launches += 4;
+    if ((rc = after_kernel("compact_rows_kernel", stream))) return rc;
+    long long total = 0;
+    CAKE_CUDA_OK(cudaMemcpyAsync(&total, l.ptr + M, sizeof(total), cudaMemcpyDeviceToHost, stream));
+    CAKE_CUDA_OK(cudaStreamSynchronize(stream));
+    if (nnz) *nnz = total;
+    if (launches) *launches += 3;
+    return CAKEB200_OK;
+}
+
+// Step 2: multiply the compacted rows.  Below ~3 % nonzeros rows are gathered from L2
+// one nonzero at a time; above, slabs of B are staged in shared memory and shared by 64 rows.
+int sp_multiply(const float* B, float* C, int M, int N, int K, void* scratch, long long nnz, int* status_word,
+                cudaStream_t stream, int* launches) {
+    const SparseLayout l = layout_of(scratch, M, K);
+    int rc;
+    const bool vec = (N % 4 == 0) && (((uintptr_t) B | (uintptr_t) C) % 16 == 0);
+    const bool gather = (double) nnz < 0.03 * (double) M * (double) K;
+    if (gather) {
+        dim3 grid((N + SG_BN - 1) / SG_BN, (M + 7) / 8);
+        if (vec)
+            spmm_gather_kernel<true><<<grid, 256, 0, stream>>>(l.ptr, l.cols, l.vals, B, C, M, N, K, status_word);
+        else
+            spmm_gather_kernel<false><<<grid, 256, 0, stream>>>(l.ptr, l.cols, l.vals, B, C, M, N, K, status_word);
+    } else {
+        dim3 grid((N + SP_BN - 1) / SP_BN, (M + SP_BM - 1) / SP_BM);
+        if (vec)
+            spmm_rows_kernel<true><<<grid, SP_WARPS * 32, 0, stream>>>(l.ptr, l.cols, l.vals, B, C, M, N, K, status_word);
+        else
+            spmm_rows_kernel<false><<<grid, SP_WARPS * 32, 0, stream>>>(l.ptr, l.cols, l.vals, B, C, M, N, K, status_word);
+    }
+    CAKE_CUDA_OK(cudaGetLastError());
+    if ((rc = after_kernel(gather ? "spmm_gather_kernel" : "spmm_rows_kernel", stream))) return rc;
+    if (launches) *launches += 1;
     return CAKEB200_OK;
 }
 

@@ -215,30 +215,59 @@ def test_pack_on_device_pointers(cake, oracle):
 
 
 def test_sparse_product_bit_exact_and_against_dense_reference(cake, oracle):
-    for (M, K, N, d) in [(300, 257, 130, 0.5), (513, 1000, 260, 0.1), (1024, 2048, 515, 0.01), (7, 5, 3, 0.5)]:
+    # densities on both sides of the 3 % switch between the staged and the gathering multiply kernel,
+    # aligned and ragged N, an all-zero operand
+    for (M, K, N, d) in [(300, 257, 130, 0.5), (513, 1000, 260, 0.1), (1024, 2048, 515, 0.01), (7, 5, 3, 0.5),
+                         (512, 1024, 640, 0.02), (130, 300, 1100, 0.005), (64, 64, 64, 0.0)]:
         A = oracle.sparse((M, K), 1, 3, d)
         B = oracle.uniform((K, N), 2)
-        C = cake.cake_sp_sgemm(A, B)
+        C = cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_FFMA)  # forced zero-skipping kernels
+        assert cake.last_stats()["kernel"] == cake.KERNEL_FFMA
         assert np.array_equal(C, oracle.sp_sgemm(A, B)), (M, K, N, d)
         dense_ref, _ = oracle.sgemm(A, B, 8, NA)  # the reference's dense path on the densified operand
         assert rel_err(C, dense_ref, A, B) <= TOL
-        C3 = cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_TF32X3)
-        assert rel_err(C3, dense_ref, A, B) <= TOL
+        for kernel in (cake.KERNEL_TF32X3, cake.KERNEL_AUTO):
+            C3 = cake.cake_sp_sgemm(A, B, kernel=kernel)
+            assert rel_err(C3, dense_ref, A, B) <= TOL
+    # AUTO: dense tensor-core product once more than ~1 % is nonzero and the product is large, else zero skipping
+    A, B = oracle.sparse((1024, 2048), 1, 3, 0.05), oracle.uniform((2048, 512), 2)
+    cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_AUTO)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+    A = oracle.sparse((1024, 2048), 1, 3, 0.002)
+    cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_AUTO)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_FFMA
 
 
 def test_im2col_and_conv(cake, oracle):
     for (b, cin, H, W, cout, hf, stride, pad) in [(2, 3, 7, 6, 5, 3, 1, 1), (3, 8, 14, 14, 16, 3, 1, 1),
-                                                 (1, 4, 9, 9, 6, 3, 2, 0), (2, 16, 12, 12, 32, 1, 1, 0)]:
+                                                 (1, 4, 9, 9, 6, 3, 2, 0), (2, 16, 12, 12, 32, 1, 1, 0),
+                                                 (1, 64, 5, 300, 8, 3, 1, 1)]:  # last: rows too wide to stage in shared memory
         x = oracle.normal((b, cin, H, W), 4, 0.1)
         w = oracle.normal((cout, cin, hf, hf), 5, 0.1)
         assert np.array_equal(cake.im2col(x, hf, hf, stride, pad), oracle.im2col(x, hf, hf, stride, pad))
-        out = cake.cake_conv2d(x, w, stride, pad)
         ref = oracle.conv2d(x, w, stride, pad, 8)
         col = oracle.im2col(x, hf, hf, stride, pad)
-        Ho, Wo = out.shape[2:]
-        got = out.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
-        want = ref.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
-        assert rel_err(got, want, w.reshape(cout, -1), col) <= TOL
+        for kernel in (cake.KERNEL_FFMA, cake.KERNEL_TF32X3, cake.KERNEL_AUTO):
+            out = cake.cake_conv2d(x, w, stride, pad, kernel=kernel)
+            Ho, Wo = out.shape[2:]
+            got = out.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+            want = ref.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+            assert rel_err(got, want, w.reshape(cout, -1), col) <= TOL, (b, cin, H, W, cout, kernel)
+
+
+def test_conv_benchmark_shape_scaled_down(cake, oracle):
+    """The second convolution configuration (256 -> 512 channels, 14 x 14, 3 x 3, pad 1) at batch 4:
+    large enough for the tensor-core route, checked against float64."""
+    import torch
+    x = oracle.normal((4, 256, 14, 14), 4, 0.1)
+    w = oracle.normal((512, 256, 3, 3), 5, 0.1)
+    out = cake.cake_conv2d(x, w, 1, 1)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+    ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=1).numpy()
+    col = oracle.im2col(x, 3, 3, 1, 1)
+    got = out.transpose(1, 0, 2, 3).reshape(512, -1)
+    want = ref.transpose(1, 0, 2, 3).reshape(512, -1)
+    assert rel_err(got, want, w.reshape(512, -1), col) <= TOL
 
 
 def test_batched_small(cake, oracle):
