@@ -1,0 +1,50 @@
+"""One product over the GPUs of a box, one process per GPU (torch.distributed, NCCL).
+
+Rows (or columns) of C are independent, so each rank multiplies its block with
+the library and nothing is exchanged.  Only the deep-K shape is different: K is
+cut, every rank produces a full-size partial product, and the partials are
+summed with a reduce-scatter so that rank r ends up with its row block of C.
+The reference has no distributed layer; its K-first schedule splits a block of
+rows over cores in the same way (reference src/cake_sgemm_k_first.cpp:85-129).
+"""
+import torch
+import torch.distributed as dist
+
+from . import api, partition
+
+
+def _local(a, b, kernel):
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=torch.float32, device=a.device)
+    return api.cake_sgemm(a.contiguous(), b.contiguous(), out, kernel=kernel)
+
+
+def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
+    """A (M x K) and B (K x N) are CUDA tensors present on every rank.  Returns
+    (kind, (lo, hi), block): kind 'rows' -> block = C[lo:hi, :], 'cols' ->
+    C[:, lo:hi], 'k' -> C[lo:hi, :] after the reduce-scatter."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    M, K = A.shape
+    N = B.shape[1]
+
+    def reduce_scatter(partial, r0, r1):
+        if M % world == 0:
+            out = torch.empty((M // world, N), dtype=torch.float32, device=partial.device)
+            dist.reduce_scatter_tensor(out, partial, group=group)
+            lo = rank * (M // world)
+            return out, (lo, lo + M // world)
+        dist.all_reduce(partial, group=group)  # ragged row blocks: sum everywhere, keep the own block
+        return partial[r0:r1], (r0, r1)
+
+    kind = partition.plan(M, N, K, world)
+    if kind == "rows":
+        r0, r1 = partition.row_block(M, world, rank)
+        return kind, (r0, r1), _local(A[r0:r1], B, kernel)
+    if kind == "cols":
+        c0, c1 = partition.col_block(N, world, rank)
+        return kind, (c0, c1), _local(A, B[:, c0:c1], kernel)
+    k0, k1 = partition.k_block(K, world, rank)
+    partial = _local(A[:, k0:k1], B[k0:k1], kernel)
+    r0, r1 = partition.row_block(M, world, rank)
+    block, span = reduce_scatter(partial, r0, r1)
+    return kind, span, block

@@ -1,0 +1,91 @@
+"""One process per GPU over NCCL: row split, column split and the K split with
+its reduce-scatter, each checked against a float64 product.  Needs two GPUs;
+skipped on a single-GPU box (the host logic is covered on CPU by test_partition_gloo.py)."""
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from cake_on_cpu_b200 import distributed
+    results = []
+    for (M, K, N, want) in [(2048, 512, 768, "rows"), (256, 384, 4096, "cols"), (512, 16384, 256, "k"), (300, 20000, 130, "k")]:
+        g = torch.Generator(device="cuda").manual_seed(5)
+        A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
+        B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
+        kind, (lo, hi), block = distributed.sharded_sgemm(A, B)
+        full = A.double() @ B.double()
+        ref = full[:, lo:hi] if kind == "cols" else full[lo:hi]
+        den = A.double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
+        den = den[:, lo:hi] if kind == "cols" else den[lo:hi]
+        err = ((block.double() - ref).abs() / den).max().item()
+        results.append((kind == want, err, lo, hi))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, results)
+    if rank == 0:
+        out.put(gathered)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_nccl(cake):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = out.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for per_rank in res:
+        for ok_kind, err, lo, hi in per_rank:
+            assert ok_kind
+            assert err <= 1e-5
+    # the two ranks' blocks tile the matrix
+    for case in range(len(res[0])):
+        assert res[0][case][2] == 0 and res[0][case][3] == res[1][case][2]
+
+
+def test_cpp_api_splits_rows_over_visible_gpus(cake, tmp_path):
+    """cake_sgemm(p > 1) with host pointers: one host thread per device inside the call."""
+    import numpy as np
+    import ctypes
+    L = ctypes.CDLL(cake.library_path())
+    rng = np.random.default_rng(3)
+    M, K, N = 2304, 256, 640
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    # C++ symbol of cake_sgemm(float*, float*, float*, int, int, int, int, cake_cntx_t*, char**, bool, bool, float, float, sched, int, int, int)
+    fn = getattr(L, "_Z10cake_sgemmPfS_S_iiiiP11cake_cntx_tPPcbbff5schediii")
+    fn.restype = ctypes.c_double
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_bool, ctypes.c_bool,
+                                                              ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+                                                              ctypes.c_int, ctypes.c_int]
+    t = fn(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K, 8, None, None, False, False, 1.0, 0.0, 3, 0, 0, 0)
+    assert t > 0
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    den = np.outer(np.linalg.norm(A, axis=1), np.linalg.norm(B, axis=0))
+    assert (np.abs(C - ref) / den).max() <= 1e-5
