@@ -1,0 +1,168 @@
+"""Times the benchmark configurations of the CAKE SGEMM path on one GPU.
+
+    python -m cake_on_cpu_b200.workloads [--config NAME ...] [--reps R] [--list]
+
+Each configuration prints one JSON line: device time of the whole library call
+(CUDA events on the calling stream, operands resident in device memory, best of
+R after one warm-up), the algorithmic work, and the rate against the bound that
+applies (tensor pipe, FP32 pipe or HBM).  Inputs are synthetic and seeded:
+uniform(-1, 1) operands, Bernoulli masks for the sparse operand, normal(0, 0.1)
+for the convolution, as the configurations specify.
+
+The headline number (8192^3 with its end-to-end and CPU-baseline legs) comes from
+bench.py at the repository root; this module covers the other shapes: the square
+sweep, the M-first / N-first / K-first rectangles, the batch of small products,
+sparse A at several densities, the two convolutions and the packing routines.
+"""
+import argparse
+import json
+import sys
+
+import torch
+
+from . import api
+
+HBM_GBS = 6551.4          # measured copy bandwidth of this pool's B200s
+TENSOR_3XTF32 = 274.5     # measured BF16 burst 1647.2 / 2 / 3, TFLOP/s
+FP32_PIPE = 74.4          # 148 SMs x 128 lanes x 2 x 1.965 GHz, TFLOP/s
+
+
+def _timed(fn, reps):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(reps):
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best
+
+
+def _uniform(gen, *shape):
+    return torch.rand(shape, device="cuda", generator=gen) * 2 - 1
+
+
+def _dense(M, K, N, kernel):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        A, B, C = _uniform(g, M, K), _uniform(g, K, N), torch.empty((M, N), device="cuda")
+        ms = _timed(lambda: api.cake_sgemm(A, B, C, kernel=kernel), reps)
+        st = api.last_stats()
+        flops = 2.0 * M * N * K
+        peak = TENSOR_3XTF32 if st["kernel"] == api.KERNEL_TF32X3 else FP32_PIPE
+        return {"ms": ms, "flops": flops, "tflops": flops / ms / 1e9, "bound": "tensor" if peak == TENSOR_3XTF32 else "fp32",
+                "frac": flops / ms / 1e9 / peak, "kernel_ms": st["ms_gemm"], "prepass_ms": st["ms_prepass"],
+                "sched": ["KMN", "MKN", "NKM", "NA"][st["sched"]], "launches": st["launches"]}
+    return run
+
+
+def _batched(batch, n):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        A, B = _uniform(g, batch, n, n), _uniform(g, batch, n, n)
+        C = torch.empty((batch, n, n), device="cuda")
+        ms = _timed(lambda: api.cake_sgemm_batched(A, B, C), reps)
+        flops, nbytes = 2.0 * batch * n ** 3, 3.0 * batch * n * n * 4
+        return {"ms": ms, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
+                "bound": "hbm", "frac": nbytes / ms / 1e6 / HBM_GBS, "frac_fp32_pipe": flops / ms / 1e9 / FP32_PIPE}
+    return run
+
+
+def _sparse(n, density, kernel):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        A = _uniform(g, n, n) * (torch.rand((n, n), device="cuda", generator=g) < density)
+        B, C = _uniform(g, n, n), torch.empty((n, n), device="cuda")
+        nnz = int((A != 0).sum().item())
+        ms = _timed(lambda: api.cake_sp_sgemm(A, B, C, kernel=kernel), reps)
+        st = api.last_stats()
+        flops = 2.0 * nnz * n
+        nbytes = n * n / 8 + 4.0 * nnz + 4.0 * n * n + 4.0 * n * n
+        return {"ms": ms, "nnz": nnz, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
+                "ran": "dense tcgen05" if st["kernel"] == api.KERNEL_TF32X3 else "zero skipping", "bound": "hbm",
+                "frac": nbytes / ms / 1e6 / HBM_GBS}
+    return run
+
+
+def _conv(b, cin, hw, cout):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(4)
+        x = torch.randn((b, cin, hw, hw), device="cuda", generator=g) * 0.1
+        w = torch.randn((cout, cin, 3, 3), device="cuda", generator=g) * 0.1
+        out = torch.empty((b, cout, hw, hw), device="cuda")
+        ms = _timed(lambda: api.cake_conv2d(x, w, 1, 1, out), reps)
+        flops = 2.0 * cout * cin * 9 * b * hw * hw
+        nbytes = 4.0 * (x.numel() + w.numel() + out.numel())
+        return {"ms": ms, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
+                "bound": "tensor", "frac": flops / ms / 1e9 / TENSOR_3XTF32,
+                "ran": "tcgen05" if api.last_stats()["kernel"] == api.KERNEL_TF32X3 else "ffma"}
+    return run
+
+
+def _pack(n, which):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        X = _uniform(g, n, n)
+        cx = api.Cntx.make(49152, 2097152, 110100480, 8)  # CPU-style block sizes, as a caller of the reference has
+        x = api.init_block_dims(n, n, n, 8, cx, api.KMN)
+        if which == "A":
+            P = torch.empty(api.cake_sgemm_packed_A_size(n, n, 8, x, cx, x.sch) // 4, device="cuda")
+            ms = _timed(lambda: api.pack_A(X, n, n, 8, x, cx, P), reps)
+        elif which == "B":
+            P = torch.empty(api.cake_sgemm_packed_B_size(n, n, 8, x, cx) // 4, device="cuda")
+            ms = _timed(lambda: api.pack_B(X, n, n, 8, x, cx, P), reps)
+        else:
+            P = torch.empty(api.cake_sgemm_packed_C_size(n, n, 8, x, cx, x.sch) // 4, device="cuda")
+            api.pack_C(X, n, n, 8, x, cx, P)
+            ms = _timed(lambda: api.unpack_C(P, n, n, 8, x, cx, X), reps)
+        nbytes = 8.0 * n * n
+        return {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "bound": "hbm", "frac": nbytes / ms / 1e6 / HBM_GBS}
+    return run
+
+
+CONFIGS = {}
+for _n in (1024, 2048, 3000, 4096, 8192, 16384, 32768):
+    CONFIGS["square_%d" % _n] = _dense(_n, _n, _n, api.KERNEL_AUTO)
+CONFIGS["square_8192_ffma"] = _dense(8192, 8192, 8192, api.KERNEL_FFMA)
+CONFIGS["rect_m_first"] = _dense(65536, 1024, 1024, api.KERNEL_AUTO)
+CONFIGS["rect_n_first"] = _dense(1024, 1024, 65536, api.KERNEL_AUTO)
+CONFIGS["rect_k_first"] = _dense(1024, 262144, 1024, api.KERNEL_AUTO)
+CONFIGS["small_batch"] = _batched(4096, 96)
+for _d, _name in ((0.5, "50"), (0.1, "10"), (0.01, "1")):
+    CONFIGS["sparse_%s" % _name] = _sparse(8192, _d, api.KERNEL_AUTO)
+    CONFIGS["sparse_%s_zero_skipping" % _name] = _sparse(8192, _d, api.KERNEL_FFMA)
+CONFIGS["conv_64x64x56"] = _conv(64, 64, 56, 64)
+CONFIGS["conv_256x512x14"] = _conv(64, 256, 14, 512)
+CONFIGS["pack_A_8192"] = _pack(8192, "A")
+CONFIGS["pack_B_8192"] = _pack(8192, "B")
+CONFIGS["unpack_C_8192"] = _pack(8192, "C")
+
+DEFAULT = [k for k in CONFIGS if k not in ("square_32768", "sparse_50_zero_skipping", "sparse_10_zero_skipping")]
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", nargs="*", default=None)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--list", action="store_true")
+    args = ap.parse_args(argv)
+    if args.list:
+        print("\n".join(CONFIGS))
+        return 0
+    api.lib()
+    for name in (args.config or DEFAULT):
+        if name not in CONFIGS:
+            print(json.dumps({"config": name, "error": "unknown configuration"}))
+            continue
+        res = CONFIGS[name](args.reps)
+        res = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items()}
+        print(json.dumps(dict(config=name, **res)), flush=True)
+        torch.cuda.empty_cache()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
