@@ -25,26 +25,52 @@ struct ObDesc {
     int row0, col0;        // global coordinates used for the bounds test
 };
 
-// Element e of a packed block -> (row, col) inside the block.
-template <int KIND>
-__device__ __forceinline__ void ob_coords(long long e, int rows, int cols, int mr, int nr, int& r, int& c) {
+// Element e of a packed block -> (row, col) inside the block.  IDX is 32-bit for
+// every block a cache-sized blocking produces; 64-bit only for huge user-defined blocks.
+template <int KIND, typename IDX>
+__device__ __forceinline__ void ob_coords(IDX e, int rows, int cols, int mr, int nr, int& r, int& c) {
     if (KIND == OB_A) {  // [row panel][k][row in panel]
-        long long panel = e / ((long long) cols * mr);
-        int rem = (int) (e - panel * cols * mr);
-        c = rem / mr;
-        r = (int) panel * mr + rem % mr;
+        const IDX per_panel = (IDX) cols * mr;
+        const IDX panel = e / per_panel;
+        const unsigned rem = (unsigned) (e - panel * per_panel);
+        const unsigned k = rem / (unsigned) mr;
+        c = (int) k;
+        r = (int) panel * mr + (int) (rem - k * mr);
     } else if (KIND == OB_B) {  // [col panel][k][col in panel]
-        long long panel = e / ((long long) rows * nr);
-        int rem = (int) (e - panel * rows * nr);
-        r = rem / nr;
-        c = (int) panel * nr + rem % nr;
+        const IDX per_panel = (IDX) rows * nr;
+        const IDX panel = e / per_panel;
+        const unsigned rem = (unsigned) (e - panel * per_panel);
+        const unsigned k = rem / (unsigned) nr;
+        r = (int) k;
+        c = (int) panel * nr + (int) (rem - k * nr);
     } else {  // [col panel][row panel][m_r x n_r tile, row-major]
-        long long panel = e / ((long long) rows * nr);
-        int rem = (int) (e - panel * rows * nr);
-        int rp = rem / (mr * nr);
-        int t = rem - rp * mr * nr;
-        r = rp * mr + t / nr;
-        c = (int) panel * nr + t % nr;
+        const IDX per_panel = (IDX) rows * nr;
+        const IDX panel = e / per_panel;
+        const unsigned rem = (unsigned) (e - panel * per_panel);
+        const unsigned tile = (unsigned) (mr * nr);
+        const unsigned rp = rem / tile;
+        const unsigned t = rem - rp * tile;
+        const unsigned tr = t / (unsigned) nr;
+        r = (int) (rp * mr + tr);
+        c = (int) panel * nr + (int) (t - tr * nr);
+    }
+}
+
+template <int KIND, bool UNPACK, typename IDX>
+__device__ __forceinline__ void ob_move_block(const ObDesc& d, float* __restrict__ mat, float* __restrict__ packed, int ld,
+                                              int row_limit, int col_limit, int mr, int nr) {
+    const IDX elems = (IDX) d.rows * (IDX) d.cols;
+    const IDX step = (IDX) gridDim.y * blockDim.x;
+    for (IDX e = (IDX) blockIdx.y * blockDim.x + threadIdx.x; e < elems; e += step) {
+        int r, c;
+        ob_coords<KIND, IDX>(e, d.rows, d.cols, mr, nr, r, c);
+        const bool inside = (d.row0 + r < row_limit) && (d.col0 + c < col_limit);
+        const long long m_idx = d.mat_off + (long long) r * ld + c;
+        if (UNPACK) {
+            if (inside) mat[m_idx] = packed[d.packed_off + (long long) e];
+        } else {
+            packed[d.packed_off + (long long) e] = inside ? __ldg(mat + m_idx) : 0.0f;
+        }
     }
 }
 
@@ -53,19 +79,10 @@ __global__ void __launch_bounds__(256)
 ob_move_kernel(const ObDesc* __restrict__ descs, float* __restrict__ mat, float* __restrict__ packed,
                int ld, int row_limit, int col_limit, int mr, int nr) {
     const ObDesc d = descs[blockIdx.x];
-    const long long elems = (long long) d.rows * d.cols;
-    for (long long e = (long long) blockIdx.y * blockDim.x + threadIdx.x; e < elems;
-         e += (long long) gridDim.y * blockDim.x) {
-        int r, c;
-        ob_coords<KIND>(e, d.rows, d.cols, mr, nr, r, c);
-        const bool inside = (d.row0 + r < row_limit) && (d.col0 + c < col_limit);
-        const long long m_idx = d.mat_off + (long long) r * ld + c;
-        if (UNPACK) {
-            if (inside) mat[m_idx] = packed[d.packed_off + e];
-        } else {
-            packed[d.packed_off + e] = inside ? __ldg(mat + m_idx) : 0.0f;
-        }
-    }
+    if ((long long) d.rows * d.cols < 0x7fffffffLL - (long long) gridDim.y * blockDim.x)
+        ob_move_block<KIND, UNPACK, unsigned>(d, mat, packed, ld, row_limit, col_limit, mr, nr);
+    else
+        ob_move_block<KIND, UNPACK, long long>(d, mat, packed, ld, row_limit, col_limit, mr, nr);
 }
 
 struct Split {
