@@ -664,8 +664,8 @@ int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch
         // hi / lo planes are produced directly from the input (im2col is never materialised); the
         // epilogue stores (cout, (image, position)) straight into NCHW.
         Tf32x3Planes planes;
-        if ((rc = ensure_scratch(st, tf32x3_plane_bytes(cout, (int) Ng, Kg)))) return rc;
-        if ((rc = tf32x3_planes(cout, (int) Ng, Kg, st->scratch, st->scratch_bytes, &planes))) return rc;
+        if ((rc = ensure_scratch(st, tf32x3_plane_bytes(cout, (int) Ng, Kg, st->sm_count)))) return rc;
+        if ((rc = tf32x3_planes(cout, (int) Ng, Kg, st->scratch, st->scratch_bytes, &planes, st->sm_count))) return rc;
         if ((rc = tf32x3_split_A_rows((const float*) of.dev, Kg, 0, cout, Kg, planes, st->sm_count, s))) return rc;
         if ((rc = tf32x3_split_im2col((const float*) oi.dev, batch, cin, H, W, hf, wf, stride, pad, planes, st->sm_count, s)))
             return rc;

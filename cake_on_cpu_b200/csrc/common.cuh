@@ -71,10 +71,11 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
 // row-band interface of the 3xTF32 path (operand planes laid out once, rows multiplied band by band)
 struct Tf32x3Planes {
     float *a_hi, *a_lo, *b_hi, *b_lo;
-    int Kp;
+    float* partials;  // room for partial tiles (nullptr: none reserved)
+    int M, Kp;
 };
-size_t tf32x3_plane_bytes(int M, int N, int K);
-int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out);
+size_t tf32x3_plane_bytes(int M, int N, int K, int slots_for_sms = 0);
+int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out, int slots_for_sms = 0);
 int tf32x3_split_B(const float* B, int ldb, int K, int N, const Tf32x3Planes& p, cudaStream_t stream);
 int tf32x3_split_A_rows(const float* A, int lda, int r0, int rows, int K, const Tf32x3Planes& p, int sm_count,
                         cudaStream_t stream);

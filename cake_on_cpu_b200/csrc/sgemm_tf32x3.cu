@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -162,20 +163,46 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (m >> 4) << 24);
 }
 
+// Work of one CTA: first whole tiles taken round-robin (tile = blockIdx.x + i * gridDim.x
+// for tiles below dp_tiles), then the K-range pieces listed for it in `units`.  A piece
+// that covers only part of K stores its accumulator in a slot of `partials`; a separate
+// kernel adds the slots of each tile up in a fixed order.
 struct Tf32x3Args {
-    float* C;            // output (or split-K partial planes when splits > 1)
-    long long plane;     // elements between split-K partial planes
+    float* C;
+    float* partials;         // [slot][BM x BN]
+    const int4* units;       // {tile, first k-block, end k-block, slot or -1 = whole K, store to C}
+    const int* cta_begin;    // units of CTA b are [cta_begin[b], cta_begin[b + 1])
+    int dp_tiles;
     int M, N, K;
     int ldc;
     int tiles_m, tiles_n;
-    int splits;          // K is cut into this many ranges, one work unit each
-    int kblocks;         // ceil(K / BK)
+    int kblocks;             // ceil(K / BK)
     int order;
-    int accumulate;      // only honoured when splits == 1
-    int out_p;           // > 0: N axis is (image, position), see GemmProblem::out_p
+    int accumulate;          // for tiles stored straight to C
+    int out_p;               // > 0: N axis is (image, position), see GemmProblem::out_p
     long long out_image_stride;
     int* status_word;
 };
+
+struct WorkPiece {
+    int tile, kb0, kb1, slot;
+};
+
+// The it-th piece of this CTA; every role of the CTA walks the same sequence.
+__device__ __forceinline__ bool work_piece(const Tf32x3Args& a, int it, WorkPiece& w) {
+    const int g = (int) gridDim.x, b = (int) blockIdx.x;
+    const int whole = (b < a.dp_tiles) ? (a.dp_tiles - b + g - 1) / g : 0;
+    if (it < whole) {
+        w.tile = b + it * g; w.kb0 = 0; w.kb1 = a.kblocks; w.slot = -1;
+        return true;
+    }
+    if (a.units == nullptr) return false;
+    const int u = a.cta_begin[b] + (it - whole);
+    if (u >= a.cta_begin[b + 1]) return false;
+    const int4 p = a.units[u];
+    w.tile = p.x; w.kb0 = p.y; w.kb1 = p.z; w.slot = p.w;
+    return true;
+}
 
 // ------------------------------------------------------------------ the kernel
 
@@ -224,8 +251,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int units = args.tiles_m * args.tiles_n * args.splits;
-    const int kb_per_split = (args.kblocks + args.splits - 1) / args.splits;
+    WorkPiece w;
 
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer
@@ -233,12 +259,10 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const int split = u % args.splits, tile = u / args.splits;
+            for (int it = 0; ok && work_piece(args, it, w); it++) {
                 int tm, tn;
-                tile_coords(tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
-                const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
-                for (int kb = kb0; kb < kb1; kb++) {
+                tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
                     if (!ok) break;
                     const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
@@ -269,9 +293,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, local++) {
-                const int split = u % args.splits;
-                const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
+            for (; ok && work_piece(args, local, w); local++) {
+                const int kb0 = w.kb0, kb1 = w.kb1;
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
@@ -309,11 +332,10 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
         int local = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, local++) {
-            const int split = u % args.splits, tile = u / args.splits;
+        for (; ok && work_piece(args, local, w); local++) {
             int tm, tn;
-            tile_coords(tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
-            const int kb0 = split * kb_per_split, kb1 = min(kb0 + kb_per_split, args.kblocks);
+            tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
+            const int kb0 = w.kb0, kb1 = w.kb1;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
@@ -321,9 +343,12 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             if (!ok) break;
             tcgen05_fence_after();
             const int row = tm * BM + quarter * 32 + lane;
-            float* crow = args.C + (long long) split * args.plane + (long long) row * args.ldc;
-            const bool vec_ok = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0) && (args.plane % 4 == 0);
-            const bool empty_range = kb0 >= kb1;  // a split with no K range contributes zeros
+            float* crow = args.C + (long long) row * args.ldc;
+            const bool vec_ok = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
+            const bool empty_range = kb0 >= kb1;  // a piece with no K range contributes zeros
+            // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
+            // beyond the matrix are zeros computed from zero-filled operand tiles)
+            float* slot_row = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32 + lane) * BN : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 float v[32];
@@ -335,7 +360,11 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                     for (int j = 0; j < 32; j++) v[j] = 0.0f;
                 }
                 const int col0 = tn * BN + c * 32;
-                if (args.out_p > 0) {
+                if (slot_row != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(slot_row + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else if (args.out_p > 0) {
                     // convolution output: columns are (image, position); rows are output channels
                     if (row < args.M && col0 < args.N) {
                         const int img = col0 / args.out_p, pos = col0 - img * args.out_p;
@@ -511,17 +540,42 @@ im2col_split_rows_kernel(const float* __restrict__ in, float* __restrict__ hi, f
     }
 }
 
-// sum of split-K partial planes -> C
+// A tile whose K range was cut into pieces: its partial accumulators sit in `count`
+// consecutive slots and are added up in slot order (ascending K), then stored to C.
+struct TilePieces {
+    int tm, tn, first_slot, count;
+};
+
+template <int BN>
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ part, long long plane, int splits, float* __restrict__ C, int M, int N, int ldc,
-                     int accumulate) {
-    const long long total = (long long) M * N;
-    for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long) gridDim.x * blockDim.x) {
-        const int m = (int) (i / N), n = (int) (i - (long long) m * N);
-        float s = 0.f;
-        for (int p = 0; p < splits; p++) s += part[(long long) p * plane + i];
-        float* dst = C + (long long) m * ldc + n;
-        *dst = accumulate ? *dst + s : s;
+reduce_pieces_kernel(const float* __restrict__ partials, const TilePieces* __restrict__ tiles, float* __restrict__ C, int M,
+                     int N, int ldc, int accumulate, int out_p, long long out_image_stride) {
+    const TilePieces t = tiles[blockIdx.x];
+    const float* base = partials + (long long) t.first_slot * (BM * BN);
+    // gridDim.y CTAs share a tile, each taking a band of its rows
+    const int rows_per = BM / (int) gridDim.y, r_lo = (int) blockIdx.y * rows_per;
+    for (int i = threadIdx.x; i < rows_per * BN / 4; i += blockDim.x) {
+        const int r = r_lo + i / (BN / 4), c = (i % (BN / 4)) * 4;
+        float4 s = *reinterpret_cast<const float4*>(base + (long long) r * BN + c);
+        for (int p = 1; p < t.count; p++) {
+            const float4 v = *reinterpret_cast<const float4*>(base + (long long) p * (BM * BN) + (long long) r * BN + c);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const int row = t.tm * BM + r, col = t.tn * BN + c;
+        if (row >= M) continue;
+        const float e[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (col + j >= N) break;
+            long long at;
+            if (out_p > 0) {
+                const int img = (col + j) / out_p, pos = (col + j) - img * out_p;
+                at = (long long) img * out_image_stride + (long long) row * out_p + pos;
+            } else {
+                at = (long long) row * ldc + col + j;
+            }
+            C[at] = accumulate ? C[at] + e[j] : e[j];
+        }
     }
 }
 
@@ -570,23 +624,175 @@ int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int b
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
 
-// Tile width and number of K ranges per tile.  With few output tiles the K
-// dimension is cut so that every SM still gets work (the role K-first blocking
-// plays in the reference when M and N are small, src/block_sizing.cpp:434-462).
-void plan_tiles(int M, int N, int K, int sm_count, int* bn, int* splits) {
-    *bn = (N > 128) ? 256 : 128;
-    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + *bn - 1) / *bn);
-    const int kblocks = (K + BK - 1) / BK;
-    *splits = 1;
-    if (tiles * 2 > sm_count) return;
-    int s = (int) (sm_count / tiles);
-    s = std::min(s, std::max(kblocks / 8, 1));  // at least 8 k-blocks (256 of K) per range
-    *splits = std::max(1, std::min(s, 32));
+inline int tile_width(int N) { return (N > 128) ? 256 : 128; }
+
+// host copy of tile_coords (common.cuh)
+void host_tile_coords(int id, int tiles_m, int tiles_n, int order, int& tm, int& tn) {
+    if (order == CAKEB200_SCHED_MKN) {
+        tm = id % tiles_m; tn = id / tiles_m;
+    } else if (order == CAKEB200_SCHED_NKM) {
+        tn = id % tiles_n; tm = id / tiles_n;
+    } else {
+        const int G = 8, band = id / (G * tiles_n), first = band * G;
+        const int rows = std::min(G, tiles_m - first), in_band = id - band * G * tiles_n;
+        tm = first + in_band % rows;
+        tn = in_band / rows;
+        if (band & 1) tn = tiles_n - 1 - tn;
+    }
 }
 
+// How the tiles of one product are spread over the persistent CTAs.  Whole waves of
+// tiles are taken round-robin, one whole-K tile per CTA per wave.  When the tile count
+// is not a multiple of the CTA count, the last full wave plus the remainder (or all
+// tiles, when there are fewer tiles than CTAs) is laid out as one long row of k-blocks
+// and cut into equal shares, so every CTA finishes at the same time; tiles that end up
+// cut get their pieces summed by reduce_pieces_kernel.  This is how the K-first schedule
+// keeps all cores busy on shapes with few output blocks (src/cake_sgemm_k_first.cpp:75-98).
+struct HostPlan {
+    int grid = 0, dp_tiles = 0, slots = 0;
+    std::vector<int4> units;
+    std::vector<int> cta_begin;
+    std::vector<TilePieces> pieces;
+};
+
+HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count) {
+    HostPlan p;
+    const long long T = (long long) tiles_m * tiles_n;
+    const int G = (int) std::min<long long>(T, sm_count);
+    p.grid = G;
+    p.dp_tiles = (int) T;
+    p.cta_begin.assign(G + 1, 0);
+    if (G == 0) return p;
+    // Whole waves are taken round-robin.  The R tiles left over (fewer than there are SMs)
+    // would occupy only R SMs for a whole tile time, so each of them is cut into s equal
+    // K ranges.  Pieces are numbered K-range-major: pieces that run at the same time read
+    // the same K range of the operands, which keeps them shared in L2 (a cut that staggers
+    // the K ranges over the CTAs turned out DRAM-bound).  s minimises
+    // ceil(R*s / SMs) / s tile times plus the cost of writing and re-reading the partial tiles.
+    const int R = (int) (T % sm_count);
+    if (R == 0 || kblocks < 16) return p;
+    const int s_max = std::min(std::min(32, kblocks / 8), std::max(1, (4 * sm_count) / R));
+    const double tile_us = 1.17 * kblocks, slot_us = 0.09, fixed_us = 8.0;
+    int best_s = 1;
+    double best = tile_us;
+    for (int s = 2; s <= s_max; s++) {
+        const long long rounds = ((long long) R * s + sm_count - 1) / sm_count;
+        const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
+        if (cost < best * 0.97) { best = cost; best_s = s; }
+    }
+    if (best_s == 1) return p;
+    const int s = best_s;
+    p.dp_tiles = (int) T - R;
+    p.grid = (int) std::min<long long>((long long) sm_count, std::max<long long>(G, (long long) R * s));
+    p.slots = R * s;
+    const int per = (kblocks + s - 1) / s;
+    std::vector<std::vector<int4>> per_cta(p.grid);
+    for (int q = 0; q < s; q++)
+        for (int r = 0; r < R; r++) {
+            const int u = q * R + r;
+            const int k0 = std::min(kblocks, q * per), k1 = std::min(kblocks, k0 + per);
+            per_cta[u % p.grid].push_back(make_int4(p.dp_tiles + r, k0, k1, r * s + q));
+        }
+    p.cta_begin.assign(p.grid + 1, 0);
+    for (int c = 0; c < p.grid; c++) {
+        p.cta_begin[c] = (int) p.units.size();
+        p.units.insert(p.units.end(), per_cta[c].begin(), per_cta[c].end());
+    }
+    p.cta_begin[p.grid] = (int) p.units.size();
+    for (int r = 0; r < R; r++) {
+        int tm, tn;
+        host_tile_coords(p.dp_tiles + r, tiles_m, tiles_n, order, tm, tn);
+        p.pieces.push_back({tm, tn, r * s, s});
+    }
+    return p;
+}
+
+// Device copies of plans, cached per device by shape.  A slot is overwritten only after
+// the last kernel that read it has finished (event), so asynchronous callers may queue
+// many products ahead.
+struct PlanKey {
+    int tiles_m, tiles_n, kblocks, order, sm_count, bn;
+    bool operator==(const PlanKey& o) const {
+        return tiles_m == o.tiles_m && tiles_n == o.tiles_n && kblocks == o.kblocks && order == o.order &&
+               sm_count == o.sm_count && bn == o.bn;
+    }
+};
+struct DevicePlan {
+    PlanKey key = {};
+    bool valid = false;
+    int grid = 0, dp_tiles = 0, slots = 0, num_pieces = 0;
+    char* dev = nullptr;
+    size_t dev_bytes = 0;
+    const int4* units = nullptr;
+    const int* cta_begin = nullptr;
+    const TilePieces* pieces = nullptr;
+    cudaEvent_t last_use = nullptr;
+    unsigned long long stamp = 0;
+};
+constexpr int PLAN_SLOTS = 16, PLAN_DEVICES = 64;
+DevicePlan g_plans[PLAN_DEVICES][PLAN_SLOTS];
+unsigned long long g_plan_clock = 0;
+std::mutex g_plan_mutex;
+
+int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn, cudaStream_t stream, DevicePlan** out) {
+    int dev = 0;
+    CAKE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= PLAN_DEVICES) dev = 0;
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn};
+    DevicePlan* slots = g_plans[dev];
+    DevicePlan* victim = &slots[0];
+    for (int i = 0; i < PLAN_SLOTS; i++) {
+        if (slots[i].valid && slots[i].key == key) {
+            slots[i].stamp = ++g_plan_clock;
+            *out = &slots[i];
+            return CAKEB200_OK;
+        }
+        if (!slots[i].valid) { victim = &slots[i]; break; }
+        if (slots[i].stamp < victim->stamp) victim = &slots[i];
+    }
+    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count);
+    const size_t units_b = align_up(hp.units.size() * sizeof(int4) + 16, 256);
+    const size_t begin_b = align_up(hp.cta_begin.size() * sizeof(int), 256);
+    const size_t pieces_b = align_up(hp.pieces.size() * sizeof(TilePieces) + 16, 256);
+    const size_t need = units_b + begin_b + pieces_b;
+    if (victim->last_use) CAKE_CUDA_OK(cudaEventSynchronize(victim->last_use));
+    else CAKE_CUDA_OK(cudaEventCreateWithFlags(&victim->last_use, cudaEventDisableTiming));
+    if (need > victim->dev_bytes) {
+        if (victim->dev) CAKE_CUDA_OK(cudaFree(victim->dev));
+        victim->dev = nullptr;
+        victim->dev_bytes = 0;
+        CAKE_CUDA_OK(cudaMalloc((void**) &victim->dev, need));
+        victim->dev_bytes = need;
+    }
+    victim->valid = false;
+    if (!hp.units.empty())
+        CAKE_CUDA_OK(cudaMemcpyAsync(victim->dev, hp.units.data(), hp.units.size() * sizeof(int4), cudaMemcpyHostToDevice, stream));
+    CAKE_CUDA_OK(cudaMemcpyAsync(victim->dev + units_b, hp.cta_begin.data(), hp.cta_begin.size() * sizeof(int),
+                                 cudaMemcpyHostToDevice, stream));
+    if (!hp.pieces.empty())
+        CAKE_CUDA_OK(cudaMemcpyAsync(victim->dev + units_b + begin_b, hp.pieces.data(), hp.pieces.size() * sizeof(TilePieces),
+                                     cudaMemcpyHostToDevice, stream));
+    CAKE_CUDA_OK(cudaStreamSynchronize(stream));  // the host vectors die with this scope
+    victim->key = key;
+    victim->grid = hp.grid; victim->dp_tiles = hp.dp_tiles; victim->slots = hp.slots;
+    victim->num_pieces = (int) hp.pieces.size();
+    victim->units = hp.units.empty() ? nullptr : (const int4*) victim->dev;
+    victim->cta_begin = (const int*) (victim->dev + units_b);
+    victim->pieces = (const TilePieces*) (victim->dev + units_b + begin_b);
+    victim->stamp = ++g_plan_clock;
+    victim->valid = true;
+    *out = victim;
+    return CAKEB200_OK;
+}
+
+// bytes of partial-tile slots a product may need (an upper bound that does not depend on the plan)
+size_t partial_slot_bytes(int sm_count) { return (size_t) (4 * sm_count + 8) * BM * 256 * sizeof(float); }
+
+// plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots)
 template <int BN>
-int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, int splits,
-           int* status_word, int sm_count, cudaStream_t stream) {
+int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, DevicePlan* plan,
+           int* status_word, int sm_count, cudaStream_t stream, int* launches) {
     const int Kp = padded_k(g.K);
     alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
@@ -596,29 +802,42 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, BN))) return rc;
 
     Tf32x3Args a;
+    a.C = g.C;
+    a.partials = partials;
     a.M = g.M; a.N = g.N; a.K = g.K;
+    a.ldc = g.ldc;
     a.tiles_m = (g.M + BM - 1) / BM;
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
-    a.splits = splits;
     a.order = g.order;
-    a.out_p = (splits > 1) ? 0 : g.out_p;
+    a.accumulate = g.accumulate;
+    a.out_p = g.out_p;
     a.out_image_stride = g.out_image_stride;
     a.status_word = status_word;
-    if (splits > 1) {
-        a.C = partials; a.plane = (long long) g.M * g.N; a.ldc = g.N; a.accumulate = 0;
-    } else {
-        a.C = g.C; a.plane = 0; a.ldc = g.ldc; a.accumulate = g.accumulate;
-    }
-    const long long units = (long long) a.tiles_m * a.tiles_n * splits;
-    if (units > 0x7fffffffLL) {
+    const long long tiles = (long long) a.tiles_m * a.tiles_n;
+    if (tiles > 0x7fffffffLL) {
         set_error("sgemm_tf32x3: too many tiles");
         return CAKEB200_ERR_TOO_LARGE;
     }
+    int grid;
+    if (plan && plan->units && partials) {
+        a.units = plan->units; a.cta_begin = plan->cta_begin; a.dp_tiles = plan->dp_tiles;
+        grid = plan->grid;
+    } else {
+        a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
+        grid = (int) std::min<long long>(tiles, sm_count);
+    }
     CAKE_CUDA_OK(cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
-    const int grid = (int) std::min<long long>(units, sm_count);
     sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
     CAKE_CUDA_OK(cudaGetLastError());
+    if (launches) (*launches)++;
+    if (a.units && plan->num_pieces > 0) {
+        reduce_pieces_kernel<BN><<<dim3(plan->num_pieces, 16), 256, 0, stream>>>(partials, plan->pieces, g.C, g.M, g.N, g.ldc, g.accumulate,
+                                                                      g.out_p, g.out_image_stride);
+        CAKE_CUDA_OK(cudaGetLastError());
+        if (launches) (*launches)++;
+    }
+    if (a.units) CAKE_CUDA_OK(cudaEventRecord(plan->last_use, stream));
     return CAKEB200_OK;
 }
 
@@ -656,13 +875,16 @@ int run_split_transpose(const float* B, float* hi, float* lo, int K, int N, int 
 // Planes for the whole product are laid out once; B is split once; then each band of
 // rows is split and multiplied as soon as its rows have arrived.
 
-size_t tf32x3_plane_bytes(int M, int N, int K) {
+// slots_for_sms > 0 also reserves room for partial tiles, so that a whole product multiplied
+// through tf32x3_multiply_rows can balance its tiles over that many SMs
+size_t tf32x3_plane_bytes(int M, int N, int K, int slots_for_sms) {
     const size_t Kp = (size_t) padded_k(K);
-    return 2 * align_up((size_t) M * Kp * 4, 1024) + 2 * align_up((size_t) N * Kp * 4, 1024) + 2048;
+    return 2 * align_up((size_t) M * Kp * 4, 1024) + 2 * align_up((size_t) N * Kp * 4, 1024) + 2048 +
+           (slots_for_sms > 0 ? partial_slot_bytes(slots_for_sms) : 0);
 }
 
-int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out) {
-    if (tf32x3_plane_bytes(M, N, K) > scratch_bytes) {
+int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32x3Planes* out, int slots_for_sms) {
+    if (tf32x3_plane_bytes(M, N, K, slots_for_sms) > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small for the operand planes");
         return CAKEB200_ERR_ARG;
     }
@@ -673,6 +895,8 @@ int tf32x3_planes(int M, int N, int K, void* scratch, size_t scratch_bytes, Tf32
     out->a_lo = (float*) (base + a_bytes);
     out->b_hi = (float*) (base + 2 * a_bytes);
     out->b_lo = (float*) (base + 2 * a_bytes + b_bytes);
+    out->partials = slots_for_sms > 0 ? (float*) (base + 2 * a_bytes + 2 * b_bytes) : nullptr;
+    out->M = M;
     out->Kp = Kp;
     return CAKEB200_OK;
 }
@@ -722,18 +946,21 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     g.out_image_stride = out_image_stride;
     float* a_hi = p.a_hi + (size_t) r0 * p.Kp;
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
-    return (N > 128) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, nullptr, 1, status_word, sm_count, stream)
-                     : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, nullptr, 1, status_word, sm_count, stream);
+    DevicePlan* plan = nullptr;
+    if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
+        const int bn = tile_width(N);
+        int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, stream, &plan);
+        if (rc) return rc;
+    }
+    return (N > 128) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr)
+                     : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr);
 }
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + split-K partials (worst case)
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     const size_t Kp = (size_t) padded_k(K);
     const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
-    int bn, splits;
-    plan_tiles(M, N, K, sm_count, &bn, &splits);
-    const size_t part = splits > 1 ? align_up((size_t) splits * M * N * 4, 1024) : 0;
-    return 2 * a + 2 * b + part + 2048;
+    return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
 }
 
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word, int sm_count,
@@ -751,9 +978,8 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* b_lo = (float*) (base + 2 * a_bytes + b_bytes);
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
-    int bn, splits;
-    plan_tiles(g.M, g.N, g.K, sm_count, &bn, &splits);
-    const size_t need = 2 * a_bytes + 2 * b_bytes + (splits > 1 ? (size_t) splits * g.M * g.N * 4 : 0) + 1024;
+    const int bn = tile_width(g.N);
+    const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
         return CAKEB200_ERR_ARG;
@@ -765,17 +991,13 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     if ((rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream))) return rc;
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
-    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream)
-                         : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, splits, status_word, sm_count, stream);
+    DevicePlan* plan = nullptr;
+    if ((rc = get_plan((g.M + BM - 1) / BM, (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order, sm_count, bn, stream, &plan)))
+        return rc;
+    int launches = 2;
+    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches)
+                     : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches);
     if (rc) return rc;
-    int launches = 3;
-    if (splits > 1) {
-        const long long total = (long long) g.M * g.N;
-        const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) sm_count * 16);
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partials, (long long) g.M * g.N, splits, g.C, g.M, g.N, g.ldc, g.accumulate);
-        CAKE_CUDA_OK(cudaGetLastError());
-        launches++;
-    }
     if (stats) {
         stats->launches += launches;
         stats->tile_m = BM; stats->tile_n = bn; stats->tile_k = BK;
@@ -898,8 +1120,8 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
     // one K range per tile: split-K would need partial planes, i.e. more scratch
-    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, 1, status_word, sm_count, s)
-                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, 1, status_word, sm_count, s);
+    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr)
+                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr);
     if (rc) return rc;
     int word[4] = {0, 0, 0, 0};
     CAKE_CUDA_OK(cudaMemcpyAsync(word, status_word, sizeof(word), cudaMemcpyDeviceToHost, s));
