@@ -80,6 +80,7 @@ for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
 
 _SIGNATURES["cakeb200_profile_begin"] = (_i, [])
 _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i)])
+_SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
 EXPORTED_SYMBOLS = sorted(_SIGNATURES)
@@ -178,6 +179,42 @@ def cake_sgemm(A, B, C=None, p=1, cake_cntx=None, packedA=False, packedB=False, 
         # the schedule decides whether beta is honoured; resolve it the way the library will
         accumulate = 1 if last_schedule_for(M, N, K) != KMN else 0
     _check(lib().cakeb200_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, accumulate, sch, kernel, _stream_of(C, stream)))
+    return C
+
+
+def cake_sgemm_ex(A, B, C=None, trans_a=False, trans_b=False, bias=None, accumulate=False, sch=NA,
+                  kernel=KERNEL_AUTO, stream=None):
+    """C (+)= op(A) @ op(B) (+ bias) on CUDA tensors, enqueued on the current stream.
+
+    ``A`` and ``B`` are 2-D float32 tensors whose rows are contiguous (a row
+    stride is allowed, so column slices work); ``trans_a`` / ``trans_b`` multiply
+    the transpose of the tensor as stored.  ``bias`` has one entry per column of
+    C and is added in the kernel's epilogue.  This is the product behind the
+    linear layer (reference src/linear.cpp:12-102) without its transposed copies.
+    """
+    import torch
+    for t in (A, B) + ((C,) if C is not None else ()) + ((bias,) if bias is not None else ()):
+        if not (_is_torch(t) and t.is_cuda and t.dtype == torch.float32):
+            raise TypeError("cake_sgemm_ex needs float32 CUDA tensors")
+    for t in (A, B) + ((C,) if C is not None else ()):
+        if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1) or (t.shape[0] > 1 and t.stride(0) < t.shape[1]):
+            raise TypeError("operands must be 2-D with contiguous rows")
+    M, K = (A.shape[1], A.shape[0]) if trans_a else A.shape
+    K2, N = (B.shape[1], B.shape[0]) if trans_b else B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if C is None:
+        C = torch.empty((M, N), dtype=torch.float32, device=A.device)
+        accumulate = False
+    if tuple(C.shape) != (M, N):
+        raise ValueError("C has the wrong shape")
+    if bias is not None and (bias.dim() != 1 or bias.shape[0] != N or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous vector with one entry per column of C")
+    ld = lambda t: t.stride(0) if t.shape[0] > 1 else t.shape[1]
+    _check(lib().cakeb200_sgemm_ex(ctypes.c_void_p(A.data_ptr()), ld(A), int(trans_a), ctypes.c_void_p(B.data_ptr()), ld(B),
+                                   int(trans_b), ctypes.c_void_p(C.data_ptr()), ld(C), M, N, K,
+                                   ctypes.c_void_p(bias.data_ptr()) if bias is not None else None,
+                                   int(bool(accumulate)), sch, kernel, _stream_of(C, stream)))
     return C
 
 

@@ -4,7 +4,10 @@ Mirrors the reference's PyTorch binding: the autograd function and module of
 python/cake.py:18-49 and the three products of src/linear.cpp (forward
 y = x W^T + b at :12-49; backward dX = dY W and dW = dY^T X at :52-102), each
 product being one cake_sgemm call.  Tensors stay on the GPU: the library is
-handed device pointers.
+handed device pointers, transposed operands are read where they lie (the weight
+of the forward product and dY of the weight gradient; the reference makes
+contiguous transposed copies at src/linear.cpp:22 and :76-80) and the bias is
+added in the product's epilogue instead of a second pass (:44-46).
 """
 import torch
 from torch import nn
@@ -13,27 +16,24 @@ from torch.nn import Parameter
 from . import api
 
 
-def _sgemm(a, b):
-    a, b = a.contiguous(), b.contiguous()
-    out = torch.empty((a.shape[0], b.shape[1]), dtype=torch.float32, device=a.device)
-    return api.cake_sgemm(a, b, out)
+def _rows(t):
+    """A 2-D view whose rows are contiguous (copies only if they are not)."""
+    return t if t.stride(-1) == 1 or t.shape[-1] == 1 else t.contiguous()
 
 
 def linear_forward(input, weight, bias=None):
     """y = input @ weight.T (+ bias), as linear_forward in src/linear.cpp:12-49."""
-    x = input.reshape(-1, input.shape[-1])
-    out = _sgemm(x, weight.t())
-    if bias is not None:
-        out.add_(bias)
+    x = _rows(input.reshape(-1, input.shape[-1]))
+    out = api.cake_sgemm_ex(x, _rows(weight), trans_b=True, bias=None if bias is None else bias.contiguous())
     return out.reshape(*input.shape[:-1], weight.shape[0])
 
 
 def linear_backward(grad_output, input, weight, bias=None):
     """(grad_input, grad_weight, grad_bias), as linear_backward in src/linear.cpp:52-102."""
-    dy = grad_output.reshape(-1, grad_output.shape[-1])
-    x = input.reshape(-1, input.shape[-1])
-    grad_input = _sgemm(dy, weight).reshape(input.shape)
-    grad_weight = _sgemm(dy.t(), x)
+    dy = _rows(grad_output.reshape(-1, grad_output.shape[-1]))
+    x = _rows(input.reshape(-1, input.shape[-1]))
+    grad_input = api.cake_sgemm_ex(dy, _rows(weight)).reshape(input.shape)
+    grad_weight = api.cake_sgemm_ex(dy, x, trans_a=True)
     grad_bias = dy.sum(0) if bias is not None else None
     return grad_input, grad_weight, grad_bias
 

@@ -401,6 +401,63 @@ int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, in
     return CAKEB200_OK;
 }
 
+// C = op(A) op(B) (+ bias) on device operands with leading dimensions, asynchronous on `stream`.
+int sgemm_ex_impl(const float* A, int lda, int trans_a, const float* B, int ldb, int trans_b, float* C, int ldc, int M,
+                  int N, int K, const float* bias, int accumulate, int sched, int kernel, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!A || !B || !C) {
+        set_error("null matrix pointer");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    if (sched < 0 || sched > CAKEB200_SCHED_NA) {
+        set_error("unknown schedule %d", sched);
+        return CAKEB200_ERR_ARG;
+    }
+    if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N) || ldc < N) {
+        set_error("leading dimension smaller than the row length (lda=%d ldb=%d ldc=%d)", lda, ldb, ldc);
+        return CAKEB200_ERR_ARG;
+    }
+    if (!on_device(A) || !on_device(B) || !on_device(C) || (bias && !on_device(bias))) {
+        set_error("cakeb200_sgemm_ex needs device pointers");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = (cudaStream_t) stream;
+
+    GemmProblem g = {};
+    g.A = A; g.B = B; g.C = C;
+    g.M = M; g.N = N; g.K = K;
+    g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.batch = 1;
+    g.accumulate = accumulate ? 1 : 0;
+    g.order = resolve_schedule(st, M, N, K, sched);
+    g.trans_a = trans_a ? 1 : 0;
+    g.trans_b = trans_b ? 1 : 0;
+    g.bias = bias;
+    g_stats.sched = g.order;
+    if (resolve_kernel(kernel, M, N, K, 1) == CAKEB200_KERNEL_FFMA && (g.trans_a || g.trans_b)) {
+        // the FFMA kernel reads row-major A and B: lay a transposed operand out that way first
+        const size_t a_bytes = g.trans_a ? ((size_t) M * K * 4 + 255) / 256 * 256 : 0;
+        const size_t b_bytes = g.trans_b ? (size_t) K * N * 4 : 0;
+        int rc = ensure_scratch(st, a_bytes + b_bytes);
+        if (rc) return rc;
+        if (g.trans_a) {
+            if ((rc = launch_transpose_copy(A, (float*) st->scratch, K, M, lda, s))) return rc;
+            g.A = (const float*) st->scratch; g.lda = K; g.trans_a = 0;
+            g_stats.launches += 1;
+        }
+        if (g.trans_b) {
+            float* bt = (float*) ((char*) st->scratch + a_bytes);
+            if ((rc = launch_transpose_copy(B, bt, N, K, ldb, s))) return rc;
+            g.B = bt; g.ldb = N; g.trans_b = 0;
+            g_stats.launches += 1;
+        }
+    }
+    return run_dense(st, g, kernel, s, false);
+}
+
 typedef int (*pack_fn)(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
 
 // mat: rows x cols matrix, packed: packed buffer of packed_bytes; unpack moves packed -> mat.
@@ -496,6 +553,11 @@ int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K
 int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
                          int kernel, void* stream) {
     return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, false);
+}
+
+int cakeb200_sgemm_ex(const float* A, int lda, int trans_a, const float* B, int ldb, int trans_b, float* C, int ldc, int M,
+                      int N, int K, const float* bias, int accumulate, int sched, int kernel, void* stream) {
+    return sgemm_ex_impl(A, lda, trans_a, B, ldb, trans_b, C, ldc, M, N, K, bias, accumulate, sched, kernel, stream);
 }
 
 int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K, int batch, int kernel,

@@ -34,10 +34,15 @@ struct GemmProblem {
     int batch;
     int accumulate;  // 0: C = A*B, 1: C += A*B (the reference's beta != 0 behaviour)
     int order;       // tile rasterisation: CAKEB200_SCHED_*
+    int band;        // tile rows (columns for N-first) per band of the rasterisation; 0 = the kernel's default
     // 3xTF32 path only: when out_p > 0 the N axis is (image, position) with out_p positions per image and
     // element (m, n) is stored at C[(n / out_p) * out_image_stride + m * out_p + n % out_p] (NCHW convolution output)
     int out_p;
     long long out_image_stride;
+    // operands stored transposed: trans_a -> A points at a K x M row-major matrix (lda >= M),
+    // trans_b -> B points at an N x K row-major matrix (ldb >= K); the product is op(A) * op(B)
+    int trans_a, trans_b;
+    const float* bias;  // length N, added to every row of the result (nullptr: none)
 };
 
 // Per-device state: scratch arena that grows on demand and is reused between calls.
@@ -65,7 +70,8 @@ DeviceState* device_state();  // state of the current device (created on first u
 int ensure_scratch(DeviceState* st, size_t bytes);
 
 // exact-FP32 FFMA path (sgemm_ffma.cu)
-int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);
+int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);  // untransposed operands only
+int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream);
 // 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
 // row-band interface of the 3xTF32 path (operand planes laid out once, rows multiplied band by band)
@@ -89,29 +95,36 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 
 
 #ifdef __CUDACC__
-// Linear tile index -> tile coordinates.  The order in which CTAs take tiles is
-// what remains of the reference's block schedules on a GPU:
-//   M-first (MKN): walk down a column of tiles, so one B panel stays hot;
-//   N-first (NKM): walk along a row of tiles, so one A panel stays hot;
-//   K-first (KMN): K runs innermost inside every tile; tiles are taken in bands
-//                  of 8 tile-rows that snake left-right, the analogue of the
-//                  snaking CB-block traversal of src/cake_sgemm_k_first.cpp:28-71.
-__device__ __forceinline__ void tile_coords(int id, int tiles_m, int tiles_n, int order, int& tm, int& tn) {
-    if (order == CAKEB200_SCHED_MKN) {
-        tm = id % tiles_m;
-        tn = id / tiles_m;
-    } else if (order == CAKEB200_SCHED_NKM) {
-        tn = id % tiles_n;
-        tm = id / tiles_n;
+// Linear tile index -> tile coordinates.  K always runs innermost inside a tile (the
+// accumulator stays in place), so what remains of the reference's block schedules on a
+// GPU is the order in which tiles are taken.  As in the reference, the name gives the
+// loop nest from the outside in:
+//   M-first (MKN) and K-first (KMN): M outermost.  Bands of `band` tile rows, each walked
+//       column by column; the direction alternates from band to band, the analogue of the
+//       snaking CB-block traversal of src/cake_sgemm_k_first.cpp:28-71 and
+//       src/cake_sgemm_m_first.cpp:26-60.
+//   N-first (NKM): N outermost.  Bands of `band` tile columns, each walked row by row
+//       (src/cake_sgemm_n_first.cpp:26-60).
+// Tiles that run at the same time (consecutive ids) therefore cover a compact
+// band x (SMs / band) patch of C and share their A and B panels through L2.
+__host__ __device__ __forceinline__ void tile_coords(int id, int tiles_m, int tiles_n, int order, int band, int& tm,
+                                                     int& tn) {
+    if (order == CAKEB200_SCHED_NKM) {
+        const int per = band * tiles_m;
+        const int b = id / per, first = b * band;
+        const int cols = (band < tiles_n - first) ? band : tiles_n - first;
+        const int in_band = id - b * per;
+        tn = first + in_band % cols;
+        tm = in_band / cols;
+        if (b & 1) tm = tiles_m - 1 - tm;
     } else {
-        constexpr int G = 8;
-        const int band = id / (G * tiles_n);
-        const int first = band * G;
-        const int rows = min(G, tiles_m - first);
-        const int in_band = id - band * G * tiles_n;
+        const int per = band * tiles_n;
+        const int b = id / per, first = b * band;
+        const int rows = (band < tiles_m - first) ? band : tiles_m - first;
+        const int in_band = id - b * per;
         tm = first + in_band % rows;
         tn = in_band / rows;
-        if (band & 1) tn = tiles_n - 1 - tn;
+        if (b & 1) tn = tiles_n - 1 - tn;
     }
 }
 #endif

@@ -27,7 +27,7 @@ sgemm_ffma_kernel(GemmProblem g, int tiles_m, int tiles_n) {
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     int tm, tn;
-    tile_coords(blockIdx.x, tiles_m, tiles_n, g.order, tm, tn);
+    tile_coords(blockIdx.x, tiles_m, tiles_n, g.order, g.band > 0 ? g.band : 8, tm, tn);
     const int m0 = tm * BM, n0 = tn * BN;
     const float* __restrict__ A = g.A + (long long) blockIdx.z * g.stride_a;
     const float* __restrict__ B = g.B + (long long) blockIdx.z * g.stride_b;
@@ -161,6 +161,10 @@ sgemm_ffma_kernel(GemmProblem g, int tiles_m, int tiles_n) {
                 if constexpr (VEC) {
                     if (col < N) {
                         float4 v = make_float4(a4[0], a4[1], a4[2], a4[3]);
+                        if (g.bias) {
+                            const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col));
+                            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                        }
                         if (g.accumulate) {
                             float4 o = *reinterpret_cast<const float4*>(crow + col);
                             v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -170,7 +174,10 @@ sgemm_ffma_kernel(GemmProblem g, int tiles_m, int tiles_n) {
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; j++)
-                        if (col + j < N) crow[col + j] = g.accumulate ? crow[col + j] + a4[j] : a4[j];
+                        if (col + j < N) {
+                            const float v = g.bias ? a4[j] + __ldg(g.bias + col + j) : a4[j];
+                            crow[col + j] = g.accumulate ? crow[col + j] + v : v;
+                        }
                 }
             }
         }
@@ -187,7 +194,9 @@ int launch_cfg(const GemmProblem& g, cudaStream_t stream) {
     dim3 grid((unsigned) tiles, 1, (unsigned) g.batch), block((BM / TM) * (BN / TN));
     const bool vec = (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (g.ldc % 4 == 0) && (g.stride_a % 4 == 0) &&
                      (g.stride_b % 4 == 0) && (g.stride_c % 4 == 0) &&
-                     (((uintptr_t) g.A | (uintptr_t) g.B | (uintptr_t) g.C) % 16 == 0);
+                     (((uintptr_t) g.A | (uintptr_t) g.B | (uintptr_t) g.C | (uintptr_t) g.bias) % 16 == 0) &&
+                     // a float4 never straddles the edge of the matrix (views inside a wider allocation)
+                     (g.K % 4 == 0) && (g.N % 4 == 0);
     if (vec)
         sgemm_ffma_kernel<BM, BN, BK, TM, TN, true><<<grid, block, 0, stream>>>(g, tiles_m, tiles_n);
     else
@@ -196,7 +205,32 @@ int launch_cfg(const GemmProblem& g, cudaStream_t stream) {
     return CAKEB200_OK;
 }
 
+// dst[c][r] = src[r][c] for a rows x cols row-major matrix (leading dimension ld_src); dst is cols x rows, dense
+__global__ void __launch_bounds__(256)
+transpose_copy_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols, int ld_src) {
+    __shared__ float tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int i = ty; i < 32; i += 8)
+        if (r0 + i < rows && c0 + tx < cols) tile[i][tx] = src[(long long) (r0 + i) * ld_src + c0 + tx];
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+        if (c0 + i < cols && r0 + tx < rows) dst[(long long) (c0 + i) * rows + r0 + tx] = tile[tx][i];
+}
+
 }  // namespace
+
+int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return CAKEB200_OK;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+    if (grid.y > 65535) {
+        set_error("transpose: too many rows (%d)", rows);
+        return CAKEB200_ERR_TOO_LARGE;
+    }
+    transpose_copy_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src);
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
 
 // Tile shape selection (the GPU analogue of get_cache_dims picking m_c / n_c,
 // src/block_sizing.cpp:304-429): big tiles when the grid still fills the SMs.

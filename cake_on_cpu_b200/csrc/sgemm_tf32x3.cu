@@ -28,6 +28,7 @@
 // own loads in flight, frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <stdlib.h>
 #include <mutex>
 #include <vector>
 
@@ -49,7 +50,8 @@ struct Cfg {
     static constexpr int B_BYTES = BN * BK * 4;   // one plane of B per stage
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;  // one 32 x 32 patch per epilogue warp
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -142,6 +144,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
+    float4 o;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(addr) : "memory");
+    return o;
+}
 
 // Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes
 // and 128-byte swizzled: 8-row groups are 1024 bytes apart (stride byte offset),
@@ -177,10 +187,11 @@ struct Tf32x3Args {
     int ldc;
     int tiles_m, tiles_n;
     int kblocks;             // ceil(K / BK)
-    int order;
+    int order, band;         // tile walk, see tile_coords
     int accumulate;          // for tiles stored straight to C
     int out_p;               // > 0: N axis is (image, position), see GemmProblem::out_p
     long long out_image_stride;
+    const float* bias;       // length N, added to every row (nullptr: none)
     int* status_word;
 };
 
@@ -261,7 +272,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             bool ok = true;
             for (int it = 0; ok && work_piece(args, it, w); it++) {
                 int tm, tn;
-                tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
+                tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
                 for (int kb = w.kb0; kb < w.kb1; kb++) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
                     if (!ok) break;
@@ -329,83 +340,112 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         }
     } else {
         // ----------------------------------------------------------- epilogue
+        // tcgen05.ld hands each thread one row of the accumulator (32 columns per load), so
+        // storing from those registers would touch 32 different rows per instruction.  Every
+        // 32 x 32 chunk therefore goes through a swizzled shared-memory patch of the warp and
+        // comes back with eight lanes per row: a store instruction then covers 4 rows x 128
+        // contiguous bytes.
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) quarter * 4096u;
+        const int sub_r = lane >> 3, sub_c = lane & 7;
+        const bool c_vec = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
+        const bool p_vec = (args.out_p % 4 == 0) && (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
         int local = 0;
         bool ok = true;
         for (; ok && work_piece(args, local, w); local++) {
             int tm, tn;
-            tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, tm, tn);
-            const int kb0 = w.kb0, kb1 = w.kb1;
+            tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
             ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
             if (!ok) break;
             tcgen05_fence_after();
-            const int row = tm * BM + quarter * 32 + lane;
-            float* crow = args.C + (long long) row * args.ldc;
-            const bool vec_ok = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
-            const bool empty_range = kb0 >= kb1;  // a piece with no K range contributes zeros
+            const bool empty_range = w.kb0 >= w.kb1;  // a piece with no K range contributes zeros
+            const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
+            const int row0 = tm * BM + quarter * 32;
             // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
             // beyond the matrix are zeros computed from zero-filled operand tiles)
-            float* slot_row = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32 + lane) * BN : nullptr;
+            float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN : nullptr;
+            float v[32];
+            if (!empty_range) {
+                tmem_ld32(t_addr, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] = 0.0f;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
-                float v[32];
+                if (!empty_range) tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                                 v[4 * j + 2], v[4 * j + 3]);
+                __syncwarp();
                 if (!empty_range) {
-                    tmem_ld32(tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN + c * 32), v);
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = 0.0f;
+                    if (c + 1 < BN / 32) {
+                        tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);  // lands while this chunk is stored
+                    } else {
+                        // the accumulator has been read out: hand the buffer back before the stores
+                        tcgen05_fence_before();
+                        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                    }
                 }
-                const int col0 = tn * BN + c * 32;
-                if (slot_row != nullptr) {
+                const int col = tn * BN + c * 32 + sub_c * 4;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(slot_row + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                } else if (args.out_p > 0) {
-                    // convolution output: columns are (image, position); rows are output channels
-                    if (row < args.M && col0 < args.N) {
-                        const int img = col0 / args.out_p, pos = col0 - img * args.out_p;
-                        float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
-                        if (pos + 32 <= args.out_p && col0 + 32 <= args.N && (args.out_p % 4 == 0) &&
-                            (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0)) {
+                for (int i = 0; i < 8; i++) {
+                    const int r = i * 4 + sub_r;
+                    float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
+                    const int row = row0 + r;
+                    if (args.bias != nullptr && slot == nullptr) {
+                        if (col < args.N) o.x += __ldg(args.bias + col);
+                        if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
+                        if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
+                        if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
+                    }
+                    if (slot != nullptr) {
+                        *reinterpret_cast<float4*>(slot + (long long) r * BN + c * 32 + sub_c * 4) = o;
+                    } else if (row < args.M && col < args.N) {
+                        if (args.out_p > 0) {
+                            // convolution output: columns are (image, position); rows are output channels
+                            const int img = col / args.out_p, pos = col - img * args.out_p;
+                            float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
+                            if (p_vec && pos + 4 <= args.out_p && col + 4 <= args.N) {
+                                *reinterpret_cast<float4*>(dst) = o;
+                            } else {
+                                const float e[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int col = col0 + j;
-                                if (col < args.N) {
-                                    const int im = col / args.out_p, ps = col - im * args.out_p;
-                                    args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = v[j];
+                                for (int j = 0; j < 4; j++) {
+                                    const int cj = col + j;
+                                    if (cj < args.N) {
+                                        const int im = cj / args.out_p, ps = cj - im * args.out_p;
+                                        args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = e[j];
+                                    }
                                 }
                             }
-                        }
-                    }
-                } else if (row < args.M && col0 < args.N) {
-                    if (vec_ok && col0 + 32 <= args.N) {
+                        } else {
+                            float* dst = args.C + (long long) row * args.ldc + col;
+                            if (c_vec && col + 4 <= args.N) {
+                                if (args.accumulate) {
+                                    const float4 old = *reinterpret_cast<const float4*>(dst);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *reinterpret_cast<float4*>(dst) = o;
+                            } else {
+                                const float e[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            if (args.accumulate) {
-                                const float4 old = *reinterpret_cast<const float4*>(crow + col0 + j);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                for (int j = 0; j < 4; j++)
+                                    if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
                             }
-                            *reinterpret_cast<float4*>(crow + col0 + j) = o;
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (col0 + j < args.N) crow[col0 + j] = args.accumulate ? crow[col0 + j] + v[j] : v[j];
                     }
                 }
+                __syncwarp();  // the patch is rewritten by the next chunk
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            if (empty_range) {
+                tcgen05_fence_before();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            }
         }
     }
 
@@ -549,7 +589,7 @@ struct TilePieces {
 template <int BN>
 __global__ void __launch_bounds__(256)
 reduce_pieces_kernel(const float* __restrict__ partials, const TilePieces* __restrict__ tiles, float* __restrict__ C, int M,
-                     int N, int ldc, int accumulate, int out_p, long long out_image_stride) {
+                     int N, int ldc, int accumulate, int out_p, long long out_image_stride, const float* __restrict__ bias) {
     const TilePieces t = tiles[blockIdx.x];
     const float* base = partials + (long long) t.first_slot * (BM * BN);
     // gridDim.y CTAs share a tile, each taking a band of its rows
@@ -574,7 +614,8 @@ reduce_pieces_kernel(const float* __restrict__ partials, const TilePieces* __res
             } else {
                 at = (long long) row * ldc + col + j;
             }
-            C[at] = accumulate ? C[at] + e[j] : e[j];
+            const float v = bias ? e[j] + __ldg(bias + col + j) : e[j];
+            C[at] = accumulate ? C[at] + v : v;
         }
     }
 }
@@ -626,19 +667,19 @@ inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be
 
 inline int tile_width(int N) { return (N > 128) ? 256 : 128; }
 
-// host copy of tile_coords (common.cuh)
-void host_tile_coords(int id, int tiles_m, int tiles_n, int order, int& tm, int& tn) {
-    if (order == CAKEB200_SCHED_MKN) {
-        tm = id % tiles_m; tn = id / tiles_m;
-    } else if (order == CAKEB200_SCHED_NKM) {
-        tn = id % tiles_n; tm = id / tiles_n;
-    } else {
-        const int G = 8, band = id / (G * tiles_n), first = band * G;
-        const int rows = std::min(G, tiles_m - first), in_band = id - band * G * tiles_n;
-        tm = first + in_band % rows;
-        tn = in_band / rows;
-        if (band & 1) tn = tiles_n - 1 - tn;
-    }
+// Band height of the tile walk.  Tiles that run together should cover a patch of C with
+// few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
+// the tall and the wide benchmark shapes alike (12 and 16 were equal on squares and up
+// to 20 % slower on the 65536 x 1024 x 1024 and 1024 x 1024 x 65536 products).
+// CAKEB200_BAND overrides it for experiments.
+int band_for(int order, int tiles_m, int tiles_n, int bn, int sm_count) {
+    (void) bn; (void) sm_count;
+    static const int forced = [] {
+        const char* e = getenv("CAKEB200_BAND");
+        return e ? atoi(e) : 0;
+    }();
+    const int band = forced > 0 ? forced : 8;
+    return std::max(1, std::min(band, order == CAKEB200_SCHED_NKM ? tiles_n : tiles_m));
 }
 
 // How the tiles of one product are spread over the persistent CTAs.  Whole waves of
@@ -655,8 +696,9 @@ struct HostPlan {
     std::vector<TilePieces> pieces;
 };
 
-HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count) {
+HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn) {
     HostPlan p;
+    const int band = band_for(order, tiles_m, tiles_n, bn, sm_count);
     const long long T = (long long) tiles_m * tiles_n;
     const int G = (int) std::min<long long>(T, sm_count);
     p.grid = G;
@@ -701,7 +743,7 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     p.cta_begin[p.grid] = (int) p.units.size();
     for (int r = 0; r < R; r++) {
         int tm, tn;
-        host_tile_coords(p.dp_tiles + r, tiles_m, tiles_n, order, tm, tn);
+        tile_coords(p.dp_tiles + r, tiles_m, tiles_n, order, band, tm, tn);
         p.pieces.push_back({tm, tn, r * s, s});
     }
     return p;
@@ -751,7 +793,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
         if (!slots[i].valid) { victim = &slots[i]; break; }
         if (slots[i].stamp < victim->stamp) victim = &slots[i];
     }
-    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count);
+    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, bn);
     const size_t units_b = align_up(hp.units.size() * sizeof(int4) + 16, 256);
     const size_t begin_b = align_up(hp.cta_begin.size() * sizeof(int), 256);
     const size_t pieces_b = align_up(hp.pieces.size() * sizeof(TilePieces) + 16, 256);
@@ -810,9 +852,11 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.order = g.order;
+    a.band = band_for(g.order, a.tiles_m, a.tiles_n, BN, sm_count);
     a.accumulate = g.accumulate;
     a.out_p = g.out_p;
     a.out_image_stride = g.out_image_stride;
+    a.bias = g.bias;
     a.status_word = status_word;
     const long long tiles = (long long) a.tiles_m * a.tiles_n;
     if (tiles > 0x7fffffffLL) {
@@ -833,7 +877,7 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     if (launches) (*launches)++;
     if (a.units && plan->num_pieces > 0) {
         reduce_pieces_kernel<BN><<<dim3(plan->num_pieces, 16), 256, 0, stream>>>(partials, plan->pieces, g.C, g.M, g.N, g.ldc, g.accumulate,
-                                                                      g.out_p, g.out_image_stride);
+                                                                      g.out_p, g.out_image_stride, g.bias);
         CAKE_CUDA_OK(cudaGetLastError());
         if (launches) (*launches)++;
     }
@@ -987,8 +1031,15 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[0], stream));
     int rc;
-    if ((rc = run_split_rows(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp, sm_count, stream))) return rc;
-    if ((rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream))) return rc;
+    // both operand planes are K-major; an operand already stored that way (A as given, B
+    // transposed, e.g. the N x K weight of a linear layer) is split in place, the other
+    // kind is transposed through shared memory on the way
+    if (g.trans_a) rc = run_split_transpose(g.A, a_hi, a_lo, g.K, g.M, g.lda, Kp, stream);
+    else rc = run_split_rows(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp, sm_count, stream);
+    if (rc) return rc;
+    if (g.trans_b) rc = run_split_rows(g.B, b_hi, b_lo, g.N, g.K, g.ldb, Kp, sm_count, stream);
+    else rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream);
+    if (rc) return rc;
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
     DevicePlan* plan = nullptr;

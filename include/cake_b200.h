@@ -105,6 +105,20 @@ int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K
 int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K,
                          int accumulate, int sched, int kernel, void* stream);
 
+/* C[M x N] (+)= op(A) * op(B) (+ bias) on device operands, enqueued on `stream`.
+ * trans_a = 0: A is M x K row-major with leading dimension lda; 1: A points at a
+ * K x M row-major matrix (lda >= M) and its transpose is multiplied.  trans_b
+ * likewise (0: K x N, ldb >= N; 1: N x K, ldb >= K).  `bias` (length N, or NULL)
+ * is added to every row in the kernel's epilogue.  This is the product the
+ * reference's PyTorch layer needs without its copies: forward y = x W^T + b with
+ * the weight used where it lies (replaces weight.t().contiguous(), the cake_sgemm
+ * call and the scalar bias loop of reference src/linear.cpp:22-46), and
+ * dW = dY^T X with dY used where it lies (replaces the transposed copy at
+ * reference src/linear.cpp:76-84). */
+int cakeb200_sgemm_ex(const float* A, int lda, int trans_a, const float* B, int ldb, int trans_b,
+                      float* C, int ldc, int M, int N, int K, const float* bias,
+                      int accumulate, int sched, int kernel, void* stream);
+
 /* Device-side timing of cakeb200_sgemm_async without synchronising: between
  * _begin and _end every asynchronous product (up to 256) records CUDA events on
  * its stream before the operand-split pass, after it and after the contraction

@@ -70,6 +70,42 @@ def test_auto_kernel_and_device_pointers(cake, oracle):
     assert cake.last_stats()["kernel"] == cake.KERNEL_FFMA
 
 
+@pytest.mark.parametrize("kernel_name", ["ffma", "tf32x3"])
+def test_transposed_operands_leading_dimensions_and_bias(cake, oracle, kernel_name):
+    """cakeb200_sgemm_ex: op(A) op(B) + bias must equal the oracle's product of the
+    explicitly transposed, densely copied operands (what reference src/linear.cpp:22,76-84
+    feeds cake_sgemm) plus the bias added afterwards (:44-46)."""
+    import torch
+    kernel = {"ffma": cake.KERNEL_FFMA, "tf32x3": cake.KERNEL_TF32X3}[kernel_name]
+    for (M, K, N) in [(300, 515, 260), (129, 96, 1031), (1000, 2111, 257)]:
+        A, B = _inputs(oracle, M, K, N)
+        bias = oracle.uniform((1, N), 7)[0]
+        ref, _ = oracle.sgemm(A, B, 8, NA)
+        dbias = torch.from_numpy(bias).cuda()
+        # operands live inside wider allocations, so every leading dimension differs from the row length
+        wide = lambda X: torch.from_numpy(np.pad(X, ((0, 0), (3, 5)))).cuda()[:, 3:3 + X.shape[1]]
+        for ta in (False, True):
+            for tb in (False, True):
+                dA = wide(np.ascontiguousarray(A.T)) if ta else wide(A)
+                dB = wide(np.ascontiguousarray(B.T)) if tb else wide(B)
+                Cw = torch.full((M, N + 8), float("nan"), device="cuda")
+                dC = Cw[:, 4:4 + N]
+                cake.cake_sgemm_ex(dA, dB, dC, trans_a=ta, trans_b=tb, bias=dbias, kernel=kernel)
+                assert cake.last_stats()["kernel"] == kernel
+                got = dC.cpu().numpy()
+                assert rel_err(got - bias[None, :], ref, A, B) <= TOL, (kernel_name, M, K, N, ta, tb)
+                assert torch.isnan(Cw[:, :4]).all() and torch.isnan(Cw[:, 4 + N:]).all()  # nothing outside the view
+                # accumulate on top of the previous result: C += A B + bias
+                cake.cake_sgemm_ex(dA, dB, dC, trans_a=ta, trans_b=tb, bias=dbias, accumulate=True, kernel=kernel)
+                assert rel_err((dC.cpu().numpy() - 2 * bias[None, :]) / 2, ref, A, B) <= TOL
+    # a leading dimension shorter than a row is an argument error, not a launch
+    import ctypes
+    x = torch.zeros((64, 64), device="cuda")
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = cake.lib().cakeb200_sgemm_ex(vp(x), 32, 0, vp(x), 64, 0, vp(x), 64, 64, 64, 64, None, 0, NA, kernel, None)
+    assert rc != 0 and b"leading dimension" in cake.lib().cakeb200_last_error()
+
+
 def test_beta_flag_matches_reference_semantics(cake, oracle):
     M, K, N = 300, 200, 260
     A, B = _inputs(oracle, M, K, N)
