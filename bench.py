@@ -163,7 +163,7 @@ def gpu_arm(args):
     import torch
     import cake_on_cpu_b200 as cake
     from cake_on_cpu_b200 import build
-    from cake_on_cpu_b200.partition import row_block
+    from cake_on_cpu_b200.partition import grid_block, grid_shape
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -181,18 +181,20 @@ def gpu_arm(args):
 
     size = args.size
     M = K = N = size
-    r0, r1 = row_block(M, world, rank)
-    rows = r1 - r0
+    # rank (i, j) of a pr x pc grid owns C[r0:r1, c0:c1]; nothing is exchanged (pc = 1: plain row blocks, B replicated)
+    pr, pc = grid_shape(M, N, K, world)
+    r0, r1, c0, c1 = grid_block(M, N, K, world, rank)
+    rows, cols = r1 - r0, c1 - c0
     kernel = cake.KERNEL_TF32X3 if args.kernel == "tf32x3" else cake.KERNEL_FFMA
 
     g = torch.Generator(device="cuda").manual_seed(1234)
     A = (torch.rand((M, K), device="cuda", generator=g) * 2 - 1)[r0:r1].contiguous()
-    B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
-    C = torch.empty((rows, N), device="cuda")
+    B = (torch.rand((K, N), device="cuda", generator=g) * 2 - 1)[:, c0:c1].contiguous()
+    C = torch.empty((rows, cols), device="cuda")
     stream = torch.cuda.current_stream()
 
     def step():
-        cake.cake_sgemm_async(A.data_ptr(), B.data_ptr(), C.data_ptr(), rows, N, K, 0, cake.NA, kernel, stream.cuda_stream)
+        cake.cake_sgemm_async(A.data_ptr(), B.data_ptr(), C.data_ptr(), rows, cols, K, 0, cake.NA, kernel, stream.cuda_stream)
 
     def barrier():
         if dist is not None:
@@ -236,8 +238,8 @@ def gpu_arm(args):
 
     # end to end through the public API: pinned host operands, copies inside the timed region
     Ah = torch.empty((rows, K), pin_memory=True).copy_(A)
-    Bh = torch.empty((K, N), pin_memory=True).copy_(B)
-    Ch = torch.empty((rows, N), pin_memory=True)
+    Bh = torch.empty((K, cols), pin_memory=True).copy_(B)
+    Ch = torch.empty((rows, cols), pin_memory=True)
     e2e_steps = max(3, min(args.steps, 10))
     cake.cake_sgemm(Ah.numpy(), Bh.numpy(), Ch.numpy(), kernel=kernel)
     barrier()
@@ -255,19 +257,20 @@ def gpu_arm(args):
     if rank == 0:
         hbm, bf16_burst, bf16_sust, which = measured_peaks()
         peak = bf16_burst / 2 / 3 if args.kernel == "tf32x3" else 148 * 128 * 2 * 1.965e9 / 1e12
-        achieved = 2.0 * rows * N * K / (kern_ms_avg * 1e-3) / 1e12
+        achieved = 2.0 * rows * cols * K / (kern_ms_avg * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": flops * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "dense FP32 SGEMM M=K=N=%d, uniform(-1,1), seeded" % size,
-                       "kernel": args.kernel, "partition": "row blocks of M over %d GPU(s), B replicated" % world,
+                       "kernel": args.kernel, "partition": ("row blocks of M over %d GPU(s), B replicated" % world) if pc == 1 else
+                                    ("%d x %d grid of GPUs: row blocks of A x column blocks of B, no exchange" % (pr, pc)),
                        "l2": "operands (%.0f MB per GPU) exceed the 126 MB L2; no flush between steps" %
-                             ((rows * K + K * N + rows * N) * 4 / 1e6),
+                             ((rows * K + K * cols + rows * cols) * 4 / 1e6),
                        "step": "operand split pass + contraction kernel"},
             "clocks": clocks,
             "e2e": {"value": flops * e2e_steps / float(e2e_s.item()) / 1e12, "unit": UNIT,
-                    "h2d_bytes_per_step": (rows * K + K * N) * 4, "d2h_bytes_per_step": rows * N * 4,
+                    "h2d_bytes_per_step": (rows * K + K * cols) * 4, "d2h_bytes_per_step": rows * cols * 4,
                     "ms_h2d": e2e_stats["ms_h2d"], "ms_d2h": e2e_stats["ms_d2h"], "steps": e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "tensor", "kernel": "sgemm_tf32x3_kernel" if args.kernel == "tf32x3" else "sgemm_ffma_kernel",

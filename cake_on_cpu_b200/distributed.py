@@ -20,8 +20,9 @@ def _local(a, b, kernel):
 
 def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
     """A (M x K) and B (K x N) are CUDA tensors present on every rank.  Returns
-    (kind, (lo, hi), block): kind 'rows' -> block = C[lo:hi, :], 'cols' ->
-    C[:, lo:hi], 'k' -> C[lo:hi, :] after the reduce-scatter."""
+    (kind, span, block): kind 'rows' -> span (lo, hi), block = C[lo:hi, :]; 'cols' ->
+    C[:, lo:hi]; 'grid' -> span (r0, r1, c0, c1), block = C[r0:r1, c0:c1]; 'k' ->
+    C[lo:hi, :] after the reduce-scatter."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     M, K = A.shape
@@ -43,6 +44,10 @@ def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
     if kind == "cols":
         c0, c1 = partition.col_block(N, world, rank)
         return kind, (c0, c1), _local(A, B[:, c0:c1], kernel)
+    if kind == "grid":
+        r0, r1, c0, c1 = partition.grid_block(M, N, K, world, rank)
+        # the column block of B is read where it lies (leading dimension N), no copy
+        return kind, (r0, r1, c0, c1), api.cake_sgemm_ex(A[r0:r1], B[:, c0:c1], kernel=kernel)
     k0, k1 = partition.k_block(K, world, rank)
     partial = _local(A[:, k0:k1], B[k0:k1], kernel)
     r0, r1 = partition.row_block(M, world, rank)

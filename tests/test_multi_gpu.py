@@ -1,5 +1,5 @@
-"""One process per GPU over NCCL: row split, column split and the K split with
-its reduce-scatter, each checked against a float64 product.  Needs two GPUs;
+"""One process per GPU over NCCL: row split, column split, the 2 x 2 grid and the K split
+with its reduce-scatter, each checked against a float64 product.  Needs two (four) GPUs;
 skipped on a single-GPU box (the host logic is covered on CPU by test_partition_gloo.py)."""
 import os
 import socket
@@ -17,7 +17,11 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out):
+TWO_RANK_CASES = [(2048, 512, 768, "rows"), (256, 384, 4096, "cols"), (512, 16384, 256, "k"), (300, 20000, 130, "k")]
+FOUR_RANK_CASES = [(4096, 512, 4096, "grid"), (3000, 700, 2900, "grid"), (8192, 256, 512, "rows"), (640, 32768, 256, "k")]
+
+
+def _worker(rank, world, port, out, cases=TWO_RANK_CASES):
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -25,17 +29,21 @@ def _worker(rank, world, port, out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     from cake_on_cpu_b200 import distributed
     results = []
-    for (M, K, N, want) in [(2048, 512, 768, "rows"), (256, 384, 4096, "cols"), (512, 16384, 256, "k"), (300, 20000, 130, "k")]:
+    for (M, K, N, want) in cases:
         g = torch.Generator(device="cuda").manual_seed(5)
         A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
         B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
-        kind, (lo, hi), block = distributed.sharded_sgemm(A, B)
+        kind, span, block = distributed.sharded_sgemm(A, B)
         full = A.double() @ B.double()
-        ref = full[:, lo:hi] if kind == "cols" else full[lo:hi]
         den = A.double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
-        den = den[:, lo:hi] if kind == "cols" else den[lo:hi]
-        err = ((block.double() - ref).abs() / den).max().item()
-        results.append((kind == want, err, lo, hi))
+        if kind == "grid":
+            cut = lambda X: X[span[0]:span[1], span[2]:span[3]]
+        elif kind == "cols":
+            cut = lambda X: X[:, span[0]:span[1]]
+        else:
+            cut = lambda X: X[span[0]:span[1]]
+        err = ((block.double() - cut(full)).abs() / cut(den)).max().item() if block.shape == cut(full).shape else float("inf")
+        results.append((kind == want, err, span[0], span[1], block.numel()))
     gathered = [None] * world
     dist.all_gather_object(gathered, results)
     if rank == 0:
@@ -60,12 +68,37 @@ def test_two_ranks_nccl(cake):
         p.join(timeout=120)
         assert p.exitcode == 0
     for per_rank in res:
-        for ok_kind, err, lo, hi in per_rank:
+        for ok_kind, err, lo, hi, _ in per_rank:
             assert ok_kind
             assert err <= 1e-5
     # the two ranks' blocks tile the matrix
     for case in range(len(res[0])):
         assert res[0][case][2] == 0 and res[0][case][3] == res[1][case][2]
+
+
+def test_four_ranks_nccl_grid(cake):
+    """2 x 2 process grid (no exchange), a row split and a K split at world size 4."""
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 4, port, out, FOUR_RANK_CASES)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = out.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for per_rank in res:
+        for ok_kind, err, lo, hi, _ in per_rank:
+            assert ok_kind
+            assert err <= 1e-5
+    # every element of C is owned exactly once
+    for case, (M, K, N, _) in enumerate(FOUR_RANK_CASES):
+        assert sum(per_rank[case][4] for per_rank in res) == M * N
 
 
 def test_cpp_api_splits_rows_over_visible_gpus(cake, tmp_path):

@@ -26,11 +26,25 @@ def test_blocks_tile_the_range():
 
 
 def test_plan_follows_the_benchmark_shapes():
-    assert partition.plan(8192, 8192, 8192, 8) == "rows"
+    assert partition.plan(8192, 8192, 8192, 2) == "rows"
+    assert partition.plan(8192, 8192, 8192, 4) == "grid" and partition.grid_shape(8192, 8192, 8192, 4) == (2, 2)
+    assert partition.plan(8192, 8192, 8192, 8) == "grid" and partition.grid_shape(8192, 8192, 8192, 8) == (4, 2)
     assert partition.plan(65536, 1024, 1024, 8) == "rows"
     assert partition.plan(1024, 65536, 1024, 8) == "cols"
     assert partition.plan(1024, 1024, 262144, 8) == "k"
     assert partition.plan(5, 5, 5, 1) == "rows"
+
+
+def test_grid_blocks_tile_the_matrix():
+    for (M, N, K) in [(8192, 8192, 8192), (3000, 3000, 3000), (16384, 4096, 512), (1000, 5000, 64)]:
+        for world in (1, 2, 4, 6, 8):
+            pr, pc = partition.grid_shape(M, N, K, world)
+            assert pr * pc == world
+            cover = np.zeros((M, N), np.int8)
+            for r in range(world):
+                r0, r1, c0, c1 = partition.grid_block(M, N, K, world, r)
+                cover[r0:r1, c0:c1] += 1
+            assert (cover == 1).all()
 
 
 def _free_port():
@@ -54,10 +68,15 @@ def _worker(rank, world, port, shape, out):
         dist.all_reduce(t)  # gloo has no reduce_scatter; the row block is cut from the sum
         return t.numpy()[r0:r1]
 
-    kind, (lo, hi), local = partition.sharded_sgemm(A, B, rank, world, lambda a, b: a @ b, reduce_scatter)
+    kind, span, local = partition.sharded_sgemm(A, B, rank, world, lambda a, b: a @ b, reduce_scatter)
     full = A @ B
-    want = full[lo:hi] if kind in ("rows", "k") else full[:, lo:hi]
-    ok = np.allclose(local, want, atol=1e-3)
+    if kind == "grid":
+        want = full[span[0]:span[1], span[2]:span[3]]
+        lo, hi = span[0] * N + span[2], span[1] * N + span[3]  # only reported
+    else:
+        lo, hi = span
+        want = full[lo:hi] if kind in ("rows", "k") else full[:, lo:hi]
+    ok = local.shape == want.shape and np.allclose(local, want, atol=1e-3)
     gathered = [None] * world
     dist.all_gather_object(gathered, (kind, lo, hi, bool(ok)))
     if rank == 0:
@@ -81,3 +100,21 @@ def test_two_ranks_reassemble_the_product(shape):
     assert len(kinds) == 1
     assert all(r[3] for r in res)
     assert res[0][1] == 0 and res[0][2] == res[1][1]
+
+
+def test_four_ranks_on_a_grid():
+    """2 x 2 grid: every rank's block equals the matching block of the full product, nothing exchanged."""
+    shape = (2048, 32, 2048)
+    assert partition.plan(shape[0], shape[2], shape[1], 4) == "grid"
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 4, port, shape, out)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = out.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert {r[0] for r in res} == {"grid"}
+    assert all(r[3] for r in res)
