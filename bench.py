@@ -258,6 +258,14 @@ def gpu_arm(args):
         hbm, bf16_burst, bf16_sust, which = measured_peaks()
         peak = bf16_burst / 2 / 3 if args.kernel == "tf32x3" else 148 * 128 * 2 * 1.965e9 / 1e12
         achieved = 2.0 * rows * cols * K / (kern_ms_avg * 1e-3) / 1e12
+        # DRAM bytes of one contraction launch, from one ncu capture of the 8192^3 launch on one GPU
+        # (dram__bytes_read.sum 5.22 GB + dram__bytes_write.sum 0.255 GB; summary under profiles/).  The
+        # algorithmic bytes are 1.34 GB (four operand planes read once, C written once); the rest is A and B
+        # panels read again by later waves of tiles once they have left the 126 MB L2.  A rank of a
+        # multi-GPU run owns rows x cols of C and its traffic is scaled by that share.
+        traffic = None
+        if args.kernel == "tf32x3" and size == 8192:
+            traffic = (5.22e9 + 0.25544e9) * (rows * cols) / float(M * N)
         line = {
             "metric": METRIC, "value": flops * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
@@ -279,7 +287,7 @@ def gpu_arm(args):
                          if args.kernel == "tf32x3" else "148 SMs x 128 lanes x 2 flop x 1.965 GHz",
                          "frac_of_sustained": achieved / (bf16_sust / 6) if args.kernel == "tf32x3" else None,
                          "kernel_ms": kern_ms_avg, "prepass_ms": float(pre.item()),
-                         "traffic": None},
+                         "traffic": traffic},
         }
         if world == 1 and not args.no_cpu_baseline:
             try:
