@@ -568,12 +568,17 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
         return CAKEB200_ERR_ARG;
     }
     if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
-    if (kernel == CAKEB200_KERNEL_TF32X3) {
-        set_error("the batched entry point runs on the FFMA kernel");
+    if (kernel == CAKEB200_KERNEL_TF32X3 && !small_tf32x3_fits(M, N, K)) {
+        set_error("the batched tensor-core kernel needs M <= 128 and N <= 256 (M=%d N=%d)", M, N);
         return CAKEB200_ERR_ARG;
     }
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
+    // The tensor-core kernel wins once the 128-row tile is reasonably full and there are products
+    // for most SMs; a few tiny products stay on the exact-FP32 kernel.
+    const bool tensor = kernel == CAKEB200_KERNEL_TF32X3 ||
+                        (kernel == CAKEB200_KERNEL_AUTO && small_tf32x3_fits(M, N, K) && M >= 48 && N >= 32 && K >= 32 &&
+                         batch >= st->sm_count / 2);
     cudaStream_t s = (cudaStream_t) stream;  // NULL = the CUDA default stream, ordered with the caller's default-stream work
     Operand oa, ob, oc;
     int rc;
@@ -588,7 +593,12 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
     g.lda = K; g.ldb = N; g.ldc = N;
     g.stride_a = (long long) M * K; g.stride_b = (long long) K * N; g.stride_c = (long long) M * N;
     g.order = CAKEB200_SCHED_MKN;
-    for (int done = 0; done < batch; done += 65535) {  // gridDim.z limit
+    if (tensor) {
+        g.batch = batch;
+        if ((rc = launch_sgemm_small_tf32x3(g, st->status_word, st->sm_count, s))) return rc;
+        g_stats.launches++;
+    }
+    for (int done = 0; !tensor && done < batch; done += 65535) {  // gridDim.z limit
         GemmProblem part = g;
         part.batch = std::min(65535, batch - done);
         part.A += (long long) done * g.stride_a;
@@ -597,11 +607,11 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
         if ((rc = launch_sgemm_ffma(part, s))) return rc;
         g_stats.launches++;
     }
-    g_stats.kernel = CAKEB200_KERNEL_FFMA;
+    g_stats.kernel = tensor ? CAKEB200_KERNEL_TF32X3 : CAKEB200_KERNEL_FFMA;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
     if ((rc = stage_out(oc, s))) return rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
-    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    if ((rc = check_status_word(st, s))) return rc;
     g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
     g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
     g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);

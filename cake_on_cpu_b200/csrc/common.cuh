@@ -72,6 +72,9 @@ int ensure_scratch(DeviceState* st, size_t bytes);
 // exact-FP32 FFMA path (sgemm_ffma.cu)
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);  // untransposed operands only
 int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream);
+// batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)
+bool small_tf32x3_fits(int M, int N, int K);
+int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_count, cudaStream_t stream);
 // 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
 // row-band interface of the 3xTF32 path (operand planes laid out once, rows multiplied band by band)

@@ -59,15 +59,18 @@ def _dense(M, K, N, kernel):
     return run
 
 
-def _batched(batch, n):
+def _batched(batch, n, kernel=api.KERNEL_AUTO):
     def run(reps):
         g = torch.Generator(device="cuda").manual_seed(1)
         A, B = _uniform(g, batch, n, n), _uniform(g, batch, n, n)
         C = torch.empty((batch, n, n), device="cuda")
-        ms = _timed(lambda: api.cake_sgemm_batched(A, B, C), reps)
+        ms = _timed(lambda: api.cake_sgemm_batched(A, B, C, kernel=kernel), reps)
+        st = api.last_stats()
         flops, nbytes = 2.0 * batch * n ** 3, 3.0 * batch * n * n * 4
         return {"ms": ms, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
-                "bound": "hbm", "frac": nbytes / ms / 1e6 / HBM_GBS, "frac_fp32_pipe": flops / ms / 1e9 / FP32_PIPE}
+                "bound": "hbm", "frac": nbytes / ms / 1e6 / HBM_GBS, "kernel_ms": st["ms_gemm"],
+                "ran": "tcgen05, operands split in shared memory" if st["kernel"] == api.KERNEL_TF32X3 else "ffma",
+                "frac_fp32_pipe": flops / ms / 1e9 / FP32_PIPE}
     return run
 
 
@@ -131,6 +134,7 @@ CONFIGS["rect_m_first"] = _dense(65536, 1024, 1024, api.KERNEL_AUTO)
 CONFIGS["rect_n_first"] = _dense(1024, 1024, 65536, api.KERNEL_AUTO)
 CONFIGS["rect_k_first"] = _dense(1024, 262144, 1024, api.KERNEL_AUTO)
 CONFIGS["small_batch"] = _batched(4096, 96)
+CONFIGS["small_batch_ffma"] = _batched(4096, 96, api.KERNEL_FFMA)
 for _d, _name in ((0.5, "50"), (0.1, "10"), (0.01, "1")):
     CONFIGS["sparse_%s" % _name] = _sparse(8192, _d, api.KERNEL_AUTO)
     CONFIGS["sparse_%s_zero_skipping" % _name] = _sparse(8192, _d, api.KERNEL_FFMA)

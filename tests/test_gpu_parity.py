@@ -315,6 +315,38 @@ def test_batched_small(cake, oracle):
             assert rel_err(C[i], ref[i], A[i], B[i]) <= TOL
 
 
+def test_batched_small_on_tensor_cores(cake, oracle):
+    """The batched kernel that splits its operands in shared memory: full and ragged tiles, K not a multiple
+    of the stage depth, N at the 256 limit, more products than SMs (several per CTA, both accumulators in use)."""
+    shapes = [(300, 96, 96, 96), (7, 128, 64, 256), (333, 33, 17, 70), (40, 100, 200, 48), (2, 1, 1, 1), (150, 128, 37, 130),
+              (1, 64, 100, 64), (300, 96, 96, 96)]
+    for case, (batch, M, K, N) in enumerate(shapes):
+        # the last case repeats the first with the producers reading global memory themselves instead of the TMA ring
+        if case == len(shapes) - 1:
+            os.environ["CAKEB200_SMALL_DIRECT"] = "1"
+        A, B = oracle.uniform((batch, M, K), 1), oracle.uniform((batch, K, N), 2)
+        C = np.full((batch, M, N), np.nan, np.float32)
+        cake.cake_sgemm_batched(A, B, C, kernel=cake.KERNEL_TF32X3)
+        assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+        check = range(batch) if batch <= 8 else (0, 1, batch // 2, batch - 2, batch - 1)
+        ref = oracle.sgemm_batched(np.ascontiguousarray(A[list(check)]), np.ascontiguousarray(B[list(check)]), 8)
+        for j, i in enumerate(check):
+            assert rel_err(C[i], ref[j], A[i], B[i]) <= TOL, (batch, M, K, N, i)
+        # every item against float64 as well (cheap), so no item is skipped
+        ref64 = np.einsum("bmk,bkn->bmn", A.astype(np.float64), B.astype(np.float64))
+        den = np.linalg.norm(A, axis=2)[:, :, None] * np.linalg.norm(B, axis=1)[:, None, :]
+        assert (np.abs(C - ref64) / np.maximum(den, 1e-30)).max() <= TOL
+    os.environ.pop("CAKEB200_SMALL_DIRECT", None)
+    # AUTO takes the tensor-core kernel for a large batch of well-filled tiles, FFMA for a handful of tiny ones
+    A, B = oracle.uniform((300, 96, 96), 1), oracle.uniform((300, 96, 96), 2)
+    cake.cake_sgemm_batched(A, B)
+    assert cake.last_stats()["kernel"] == cake.KERNEL_TF32X3
+    cake.cake_sgemm_batched(A[:4], B[:4])
+    assert cake.last_stats()["kernel"] == cake.KERNEL_FFMA
+    with pytest.raises(cake.CakeError):
+        cake.cake_sgemm_batched(oracle.uniform((2, 130, 8), 1), oracle.uniform((2, 8, 8), 2), kernel=cake.KERNEL_TF32X3)
+
+
 def test_errors_are_status_codes(cake):
     A = np.zeros((4, 4), np.float32)
     with pytest.raises(ValueError):
