@@ -731,10 +731,30 @@ int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch
         set_error("unknown kernel id %d", kernel);
         return CAKEB200_ERR_ARG;
     }
+    if (tensor && getenv("CAKEB200_CONV_PLANES") == nullptr &&
+        conv_tf32x3_fits((const float*) oi.dev, batch, cin, H, W, cout, hf, wf, stride, pad)) {
+        // Implicit product: input rows come on chip by TMA, the patch operand is built in shared memory
+        if ((rc = ensure_scratch(st, conv_tf32x3_scratch_bytes(cin, cout, hf, wf)))) return rc;
+        int launches = 0;
+        if ((rc = launch_conv_tf32x3((const float*) oi.dev, (const float*) of.dev, (float*) oo.dev, nullptr, batch, cin, H, W,
+                                     cout, hf, wf, pad, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s,
+                                     &launches)))
+            return rc;
+        g_stats.launches += launches;
+        g_stats.kernel = CAKEB200_KERNEL_TF32X3;
+        g_stats.tile_m = 128; g_stats.tile_n = cout >= 128 ? 128 : (cout + 15) / 16 * 16; g_stats.tile_k = 32;
+        CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+        if ((rc = stage_out(oo, s))) return rc;
+        CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+        if ((rc = check_status_word(st, s))) return rc;
+        g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+        g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+        g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+        g_stats.ms_prepass = 0.f;
+        return CAKEB200_OK;
+    }
     if (tensor) {
-        // Tensor-core route: the filters are the A operand (cout x Kg); the B operand's transposed
-        // hi / lo planes are produced directly from the input (im2col is never materialised); the
-        // epilogue stores (cout, (image, position)) straight into NCHW.
+        // Tensor-core route for the other geometries (strides, very wide images): the filters are the A operand
         Tf32x3Planes planes;
         if ((rc = ensure_scratch(st, tf32x3_plane_bytes(cout, (int) Ng, Kg, st->sm_count)))) return rc;
         if ((rc = tf32x3_planes(cout, (int) Ng, Kg, st->scratch, st->scratch_bytes, &planes, st->sm_count))) return rc;

@@ -75,6 +75,12 @@ int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int 
 // batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)
 bool small_tf32x3_fits(int M, int N, int K);
 int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_count, cudaStream_t stream);
+// stride-1 convolution as an implicit product (conv_tf32x3.cu); scratch holds the split filter planes
+bool conv_tf32x3_fits(const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad);
+size_t conv_tf32x3_scratch_bytes(int cin, int cout, int hf, int wf);
+int launch_conv_tf32x3(const float* in, const float* filters, float* out, const float* bias, int batch, int cin, int H,
+                       int W, int cout, int hf, int wf, int pad, void* scratch, size_t scratch_bytes, int* status_word,
+                       int sm_count, cudaStream_t stream, int* launches);
 // 3xTF32 tcgen05 path (sgemm_tf32x3.cu); needs scratch for the split operand planes
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count);
 // row-band interface of the 3xTF32 path (operand planes laid out once, rows multiplied band by band)

@@ -100,8 +100,10 @@ def _conv(b, cin, hw, cout):
         flops = 2.0 * cout * cin * 9 * b * hw * hw
         nbytes = 4.0 * (x.numel() + w.numel() + out.numel())
         return {"ms": ms, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
-                "bound": "tensor", "frac": flops / ms / 1e9 / TENSOR_3XTF32,
-                "ran": "tcgen05" if api.last_stats()["kernel"] == api.KERNEL_TF32X3 else "ffma"}
+                "bound": "tensor", "frac": flops / ms / 1e9 / TENSOR_3XTF32, "kernel_ms": api.last_stats()["ms_gemm"],
+                "ran": ("ffma" if api.last_stats()["kernel"] != api.KERNEL_TF32X3 else
+                        "tcgen05, implicit (patch operand built on chip)" if api.last_stats()["launches"] == 2 else
+                        "tcgen05 on im2col planes")}
     return run
 
 

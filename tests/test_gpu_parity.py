@@ -306,6 +306,47 @@ def test_conv_benchmark_shape_scaled_down(cake, oracle):
     assert rel_err(got, want, w.reshape(512, -1), col) <= TOL
 
 
+def test_implicit_convolution_geometries(cake, oracle):
+    """The stride-1 tensor-core convolution that builds its patch operand in shared memory: filter shapes,
+    paddings, channel counts off the 32 / 16 grids, several channel tiles, tiles of one and of many rows, and
+    the fallbacks (stride 2, image area not a multiple of 4 floats) - each against the oracle's im2col + GEMM
+    where that is small and against a float64 convolution always."""
+    import torch
+    cases = [  # batch, cin, H, W, cout, hf, wf, pad, implicit route expected
+        (3, 8, 14, 14, 16, 3, 3, 1, True), (2, 3, 8, 6, 5, 3, 3, 1, True), (2, 40, 12, 12, 130, 3, 3, 1, True),
+        (2, 32, 10, 10, 64, 1, 1, 0, True), (1, 16, 9, 12, 24, 5, 3, 2, True), (2, 7, 6, 10, 9, 3, 5, 0, True),
+        (5, 64, 56, 56, 64, 3, 3, 1, True), (2, 33, 16, 4, 17, 3, 3, 3, True), (1, 4, 30, 80, 8, 3, 3, 1, True),
+        (1, 64, 5, 300, 8, 3, 3, 1, False), (2, 8, 7, 7, 16, 3, 3, 1, False)]
+    for (b, cin, H, W, cout, hf, wf, pad, implicit) in cases:
+        x = oracle.normal((b, cin, H, W), 4, 0.1)
+        w = oracle.normal((cout, cin, hf, wf), 5, 0.1)
+        out = cake.cake_conv2d(x, w, 1, pad, kernel=cake.KERNEL_TF32X3)
+        st = cake.last_stats()
+        assert st["kernel"] == cake.KERNEL_TF32X3
+        assert (st["launches"] == 2) == implicit, (b, cin, H, W, cout, hf, wf, pad, st)
+        ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=pad).numpy()
+        assert out.shape == ref.shape
+        col = oracle.im2col(x, hf, wf, 1, pad)
+        Ho, Wo = out.shape[2:]
+        got = out.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+        want = ref.transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+        assert rel_err(got, want, w.reshape(cout, -1), col) <= TOL, (b, cin, H, W, cout, hf, wf, pad)
+        if b * cin * H * W <= 20000:
+            want = oracle.conv2d(x, w, 1, pad, 8).transpose(1, 0, 2, 3).reshape(cout, b * Ho * Wo)
+            assert rel_err(got, want, w.reshape(cout, -1), col) <= TOL
+    # the older route (im2col planes) must agree with the implicit one to the same tolerance
+    x, w = oracle.normal((2, 40, 12, 12), 4, 0.1), oracle.normal((130, 40, 3, 3), 5, 0.1)
+    a = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
+    os.environ["CAKEB200_CONV_PLANES"] = "1"
+    try:
+        b2 = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
+        assert cake.last_stats()["launches"] == 3
+    finally:
+        os.environ.pop("CAKEB200_CONV_PLANES", None)
+    col = oracle.im2col(x, 3, 3, 1, 1)
+    assert rel_err(a.transpose(1, 0, 2, 3).reshape(130, -1), b2.transpose(1, 0, 2, 3).reshape(130, -1), w.reshape(130, -1), col) <= TOL
+
+
 def test_batched_small(cake, oracle):
     for (batch, M, K, N) in [(64, 96, 96, 96), (5, 33, 17, 70), (3, 130, 40, 129)]:
         A, B = oracle.uniform((batch, M, K), 1), oracle.uniform((batch, K, N), 2)
