@@ -131,7 +131,11 @@ int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls);
 /* `batch` independent products of identical shape, item i at A + i*M*K etc.
  * Replaces the small-matrix entry points cake_gemm_small / schedule_*_small
  * (reference include/cake.h:52-72, src/cake_sgemm_small.cpp:7-236), whose live
- * equivalent in the reference is one cake_sgemm call per item. */
+ * equivalent in the reference is one cake_sgemm call per item.  `kernel`:
+ * CAKEB200_KERNEL_FFMA = exact FP32; CAKEB200_KERNEL_TF32X3 = tensor cores with
+ * the operands split inside the kernel (needs M <= 128 and N <= 256);
+ * CAKEB200_KERNEL_AUTO picks the tensor-core kernel for a batch that fills most
+ * SMs with reasonably full tiles. */
 int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K,
                            int batch, int kernel, void* stream);
 
@@ -145,7 +149,10 @@ int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, in
 /* NCHW convolution through im2col + SGEMM: out[b][co][ho][wo].  Replaces the
  * GEMM route of the reference's convolution example (im_2_col + cake_sgemm,
  * reference examples/cake_conv.cpp:1007-1066,1178-1213), extended with batch,
- * stride and zero padding. */
+ * stride and zero padding.  On the tensor-core path a stride-1 convolution runs
+ * as an implicit product (the patch matrix is built on chip, never in memory);
+ * other geometries build split im2col planes first; CAKEB200_KERNEL_FFMA
+ * materialises the FP32 im2col matrix and multiplies exactly. */
 int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch, int cin,
                     int H, int W, int cout, int hf, int wf, int stride, int pad,
                     int kernel, void* stream);
