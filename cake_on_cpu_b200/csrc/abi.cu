@@ -16,6 +16,7 @@ namespace cakeb200 {
 int pack_A_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
 int pack_B_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
 int pack_C_dev(const float*, float*, int, int, int, const cakeb200_blk_dims*, const cakeb200_cntx*, bool, cudaStream_t);
+int last_pack_width();
 size_t sparse_scratch_bytes(int M, int K);
 int sp_compact(const float* A, int M, int K, void* scratch, int* status_word, cudaStream_t stream, long long* nnz,
                int* launches);
@@ -478,6 +479,7 @@ int pack_impl(pack_fn fn, const float* mat, size_t mat_bytes, float* packed, siz
     if ((rc = stage_in(st, 1, op, packed, packed_bytes, unpack, s))) return rc;
     if ((rc = fn((const float*) om.dev, (float*) op.dev, d0, d1, p, x, c, unpack, s))) return rc;
     g_stats.launches = 1;
+    g_stats.tile_k = last_pack_width();  // floats moved per access: 4 when every block allows 16-byte moves
     if ((rc = stage_out(unpack ? om : op, s))) return rc;
     CAKE_CUDA_OK(cudaStreamSynchronize(s));
     return CAKEB200_OK;

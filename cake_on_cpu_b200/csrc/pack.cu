@@ -9,6 +9,9 @@
 // and pass them, so the library produces byte-identical buffers: the host walks
 // the block structure once and emits one descriptor per OB, and a single
 // bandwidth-bound kernel moves every element (padding positions become zero).
+#include <stdlib.h>
+#include <string.h>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -17,6 +20,8 @@ namespace cakeb200 {
 namespace {
 
 enum { OB_A = 0, OB_B = 1, OB_C = 2 };
+
+thread_local int g_last_width = 1;  // floats per access of this thread's last pack / unpack call
 
 struct ObDesc {
     long long mat_off;     // first element of the block in the row-major matrix
@@ -74,11 +79,119 @@ __device__ __forceinline__ void ob_move_block(const ObDesc& d, float* __restrict
     }
 }
 
+// Four packed elements per thread.  For B and C a quad is four consecutive columns of one row of a
+// register-tile panel (n_r is a multiple of 4), on both sides a 16-byte access.
+template <int KIND, bool UNPACK>
+__device__ __forceinline__ void ob_move_block_quads(const ObDesc& d, float* __restrict__ mat, float* __restrict__ packed,
+                                                    int ld, int row_limit, int col_limit, int mr, int nr) {
+    const unsigned quads = (unsigned) ((long long) d.rows * d.cols / 4);
+    const unsigned step = gridDim.y * blockDim.x;
+    for (unsigned q = blockIdx.y * blockDim.x + threadIdx.x; q < quads; q += step) {
+        int r, c;
+        ob_coords<KIND, unsigned>(q * 4u, d.rows, d.cols, mr, nr, r, c);
+        float4* pk = reinterpret_cast<float4*>(packed + d.packed_off) + q;
+        float* m = mat + d.mat_off + (long long) r * ld + c;
+        const bool row_in = d.row0 + r < row_limit;
+        if (row_in && d.col0 + c + 3 < col_limit) {
+            if (UNPACK) *reinterpret_cast<float4*>(m) = *pk;
+            else *pk = __ldg(reinterpret_cast<const float4*>(m));
+        } else {  // quad on the ragged edge of the matrix
+            if (UNPACK) {
+                const float4 v = *pk;
+                const float e[4] = {v.x, v.y, v.z, v.w};
+                for (int j = 0; j < 4; j++)
+                    if (row_in && d.col0 + c + j < col_limit) m[j] = e[j];
+            } else {
+                float e[4];
+                for (int j = 0; j < 4; j++) e[j] = (row_in && d.col0 + c + j < col_limit) ? __ldg(m + j) : 0.0f;
+                *pk = make_float4(e[0], e[1], e[2], e[3]);
+            }
+        }
+    }
+}
+
+// A: a thread owns V (4 or 2) consecutive k of one row panel: MR rows are read as V-wide vectors along k
+// (coalesced across the warp) and leave as V * MR contiguous packed floats ([k][row in panel]), written
+// 16 bytes at a time.  V = 2 serves block depths k_c that are even but not multiples of 4.
+template <bool UNPACK, int MR, int V>
+__device__ __forceinline__ void ob_move_block_a_vec(const ObDesc& d, float* __restrict__ mat, float* __restrict__ packed,
+                                                    int ld, int row_limit, int col_limit) {
+    static_assert((V * MR) % 4 == 0, "a thread's packed floats must be whole 16-byte pieces");
+    const unsigned kq = (unsigned) d.cols / V;  // vectors of k per panel
+    const unsigned items = (unsigned) (d.rows / MR) * kq;
+    const unsigned step = gridDim.y * blockDim.x;
+    for (unsigned i = blockIdx.y * blockDim.x + threadIdx.x; i < items; i += step) {
+        const unsigned panel = i / kq, k = (i - panel * kq) * V;
+        float4* pk = reinterpret_cast<float4*>(packed + d.packed_off + (long long) panel * d.cols * MR + (long long) k * MR);
+        float* m = mat + d.mat_off + (long long) panel * MR * ld + k;
+        const bool k_in = d.col0 + (int) k + V - 1 < col_limit;
+        float w[V * MR];  // w[j * MR + r] = element (row r, k + j)
+        if (UNPACK) {
+#pragma unroll
+            for (int j = 0; j < V * MR / 4; j++) {
+                const float4 v = pk[j];
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+#pragma unroll
+            for (int r = 0; r < MR; r++) {
+                if (d.row0 + (int) panel * MR + r >= row_limit) continue;
+                float* dst = m + (long long) r * ld;
+                if (k_in) {
+                    if (V == 4) *reinterpret_cast<float4*>(dst) = make_float4(w[r], w[MR + r], w[2 * MR + r], w[3 * MR + r]);
+                    else *reinterpret_cast<float2*>(dst) = make_float2(w[r], w[MR + r]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < V; j++)
+                        if (d.col0 + (int) k + j < col_limit) dst[j] = w[j * MR + r];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < MR; r++) {
+                float e[4] = {0.f, 0.f, 0.f, 0.f};
+                if (d.row0 + (int) panel * MR + r < row_limit) {
+                    const float* src = m + (long long) r * ld;
+                    if (k_in) {
+                        if (V == 4) {
+                            const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+                            e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                        } else {
+                            const float2 v = __ldg(reinterpret_cast<const float2*>(src));
+                            e[0] = v.x; e[1] = v.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < V; j++)
+                            if (d.col0 + (int) k + j < col_limit) e[j] = __ldg(src + j);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < V; j++) w[j * MR + r] = e[j];
+            }
+#pragma unroll
+            for (int j = 0; j < V * MR / 4; j++) pk[j] = make_float4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+    }
+}
+
+// `vec` (4, 2 or 1): floats per access that every block of the call allows (decided on the host: alignment
+// of the buffers, of every block offset and of the leading dimension; n_r a multiple of 4 for B and C, the
+// block depth k_c a multiple of 4 or 2 for A).
 template <int KIND, bool UNPACK>
 __global__ void __launch_bounds__(256)
 ob_move_kernel(const ObDesc* __restrict__ descs, float* __restrict__ mat, float* __restrict__ packed,
-               int ld, int row_limit, int col_limit, int mr, int nr) {
+               int ld, int row_limit, int col_limit, int mr, int nr, int vec) {
     const ObDesc d = descs[blockIdx.x];
+    if (vec > 1 && (long long) d.rows * d.cols < 0x7fffffffLL) {
+        if (KIND == OB_A) {
+            if (mr == 6 && vec == 4) return ob_move_block_a_vec<UNPACK, 6, 4>(d, mat, packed, ld, row_limit, col_limit);
+            if (mr == 6 && vec == 2) return ob_move_block_a_vec<UNPACK, 6, 2>(d, mat, packed, ld, row_limit, col_limit);
+            if (mr == 8 && vec == 4) return ob_move_block_a_vec<UNPACK, 8, 4>(d, mat, packed, ld, row_limit, col_limit);
+            if (mr == 8 && vec == 2) return ob_move_block_a_vec<UNPACK, 8, 2>(d, mat, packed, ld, row_limit, col_limit);
+        } else {
+            return ob_move_block_quads<KIND, UNPACK>(d, mat, packed, ld, row_limit, col_limit, mr, nr);
+        }
+    }
     if ((long long) d.rows * d.cols < 0x7fffffffLL - (long long) gridDim.y * blockDim.x)
         ob_move_block<KIND, UNPACK, unsigned>(d, mat, packed, ld, row_limit, col_limit, mr, nr);
     else
@@ -200,25 +313,76 @@ void describe_C(std::vector<ObDesc>& out, int M, int N, int p, const cakeb200_bl
     (void) M;
 }
 
+// Descriptor tables on the device, kept for the shapes seen last: a caller that packs the same
+// shape again (every layer call of a network, every step of a benchmark) skips the upload and the
+// synchronisation it needs.  An entry is recognised by the descriptors themselves.
+struct TableEntry {
+    int device = -1;
+    std::vector<ObDesc> host;
+    ObDesc* dev = nullptr;
+    unsigned long long used = 0;
+};
+constexpr int TABLES = 12;
+TableEntry g_tables[TABLES];
+unsigned long long g_table_clock = 0;
+std::mutex g_table_mutex;
+
+int device_table(int device, const std::vector<ObDesc>& descs, cudaStream_t stream, const ObDesc** out) {
+    std::lock_guard<std::mutex> lock(g_table_mutex);
+    const size_t bytes = descs.size() * sizeof(ObDesc);
+    TableEntry* victim = &g_tables[0];
+    for (TableEntry& e : g_tables) {
+        if (e.dev && e.device == device && e.host.size() == descs.size() && memcmp(e.host.data(), descs.data(), bytes) == 0) {
+            e.used = ++g_table_clock;
+            *out = e.dev;
+            return CAKEB200_OK;
+        }
+        if (e.used < victim->used) victim = &e;
+    }
+    if (victim->dev) {
+        cudaFree(victim->dev);  // waits for kernels that may still read the old table
+        victim->dev = nullptr;
+    }
+    CAKE_CUDA_OK(cudaMalloc((void**) &victim->dev, bytes));
+    victim->host = descs;
+    victim->device = device;
+    victim->used = ++g_table_clock;
+    CAKE_CUDA_OK(cudaMemcpyAsync(victim->dev, victim->host.data(), bytes, cudaMemcpyHostToDevice, stream));
+    CAKE_CUDA_OK(cudaStreamSynchronize(stream));
+    *out = victim->dev;
+    return CAKEB200_OK;
+}
+
 template <int KIND, bool UNPACK>
 int run_move(std::vector<ObDesc>& descs, float* mat, float* packed, int ld, int row_limit, int col_limit,
              int mr, int nr, cudaStream_t stream) {
     if (descs.empty()) return CAKEB200_OK;
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
-    const size_t bytes = descs.size() * sizeof(ObDesc);
-    int rc = ensure_scratch(st, bytes);
+    const ObDesc* table = nullptr;
+    int rc = device_table(st->device, descs, stream, &table);
     if (rc) return rc;
-    CAKE_CUDA_OK(cudaMemcpyAsync(st->scratch, descs.data(), bytes, cudaMemcpyHostToDevice, stream));
-    CAKE_CUDA_OK(cudaStreamSynchronize(stream));  // descs is a host temporary
     long long biggest = 0;
     for (const ObDesc& d : descs) biggest = std::max(biggest, (long long) d.rows * d.cols);
-    // enough CTAs per block to cover it with ~8 elements per thread, capped
+    // wide moves need every address involved to be a multiple of the width
+    auto allows = [&](int w) {
+        if (ld % w != 0 || ((uintptr_t) mat) % (4 * w) != 0 || ((uintptr_t) packed) % 16 != 0) return false;
+        if (KIND == OB_A ? !(mr == 6 || mr == 8) : (w != 4 || nr % 4 != 0)) return false;
+        for (const ObDesc& d : descs) {
+            if (d.mat_off % w != 0 || d.packed_off % 4 != 0 || d.col0 % w != 0) return false;
+            if (KIND == OB_A ? (d.cols % w != 0 || d.rows % mr != 0) : (d.cols % nr != 0)) return false;
+        }
+        return true;
+    };
+    int vec = allows(4) ? 4 : (KIND == OB_A && allows(2)) ? 2 : 1;
+    if (getenv("CAKEB200_PACK_SCALAR")) vec = 1;  // for tests: the one-element-per-thread path
+    g_last_width = vec;
+    // enough CTAs per block to cover it with ~8 elements (2 quads) per thread, capped
     int chunks = (int) std::min<long long>(std::max<long long>((biggest + 2047) / 2048, 1), 1024);
     while ((long long) chunks * descs.size() > (1LL << 22) && chunks > 1) chunks /= 2;
     dim3 grid((unsigned) descs.size(), (unsigned) chunks);
-    ob_move_kernel<KIND, UNPACK><<<grid, 256, 0, stream>>>((const ObDesc*) st->scratch, mat, packed, ld,
-                                                           row_limit, col_limit, mr, nr);
+    ob_move_kernel<KIND, UNPACK><<<grid, 256, 0, stream>>>(table, mat, packed, ld,
+                                                           row_limit, col_limit, mr, nr, vec);
     CAKE_CUDA_OK(cudaGetLastError());
     return CAKEB200_OK;
 }
@@ -232,6 +396,8 @@ bool bad(const void* a, const void* b, const cakeb200_blk_dims* x, const cakeb20
 }
 
 }  // namespace
+
+int last_pack_width() { return g_last_width; }
 
 // Device-pointer implementations behind the C ABI (pointer-kind handling lives in abi.cu).
 int pack_A_dev(const float* A, float* A_p, int M, int K, int p, const cakeb200_blk_dims* x, const cakeb200_cntx* c,

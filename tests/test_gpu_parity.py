@@ -239,6 +239,41 @@ def test_pack_unpack_bit_exact(cake, oracle):
                     assert np.array_equal(got, GOLDEN[key]), key
 
 
+def test_pack_sixteen_byte_path_bit_exact(cake, oracle):
+    """Shapes whose blocks allow 16-byte moves (A: four k at a time for the 6-row panels; B, C: four columns of
+    a 16-wide panel): same bytes as the oracle and as the one-element-per-thread path."""
+    wide = 0
+    for (M, K, N, p) in [(960, 960, 960, 8), (1200, 512, 1024, 4), (1026, 516, 1040, 8), (3000, 3000, 3000, 8)]:
+        A, B, C = oracle.uniform((M, K), 1), oracle.uniform((K, N), 2), oracle.uniform((M, N), 3)
+        for sch in (KMN, MKN, NKM):
+            cx = cake.Cntx.make(*DEFAULT_CACHES)
+            x = cake.init_block_dims(M, N, K, p, cx, sch)
+            got = {}
+            for mode in ("vector", "scalar"):
+                if mode == "scalar":
+                    os.environ["CAKEB200_PACK_SCALAR"] = "1"
+                try:
+                    Ap = cake.pack_A(A, M, K, p, x, cx); wa = cake.last_stats()["tile_k"]
+                    Bp = cake.pack_B(B, K, N, p, x, cx); wb = cake.last_stats()["tile_k"]
+                    Cp = cake.pack_C(C, M, N, p, x, cx); wc = cake.last_stats()["tile_k"]
+                    back = (cake.unpack_A(Ap, M, K, p, x, cx), cake.unpack_B(Bp, K, N, p, x, cx), cake.unpack_C(Cp, M, N, p, x, cx))
+                finally:
+                    os.environ.pop("CAKEB200_PACK_SCALAR", None)
+                got[mode] = (Ap, Bp, Cp)
+                if mode == "vector":
+                    wide += (wa > 1) + (wb > 1) + (wc > 1)
+                else:
+                    assert (wa, wb, wc) == (1, 1, 1)
+                assert np.array_equal(back[0], A) and np.array_equal(back[1], B) and np.array_equal(back[2], C)
+            for i in range(3):
+                assert np.array_equal(got["vector"][i], got["scalar"][i]), ("ABC"[i], M, K, N, p, sch)
+            if M <= 1200:
+                assert np.array_equal(got["vector"][0], oracle.pack(0, A, M, N, K, p, sch))
+                assert np.array_equal(got["vector"][1], oracle.pack(1, B, M, N, K, p, sch))
+                assert np.array_equal(got["vector"][2], oracle.pack(2, C, M, N, K, p, sch))
+    assert wide >= 24, wide  # most of these calls must actually have taken a wide path
+
+
 def test_pack_on_device_pointers(cake, oracle):
     import torch
     M, K, N, p = 500, 300, 700, 8
