@@ -81,6 +81,7 @@ for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
 _SIGNATURES["cakeb200_profile_begin"] = (_i, [])
 _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i)])
 _SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
+_SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
 EXPORTED_SYMBOLS = sorted(_SIGNATURES)
@@ -240,6 +241,23 @@ def cake_sgemm_batched(A, B, C=None, kernel=KERNEL_AUTO, stream=None):
         C = _empty_like_kind(A, (batch, M, N))
     _check(lib().cakeb200_sgemm_batched(_ptr(A), _ptr(B), _ptr(C), M, N, K, batch, kernel, _stream_of(C, stream)))
     return C
+
+
+def cake_sgemv(A, x, y=None, col_major=False, accumulate=False, stream=None):
+    """y (+)= A x (cake_sgemv of reference examples/cake_gemv.cpp:716-765).  ``col_major``: A is given as
+    the (K, M) array whose element [k, m] is A[m, k], the reference driver's layout; otherwise A is (M, K)."""
+    if col_major:
+        K, M = A.shape
+    else:
+        M, K = A.shape
+    if x.shape[0] != K:
+        raise ValueError("vector length differs from the matrix")
+    if y is None:
+        y = _empty_like_kind(A, (M,))
+        accumulate = False
+    _check(lib().cakeb200_sgemv(_ptr(A), _ptr(x), _ptr(y), M, K, int(bool(col_major)), int(bool(accumulate)),
+                                _stream_of(y, stream)))
+    return y
 
 
 def cake_sp_sgemm(A, B, C=None, kernel=KERNEL_FFMA, stream=None):

@@ -620,6 +620,40 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
     return CAKEB200_OK;
 }
 
+int cakeb200_sgemv(const float* A, const float* x, float* y, int M, int K, int col_major, int accumulate, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!A || !x || !y) {
+        set_error("null pointer");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, 1, K)) return CAKEB200_ERR_ARG;
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = (cudaStream_t) stream;
+    Operand oa, ox, oy;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if ((rc = stage_in(st, 0, oa, A, (size_t) M * K * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 1, ox, x, (size_t) K * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oy, y, (size_t) M * 4, accumulate != 0, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    if ((rc = ensure_scratch(st, sgemv_scratch_bytes(M, K, st->sm_count)))) return rc;
+    int launches = 0;
+    if ((rc = launch_sgemv((const float*) oa.dev, (const float*) ox.dev, (float*) oy.dev, M, K, K, col_major, accumulate ? 1 : 0,
+                           st->scratch, st->scratch_bytes, st->sm_count, s, &launches)))
+        return rc;
+    g_stats.launches = launches;
+    g_stats.kernel = CAKEB200_KERNEL_FFMA;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oy, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    CAKE_CUDA_OK(cudaStreamSynchronize(s));
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]);
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
 int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int kernel, void* stream) {
     g_stats = cakeb200_stats();
     if (!A || !B || !C) {

@@ -75,6 +75,10 @@ int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int 
 // batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)
 bool small_tf32x3_fits(int M, int N, int K);
 int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_count, cudaStream_t stream);
+// matrix-vector product (gemv.cu); scratch holds the partial vectors of the K slices
+size_t sgemv_scratch_bytes(int M, int K, int sm_count);
+int launch_sgemv(const float* A, const float* x, float* y, int M, int K, int lda, int col_major, int accumulate,
+                 void* scratch, size_t scratch_bytes, int sm_count, cudaStream_t stream, int* launches);
 // stride-1 convolution as an implicit product (conv_tf32x3.cu); scratch holds the split filter planes
 bool conv_tf32x3_fits(const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad);
 size_t conv_tf32x3_scratch_bytes(int cin, int cout, int hf, int wf);

@@ -443,6 +443,14 @@ double cake_sp_sgemm(float* A, float* B, float* C, int M, int N, int K, int p, c
     return now_s() - t0;
 }
 
+double cake_sgemv(float* A, float* B, float* C, int M, int K, int p, cake_cntx_t* cake_cntx, char* argv[], bool packedA,
+                  float alpha, float beta, enum sched sch) {
+    (void) p; (void) cake_cntx; (void) argv; (void) packedA; (void) alpha; (void) beta; (void) sch;
+    const double t0 = now_s();
+    if (cakeb200_sgemv(A, B, C, M, K, 1, 1, nullptr)) return fail("cake_sgemv");
+    return now_s() - t0;
+}
+
 double cake_sconv_im2col(float* in, float* filters, float* out, int batch, int Cin, int H, int W, int Cout, int Hf,
                          int Wf, int stride, int pad, int p, cake_cntx_t* cake_cntx) {
     (void) p; (void) cake_cntx;

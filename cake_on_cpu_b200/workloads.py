@@ -107,6 +107,18 @@ def _conv(b, cin, hw, cout):
     return run
 
 
+def _gemv(M, K, col_major):
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        A = _uniform(g, K, M) if col_major else _uniform(g, M, K)
+        x, y = _uniform(g, K), torch.empty(M, device="cuda")
+        ms = _timed(lambda: api.cake_sgemv(A, x, y, col_major=col_major), reps)
+        nbytes = 4.0 * M * K
+        return {"ms": ms, "kernel_ms": api.last_stats()["ms_gemm"], "bytes": nbytes, "gbs": nbytes / ms / 1e6, "bound": "hbm",
+                "frac": nbytes / ms / 1e6 / HBM_GBS, "layout": "column-major" if col_major else "row-major"}
+    return run
+
+
 def _pack(n, which):
     def run(reps):
         g = torch.Generator(device="cuda").manual_seed(1)
@@ -142,6 +154,9 @@ for _d, _name in ((0.5, "50"), (0.1, "10"), (0.01, "1")):
     CONFIGS["sparse_%s_zero_skipping" % _name] = _sparse(8192, _d, api.KERNEL_FFMA)
 CONFIGS["conv_64x64x56"] = _conv(64, 64, 56, 64)
 CONFIGS["conv_256x512x14"] = _conv(64, 256, 14, 512)
+CONFIGS["gemv_16384_col_major"] = _gemv(16384, 16384, True)
+CONFIGS["gemv_16384_row_major"] = _gemv(16384, 16384, False)
+CONFIGS["gemv_1024x262144_col_major"] = _gemv(1024, 262144, True)
 CONFIGS["pack_A_8192"] = _pack(8192, "A")
 CONFIGS["pack_B_8192"] = _pack(8192, "B")
 CONFIGS["unpack_C_8192"] = _pack(8192, "C")

@@ -131,6 +131,13 @@ double cake_sgemm_small_batched(float* A, float* B, float* C, int M, int N, int 
 double cake_sp_sgemm(float* A, float* B, float* C, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
                      float density_hint = -1.0f);
 
+/* Matrix-vector product of the reference's driver (examples/cake_gemv.cpp:7-9, 716-765), same
+ * signature: A is column-major (A[k*M + m]), B is the vector of length K, and C (length M) is
+ * added to, as the reference's microkernel does with the C it is handed.  argv, packedA, alpha,
+ * beta and sch are accepted and ignored, as there. */
+double cake_sgemv(float* A, float* B, float* C, int M, int K, int p, cake_cntx_t* cake_cntx, char* argv[] = NULL,
+                  bool packedA = 0, float alpha = 1, float beta = 0, enum sched sch = NA);
+
 /* Convolution through im2col + SGEMM (reference examples/cake_conv.cpp:1007-1066).
  * in: [batch][Cin][H][W], filters: [Cout][Cin][Hf][Wf], out: [batch][Cout][Ho][Wo]. */
 double cake_sconv_im2col(float* in, float* filters, float* out, int batch, int Cin, int H, int W, int Cout,

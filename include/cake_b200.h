@@ -139,6 +139,14 @@ int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls);
 int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K,
                            int batch, int kernel, void* stream);
 
+/* y (+)= A x for an M x K matrix.  col_major != 0: A[k*M + m], the layout of the
+ * reference's matrix-vector driver; else row-major A[m*K + k], the N = 1 case of
+ * cake_sgemm.  accumulate != 0 adds to y, which is what the reference's driver
+ * does with the C it is handed.  Replaces cake_sgemv / schedule_mvm and the
+ * 8 x 8 microkernel (reference examples/cake_gemv.cpp:87-140, 424-489, 716-765). */
+int cakeb200_sgemv(const float* A, const float* x, float* y, int M, int K, int col_major,
+                   int accumulate, void* stream);
+
 /* C = A*B where A is mostly zero: A is compacted on the device to a per-row
  * list of (column, value) and only the nonzeros are multiplied.  Replaces the
  * sparse microkernel cake_sp_sgemm_haswell_6x16 (reference

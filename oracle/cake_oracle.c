@@ -593,6 +593,23 @@ void oracle_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int
     }
 }
 
+/* cake_sgemv of the reference's matrix-vector example: schedule_mvm
+ * (examples/cake_gemv.cpp:424-489) walks blocks of rows and, inside, blocks of k in
+ * ascending order, and its microkernel cake_sgemv_haswell_8x8_col (:87-140) loads C,
+ * issues c = fma(A[k*M + m], B[k], c) for k ascending and stores C.  Per output
+ * element that is one chain of fused multiply-adds over k = 0 .. K-1 on top of the
+ * value C held on entry; A is column-major (A[k*M + m]).  parity unpinned: the
+ * example is a stand-alone program with its own main and is not part of the
+ * reference library, so this restatement is checked against float64 only. */
+void oracle_sgemv(const float* A, const float* B, float* C, int M, int K) {
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; m++) {
+        float c = C[m];
+        for (int k = 0; k < K; k++) c = __builtin_fmaf(A[(size_t) k * M + m], B[k], c);
+        C[m] = c;
+    }
+}
+
 /* --------------------------------------------------------------- generators */
 
 static inline uint64_t splitmix64(uint64_t z) {

@@ -90,6 +90,10 @@ void oracle_sgemm_batched(const float* A, const float* B, float* C, int M, int N
  * reference's sparse microkernel (zero entries of A contribute no operation). */
 void oracle_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K);
 
+/* C[m] += sum_k A[k*M + m] * B[k], one fused multiply-add chain per element over ascending k
+ * (reference examples/cake_gemv.cpp:87-140, 424-489).  parity unpinned (see the .c file). */
+void oracle_sgemv(const float* A, const float* B, float* C, int M, int K);
+
 /* seeded generators shared by tests and benches (counter based, stateless) */
 void oracle_fill_uniform(float* x, size_t n, unsigned long long seed);
 void oracle_fill_normal(float* x, size_t n, unsigned long long seed, float sigma);

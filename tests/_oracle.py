@@ -63,6 +63,7 @@ class Oracle:
         L.oracle_conv2d.argtypes = [_fp, _fp, _fp] + [_c_int] * 10 + [ctypes.POINTER(OracleCntx)]
         L.oracle_sgemm_batched.argtypes = [_fp, _fp, _fp] + [_c_int] * 5 + [ctypes.POINTER(OracleCntx)]
         L.oracle_sp_sgemm.argtypes = [_fp, _fp, _fp] + [_c_int] * 3
+        L.oracle_sgemv.argtypes = [_fp, _fp, _fp] + [_c_int] * 2
         L.oracle_fill_uniform.argtypes = [_fp, _sz, ctypes.c_ulonglong]
         L.oracle_fill_normal.argtypes = [_fp, _sz, ctypes.c_ulonglong, _c_f]
         L.oracle_fill_sparse.argtypes = [_fp, _sz, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_double]
@@ -143,6 +144,13 @@ class Oracle:
         C = np.zeros((M, N), np.float32)
         self.L.oracle_sp_sgemm(_f(A), _f(B), _f(C), M, N, K)
         return C
+
+    def sgemv(self, A_colmajor, x, y0=None):
+        """y0 + A x with A stored column-major as a (K, M) array (reference examples/cake_gemv.cpp)."""
+        K, M = A_colmajor.shape
+        y = np.zeros(M, np.float32) if y0 is None else np.array(y0, np.float32)
+        self.L.oracle_sgemv(_f(A_colmajor), _f(x), _f(y), M, K)
+        return y
 
     def uniform(self, shape, seed):
         x = np.empty(shape, np.float32)

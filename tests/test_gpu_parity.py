@@ -423,6 +423,37 @@ def test_batched_small_on_tensor_cores(cake, oracle):
         cake.cake_sgemm_batched(oracle.uniform((2, 130, 8), 1), oracle.uniform((2, 8, 8), 2), kernel=cake.KERNEL_TF32X3)
 
 
+def test_matrix_vector_product(cake, oracle):
+    """cake_sgemv: the reference driver's column-major layout (accumulating into y, as its microkernel does) and
+    the row-major N = 1 case, against the oracle's fused-multiply-add chain and float64.  Shapes cover one K
+    slice and many, row counts off the 4- and 1024-grids, and rows that cannot be read 16 bytes at a time."""
+    import torch
+    for (M, K) in [(8, 8), (1000, 77), (4096, 4096), (17, 5000), (1022, 333), (20000, 130), (64, 100000)]:
+        A = oracle.uniform((K, M), 1)   # column-major storage of the M x K matrix
+        x = oracle.uniform((K,), 2)
+        y0 = oracle.uniform((M,), 3)
+        want = oracle.sgemv(A, x, y0)
+        ref64 = y0.astype(np.float64) + A.astype(np.float64).T @ x.astype(np.float64)
+        scale = np.linalg.norm(A, axis=0) * np.linalg.norm(x)
+        y = y0.copy()
+        cake.cake_sgemv(A, x, y, col_major=True, accumulate=True)
+        assert (np.abs(y - want) / scale).max() <= TOL, (M, K)
+        assert (np.abs(y - ref64) / scale).max() <= TOL
+        # device pointers, no accumulation
+        dy = cake.cake_sgemv(torch.from_numpy(A).cuda(), torch.from_numpy(x).cuda(), col_major=True).cpu().numpy()
+        assert (np.abs(dy - (ref64 - y0)) / scale).max() <= TOL
+        # row-major
+        Ar = np.ascontiguousarray(A.T)
+        yr = cake.cake_sgemv(Ar, x)
+        assert (np.abs(yr - (ref64 - y0)) / scale).max() <= TOL
+        yr2 = y0.copy()
+        cake.cake_sgemv(Ar, x, yr2, accumulate=True)
+        assert (np.abs(yr2 - ref64) / scale).max() <= TOL
+    # twice the same call gives the same bits (fixed summation order)
+    A, x = oracle.uniform((3000, 2000), 1), oracle.uniform((3000,), 2)
+    assert np.array_equal(cake.cake_sgemv(A, x, col_major=True), cake.cake_sgemv(A, x, col_major=True))
+
+
 def test_errors_are_status_codes(cake):
     A = np.zeros((4, 4), np.float32)
     with pytest.raises(ValueError):
