@@ -69,7 +69,8 @@ struct Tf32x3Args {
     int M, N, K;
     int ldc;
     int tiles_m, tiles_n;
-    int kblocks;             // ceil(K / BK)
+    int kblocks;             // 32-deep slices of K of this launch
+    int kb_first;            // first slice (a deep product is run as several launches over ranges of K)
     int order, band;         // tile walk, see tile_coords
     int accumulate;          // for tiles stored straight to C
     int out_p;               // > 0: N axis is (image, position), see GemmProblem::out_p
@@ -87,7 +88,7 @@ __device__ __forceinline__ bool work_piece(const Tf32x3Args& a, int it, WorkPiec
     const int g = (int) gridDim.x, b = (int) blockIdx.x;
     const int whole = (b < a.dp_tiles) ? (a.dp_tiles - b + g - 1) / g : 0;
     if (it < whole) {
-        w.tile = b + it * g; w.kb0 = 0; w.kb1 = a.kblocks; w.slot = -1;
+        w.tile = b + it * g; w.kb0 = a.kb_first; w.kb1 = a.kb_first + a.kblocks; w.slot = -1;
         return true;
     }
     if (a.units == nullptr) return false;
@@ -752,6 +753,7 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_m = (g.M + BM - 1) / BM;
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
+    a.kb_first = 0;
     a.order = g.order;
     a.band = band_for(g.order, a.tiles_m, a.tiles_n, BN, sm_count);
     a.accumulate = g.accumulate;
@@ -773,6 +775,26 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
         grid = (int) std::min<long long>(tiles, sm_count);
     }
     CAKE_CUDA_OK(cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+    // A very deep product with many tiles is run as several launches over ranges of K, each adding to C.
+    // Within one launch the CTAs of a wave share their A and B panels through L2 only while they work on
+    // nearby slices of K; over thousands of slices they drift apart and the panels come from DRAM once per
+    // CTA (32768^3: 400 ms in one launch, 313 ms in ranges of 8192, at the cost of re-reading C three times).
+    const int total_kb = a.kblocks;
+    const int range_kb = (total_kb > 512 && tiles >= 4LL * sm_count && g.out_p == 0) ? 256 : total_kb;
+    if (range_kb < total_kb) {
+        a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
+        grid = (int) std::min<long long>(tiles, sm_count);
+        for (int first = 0; first < total_kb; first += range_kb) {
+            a.kb_first = first;
+            a.kblocks = std::min(range_kb, total_kb - first);
+            a.accumulate = (first > 0) ? 1 : g.accumulate;
+            a.bias = (first > 0) ? nullptr : g.bias;
+            sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
+            CAKE_CUDA_OK(cudaGetLastError());
+            if (launches) (*launches)++;
+        }
+        return CAKEB200_OK;
+    }
     sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
     CAKE_CUDA_OK(cudaGetLastError());
     if (launches) (*launches)++;

@@ -40,6 +40,24 @@ def test_rectangular_and_reference_cpu_shapes(cake, shape, want):
     assert ((C[rows] - Cf[rows]).double().abs() / den).max().item() <= TOL
 
 
+def test_deep_product_runs_in_ranges_of_k(cake):
+    """A product deeper than 16384 with several waves of tiles is issued as launches over ranges of K that add
+    to C (with a bias added once and with accumulation on top of an existing C): float64 on sampled rows."""
+    import torch
+    M, K, N = 4096, 16416 + 7, 4864
+    g = torch.Generator(device="cuda").manual_seed(2)
+    A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
+    B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
+    bias = torch.rand((N,), device="cuda", generator=g)
+    C = torch.full((M, N), float("nan"), device="cuda")
+    cake.cake_sgemm_ex(A, B, C, bias=bias, kernel=cake.KERNEL_TF32X3)
+    assert cake.last_stats()["launches"] == 2 + 3  # two split kernels, three ranges of K
+    rows = np.random.default_rng(1).integers(0, M, 32)
+    assert _sample_err(A, B, C - bias[None, :], rows) <= TOL
+    cake.cake_sgemm_ex(A, B, C, accumulate=True, kernel=cake.KERNEL_TF32X3)
+    assert _sample_err(A, B, (C - bias[None, :]) / 2, rows) <= TOL
+
+
 def test_batch_of_4096_small_products(cake):
     import torch
     g = torch.Generator(device="cuda").manual_seed(1)
