@@ -3,8 +3,10 @@
 // The reference computes a convolution as im2col followed by one cake_sgemm
 // (examples/cake_conv.cpp:1007-1066 with im_2_col at :1178-1213): the patch matrix is
 // written out, packed and multiplied.  Here the patch matrix never exists, neither in
-// HBM nor as TF32 planes.  A tile is up to 128 output positions (whole output rows of one
-// image) times up to 128 output channels.  For each group of 32 input channels one TMA
+// HBM nor as TF32 planes.  A tile is up to 128 output positions times up to 128 output
+// channels; the positions are whole output rows of one image or, when that saves a round
+// of tiles on the machine, a run of 128 consecutive positions of the whole batch (which can
+// start in the middle of a row and continue into the next images: one input box per image).  For each group of 32 input channels one TMA
 // box brings the input rows those positions need into shared memory (rows above and below
 // the image arrive as zeros), and for every filter tap (fh, fw) the producer warps build
 // the 128 x 32 operand tile "position x channel" from that box -- a shifted window, read
@@ -64,13 +66,18 @@ struct ConvArgs {
     float* out;
     const float* bias;
     int batch, cin, H, W, cout, hf, wf, pad, Ho, Wo;
-    int rows_per_tile;   // output rows of one image per tile
-    int groups;          // tiles per image along the rows
+    int flat;            // tiles are runs of 128 positions of the whole batch (else whole rows of one image)
+    int rows_per_tile;   // row tiles: output rows of one image per tile
+    int groups;          // row tiles: tiles per image
+    int plane;           // Ho * Wo
+    long long positions; // batch * plane
+    int segs;            // images a tile can touch (1 for row tiles): input boxes per raw stage
+    int box_bytes;       // one input box: box_w * 32 * 4
     int bn, ntiles;      // output channels per tile, tiles along the channels
     int ncg;             // groups of 32 input channels
     int kblocks;         // ncg * hf * wf
     int box_w;           // floats per channel in an input box
-    int raw_bytes;       // box_w * 32 * 4
+    int raw_bytes;       // one raw stage: segs * box_bytes
     int b_plane;         // bytes of one filter plane per stage: bn * 128
     int stage_bytes;     // 2 * b_plane (the patch operand of a stage lives in tensor memory)
     int a_col0;          // first tensor-memory column of the patch operand ring
@@ -98,6 +105,44 @@ split_filters_kernel(const float* __restrict__ F, float* __restrict__ hi, float*
         hi[i] = h;
         lo[i] = l;
     }
+}
+
+// The positions of a tile come from up to three images: a segment is a run of consecutive positions
+// [p0, p0 + n) of image img, served by one input box that starts at the (16-byte aligned) beginning of
+// the first input row the run needs.
+struct Seg {
+    int img, p0, n, x_al, dx;
+};
+__device__ __forceinline__ int tile_segments(const ConvArgs& a, long long tile, Seg* seg, int& nt, int& npos) {
+    nt = (int) (tile % a.ntiles);
+    const long long mt = tile / a.ntiles;
+    int count = 0;
+    if (a.flat) {
+        long long fp = mt * BM;
+        npos = (int) min((long long) BM, a.positions - fp);
+        int left = npos;
+        while (left > 0 && count < 3) {
+            Seg& s = seg[count++];
+            s.img = (int) (fp / a.plane);
+            s.p0 = (int) (fp - (long long) s.img * a.plane);
+            s.n = min(left, a.plane - s.p0);
+            fp += s.n;
+            left -= s.n;
+        }
+    } else {
+        const int oh0 = (int) (mt % a.groups) * a.rows_per_tile;
+        npos = min(a.rows_per_tile, a.Ho - oh0) * a.Wo;
+        seg[0].img = (int) (mt / a.groups);
+        seg[0].p0 = oh0 * a.Wo;
+        seg[0].n = npos;
+        count = 1;
+    }
+    for (int i = 0; i < count; i++) {
+        const int x = (seg[i].p0 / a.Wo - a.pad) * a.W;  // first input row of the run, as an index into the image plane
+        seg[i].dx = ((x % 4) + 4) % 4;                   // TMA needs a 16-byte aligned start; the remainder is added when reading
+        seg[i].x_al = x - seg[i].dx;
+    }
+    return count;
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -149,13 +194,6 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // tile index -> (image, first output row, channel tile); channel tiles of one patch of positions are neighbours
-    auto decode = [&](long long tile, int& img, int& oh0, int& nt) {
-        nt = (int) (tile % a.ntiles);
-        const long long rest = tile / a.ntiles;
-        oh0 = (int) (rest % a.groups) * a.rows_per_tile;
-        img = (int) (rest / a.groups);
-    };
     const int taps = a.hf * a.wf;
 
     if (warp == 0) {
@@ -210,18 +248,19 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < a.tiles; tile += gridDim.x) {
-                int img, oh0, nt;
-                decode(tile, img, oh0, nt);
-                const int x = (oh0 - a.pad) * a.W;
-                const int x_al = x - (((x % 4) + 4) % 4);  // TMA needs a 16-byte aligned start; the remainder is added when reading
+                Seg seg[3];
+                int nt, npos;
+                const int nseg = tile_segments(a, tile, seg, nt, npos);
                 for (int g = 0; g < a.ncg; g++) {
                     TIMER_DECL;
                     TIMER_START();
                     ok = mbar_wait(raw_empty_bar(r), phase ^ 1, abort_flag, a.status_word, 500 + r);
                     TIMER_ADD(3);
                     if (!ok) break;
-                    mbar_expect_tx(raw_full_bar(r), (uint32_t) a.raw_bytes);
-                    tma_load_3d(smem_u32(raws + r * a.raw_bytes), &map_in, x_al, g * 32, img, raw_full_bar(r));
+                    mbar_expect_tx(raw_full_bar(r), (uint32_t) (nseg * a.box_bytes));
+                    for (int i = 0; i < nseg; i++)
+                        tma_load_3d(smem_u32(raws + r * a.raw_bytes + i * a.box_bytes), &map_in, seg[i].x_al, g * 32, seg[i].img,
+                                    raw_full_bar(r));
                     if (++r == R) { r = 0; phase ^= 1; }
                 }
             }
@@ -240,8 +279,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < a.tiles; tile += gridDim.x) {
-                int img, oh0, nt;
-                decode(tile, img, oh0, nt);
+                const int nt = (int) (tile % a.ntiles);
                 for (int kb = 0; kb < a.kblocks; kb++) {
                     TIMER_DECL;
                     TIMER_START();
@@ -272,9 +310,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
         int local = 0;
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < a.tiles; tile += gridDim.x, local++) {
-            int img, oh0, nt;
-            decode(tile, img, oh0, nt);
-            const int npos = min(a.rows_per_tile, a.Ho - oh0) * a.Wo;
+            Seg seg[3];
+            int nt, npos;
+            const int nseg = tile_segments(a, tile, seg, nt, npos);
             const int buf = local & 1;
             TIMER_DECL;
             TIMER_START();
@@ -292,7 +330,11 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
                 continue;
             }
             const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * a.acc_stride);
-            float* dst0 = a.out + ((long long) img * a.cout) * plane + (long long) oh0 * a.Wo + pos;
+            // this thread's position: which image, where in its plane
+            float* dst0 = a.out;
+            for (int i = 0, first = 0; i < nseg; first += seg[i].n, i++)
+                if (pos >= first && pos < first + seg[i].n)
+                    dst0 = a.out + ((long long) seg[i].img * a.cout) * plane + seg[i].p0 + (pos - first);
             float v[32];
 #pragma unroll 1
             for (int c = 0; c < chunks; c++) {
@@ -330,14 +372,21 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
         long long kcount = 0, rcount = 0;  // slices and input boxes consumed so far by this CTA
         bool ok = true;
         for (long long tile = blockIdx.x; ok && tile < a.tiles; tile += gridDim.x) {
-            int img, oh0, nt;
-            decode(tile, img, oh0, nt);
-            const int npos = min(a.rows_per_tile, a.Ho - oh0) * a.Wo;
-            const int x = (oh0 - a.pad) * a.W;
-            const int dx = ((x % 4) + 4) % 4;
-            const int prow = pos / a.Wo, ow = pos - prow * a.Wo;
-            const int lin0 = prow * a.W + ow - a.pad + dx;  // index in the box of tap (0, 0)
+            Seg seg[3];
+            int nt, npos;
+            const int nseg = tile_segments(a, tile, seg, nt, npos);
+            // this thread's position: which box, and where in it tap (0, 0) of the position lies
             const bool live = pos < npos;
+            int ow = 0, lin0 = 0;
+            uint32_t box_off = 0;
+            for (int i = 0, first = 0; i < nseg; first += seg[i].n, i++)
+                if (pos >= first && pos < first + seg[i].n) {
+                    const int p = seg[i].p0 + (pos - first);
+                    const int oh = p / a.Wo;
+                    ow = p - oh * a.Wo;
+                    lin0 = (oh - seg[i].p0 / a.Wo) * a.W + ow - a.pad + seg[i].dx;
+                    box_off = (uint32_t) (i * a.box_bytes);
+                }
             for (int g = 0; ok && g < a.ncg; g++, rcount++) {
                 const int r = (int) (rcount % R);
                 const uint32_t raw_phase = (uint32_t) ((rcount / R) & 1);
@@ -368,7 +417,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
                         const int fh = tap / a.wf, fw = tap - fh * a.wf;
                         const int col = ow - a.pad + fw;
                         const bool inside = live && col >= 0 && col < a.W;
-                        const uint32_t src = smem_u32(raws + r * a.raw_bytes) + (uint32_t) (lin0 + fh * a.W + fw) * 4u;
+                        const uint32_t src = smem_u32(raws + r * a.raw_bytes) + box_off + (uint32_t) (lin0 + fh * a.W + fw) * 4u;
                         // this thread's lane of tensor memory is its position; columns are the 32 channels, hi then lo
                         const uint32_t dst = tmem_base + ((uint32_t) (pos & ~31) << 16) + (uint32_t) (a.a_col0 + stage * A_COLS);
 #pragma unroll
@@ -415,28 +464,14 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_cons
     }
 }
 
-// Geometry of the launch; returns false when the convolution does not fit this kernel.
-bool plan(ConvArgs& a, const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad) {
-    if (stride != 1) return false;
-    a.batch = batch; a.cin = cin; a.H = H; a.W = W; a.cout = cout; a.hf = hf; a.wf = wf; a.pad = pad;
-    a.Ho = H + 2 * pad - hf + 1;
-    a.Wo = W + 2 * pad - wf + 1;
-    if (a.Ho < 1 || a.Wo < 1 || a.Wo > BM) return false;
-    if (((long long) H * W) % 4 != 0 || ((uintptr_t) in) % 16 != 0) return false;  // TMA: channel stride in 16-byte units
-    if ((long long) H * W * 4 >= (1LL << 32) || (long long) cin * H * W * 4 >= (1LL << 40)) return false;
-    // rows per tile: at most 128 positions, and the box of input rows (+3 floats of alignment slack) at most 256 floats
-    int rows = std::min(a.Ho, BM / a.Wo);
-    rows = std::min(rows, 253 / W - hf + 1);
-    if (rows < 1) return false;
-    a.rows_per_tile = rows;
-    a.groups = (a.Ho + rows - 1) / rows;
-    a.bn = cout >= 128 ? 128 : (cout + 15) / 16 * 16;
-    a.ntiles = (cout + a.bn - 1) / a.bn;
-    a.ncg = (cin + 31) / 32;
-    a.kblocks = a.ncg * hf * wf;
-    a.box_w = ((rows + hf - 1) * W + 3 + 3) / 4 * 4;
-    if (a.box_w > 256) return false;
-    a.raw_bytes = a.box_w * 32 * 4;
+// Shared-memory and tensor-memory layout for a tiling whose tiles touch `segs` images and need
+// `rows` input-row spans per image; false when it does not fit.
+bool layout(ConvArgs& a, int segs, int span_rows) {
+    a.segs = segs;
+    a.box_w = ((span_rows + a.hf - 1) * a.W + 3 + 3) / 4 * 4;  // +3 floats of alignment slack, rounded to 16 bytes
+    if (a.box_w > 256) return false;                            // TMA boxes hold at most 256 elements per dimension
+    a.box_bytes = a.box_w * 32 * 4;
+    a.raw_bytes = segs * a.box_bytes;
     a.b_plane = a.bn * 128;
     a.stage_bytes = 2 * a.b_plane;
     const int fixed = 1024 + 256;
@@ -446,17 +481,66 @@ bool plan(ConvArgs& a, const float* in, int batch, int cin, int H, int W, int co
     a.tmem_cols = 512;
     a.stages = std::min(6, (a.tmem_cols - a.a_col0) / A_COLS);
     a.ring = std::min(MAX_RING, (MAX_SMEM - fixed - a.stages * a.stage_bytes) / a.raw_bytes);
-    if (a.ring < 2 || a.stages < 2) return false;
+    while (a.ring < 2 && a.stages > 2) {  // trade a split stage for input boxes
+        a.stages--;
+        a.ring = std::min(MAX_RING, (MAX_SMEM - fixed - a.stages * a.stage_bytes) / a.raw_bytes);
+    }
+    return a.ring >= 2 && a.stages >= 2;
+}
+
+// Geometry of the launch; returns false when the convolution does not fit this kernel.
+bool plan(ConvArgs& a, const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad,
+          int sm_count) {
+    if (stride != 1) return false;
+    a.batch = batch; a.cin = cin; a.H = H; a.W = W; a.cout = cout; a.hf = hf; a.wf = wf; a.pad = pad;
+    a.Ho = H + 2 * pad - hf + 1;
+    a.Wo = W + 2 * pad - wf + 1;
+    if (a.Ho < 1 || a.Wo < 1 || a.Wo > BM) return false;
+    if (((long long) H * W) % 4 != 0 || ((uintptr_t) in) % 16 != 0) return false;  // TMA: channel stride in 16-byte units
+    if ((long long) H * W * 4 >= (1LL << 32) || (long long) cin * H * W * 4 >= (1LL << 40)) return false;
+    a.plane = a.Ho * a.Wo;
+    a.positions = (long long) batch * a.plane;
+    a.bn = cout >= 128 ? 128 : (cout + 15) / 16 * 16;
+    a.ntiles = (cout + a.bn - 1) / a.bn;
+    a.ncg = (cin + 31) / 32;
+    a.kblocks = a.ncg * hf * wf;
     a.idesc = make_idesc_tf32(BM, a.bn);
-    a.tiles = (long long) batch * a.groups * a.ntiles;
-    return true;
+
+    // (a) tiles of whole output rows of one image: at most 128 positions, input box at most 256 floats
+    int rows = std::min(a.Ho, BM / a.Wo);
+    rows = std::min(rows, 253 / W - hf + 1);
+    const bool rows_ok = rows >= 1;
+    const long long row_tiles = rows_ok ? (long long) batch * ((a.Ho + rows - 1) / rows) * a.ntiles : 0;
+    // (b) tiles of 128 consecutive positions of the whole batch: full tiles whatever Ho * Wo is, but a run of
+    // 128 positions can start in the middle of a row and cross into the next images
+    const int span = std::min(a.Ho, (BM + a.Wo - 2) / a.Wo + 1);
+    const int segs = a.plane >= BM ? 2 : a.plane >= BM / 2 ? 3 : 0;  // images a run of 128 positions can touch
+    const long long flat_tiles = (a.positions + BM - 1) / BM * a.ntiles;
+    ConvArgs f = a;
+    f.flat = 1;
+    const bool flat_ok = segs > 0 && getenv("CAKEB200_CONV_ROWS") == nullptr && layout(f, segs, span);
+    // flat tiles when they save a round of tiles on the machine (or when row tiles do not fit at all)
+    const long long sms = std::max(sm_count, 1);
+    const bool take_flat = flat_ok && (!rows_ok || getenv("CAKEB200_CONV_FLAT") != nullptr ||
+                                       (flat_tiles + sms - 1) / sms < (row_tiles + sms - 1) / sms);
+    if (take_flat) {
+        a = f;
+        a.tiles = flat_tiles;
+        return true;
+    }
+    if (!rows_ok) return false;
+    a.flat = 0;
+    a.rows_per_tile = rows;
+    a.groups = (a.Ho + rows - 1) / rows;
+    a.tiles = row_tiles;
+    return layout(a, 1, rows);
 }
 
 }  // namespace
 
 bool conv_tf32x3_fits(const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad) {
     ConvArgs a = {};
-    return plan(a, in, batch, cin, H, W, cout, hf, wf, stride, pad);
+    return plan(a, in, batch, cin, H, W, cout, hf, wf, stride, pad, 148);
 }
 
 size_t conv_tf32x3_scratch_bytes(int cin, int cout, int hf, int wf) {
@@ -469,7 +553,7 @@ int launch_conv_tf32x3(const float* in, const float* filters, float* out, const 
                        int W, int cout, int hf, int wf, int pad, void* scratch, size_t scratch_bytes, int* status_word,
                        int sm_count, cudaStream_t stream, int* launches) {
     ConvArgs a = {};
-    if (!plan(a, in, batch, cin, H, W, cout, hf, wf, 1, pad)) {
+    if (!plan(a, in, batch, cin, H, W, cout, hf, wf, 1, pad, sm_count)) {
         set_error("conv_tf32x3: this geometry is not covered by the implicit kernel");
         return CAKEB200_ERR_ARG;
     }

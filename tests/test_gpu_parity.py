@@ -359,6 +359,14 @@ def test_implicit_convolution_geometries(cake, oracle):
         st = cake.last_stats()
         assert st["kernel"] == cake.KERNEL_TF32X3
         assert (st["launches"] == 2) == implicit, (b, cin, H, W, cout, hf, wf, pad, st)
+        # both tilings of the implicit kernel (whole rows of one image; runs of 128 positions across images)
+        for force in ("CAKEB200_CONV_ROWS", "CAKEB200_CONV_FLAT"):
+            os.environ[force] = "1"
+            try:
+                other = cake.cake_conv2d(x, w, 1, pad, kernel=cake.KERNEL_TF32X3)
+            finally:
+                os.environ.pop(force, None)
+            assert np.abs(other - out).max() <= 1e-4 * max(1.0, np.abs(out).max()), (force, b, cin, H, W, cout)
         ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=pad).numpy()
         assert out.shape == ref.shape
         col = oracle.im2col(x, hf, wf, 1, pad)
