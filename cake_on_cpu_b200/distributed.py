@@ -1,5 +1,9 @@
 """One product over the GPUs of a box, one process per GPU (torch.distributed, NCCL).
 
+The batched, sparse and convolution entry points shard by their independent units
+(products of the batch, row blocks of the sparse operand, images): every rank
+calls the library on its share and nothing is exchanged.
+
 Rows (or columns) of C are independent, so each rank multiplies its block with
 the library and nothing is exchanged.  Only the deep-K shape is different: K is
 cut, every rank produces a full-size partial product, and the partials are
@@ -53,3 +57,36 @@ def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
     r0, r1 = partition.row_block(M, world, rank)
     block, span = reduce_scatter(partial, r0, r1)
     return kind, span, block
+
+
+def _rank_world(group):
+    if dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def sharded_sgemm_batched(A, B, kernel=api.KERNEL_AUTO, group=None):
+    """A (batch x M x K), B (batch x K x N) present on every rank.  Returns ((lo, hi), C[lo:hi])."""
+    rank, world = _rank_world(group)
+    lo, hi = partition.unit_block(A.shape[0], world, rank)
+    if hi == lo:
+        return (lo, hi), torch.empty((0, A.shape[1], B.shape[2]), dtype=torch.float32, device=A.device)
+    return (lo, hi), api.cake_sgemm_batched(A[lo:hi].contiguous(), B[lo:hi].contiguous(), kernel=kernel)
+
+
+def sharded_sp_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
+    """Sparse A (M x K) and dense B present on every rank: row blocks of A.  Returns ((r0, r1), C[r0:r1])."""
+    rank, world = _rank_world(group)
+    r0, r1 = partition.row_block(A.shape[0], world, rank)
+    if r1 == r0:
+        return (r0, r1), torch.empty((0, B.shape[1]), dtype=torch.float32, device=A.device)
+    return (r0, r1), api.cake_sp_sgemm(A[r0:r1].contiguous(), B.contiguous(), kernel=kernel)
+
+
+def sharded_conv2d(x, w, stride=1, pad=0, kernel=api.KERNEL_AUTO, group=None):
+    """Input x (batch x Cin x H x W) and filters present on every rank: images.  Returns ((lo, hi), out[lo:hi])."""
+    rank, world = _rank_world(group)
+    lo, hi = partition.unit_block(x.shape[0], world, rank)
+    if hi == lo:
+        return (lo, hi), None
+    return (lo, hi), api.cake_conv2d(x[lo:hi].contiguous(), w.contiguous(), stride, pad, kernel=kernel)

@@ -41,6 +41,12 @@ def k_block(K, world, rank, tile=32):
     return min(lo, K), (K if rank == world - 1 else min(hi, K))
 
 
+def unit_block(units, world, rank):
+    """[lo, hi) of `units` independent items (products of a batch, images of a convolution) owned by
+    `rank`, balanced to within one item."""
+    return (units * rank) // world, (units * (rank + 1)) // world
+
+
 def grid_shape(M, N, K, world):
     """(pr, pc), pr * pc == world: the process grid with the least time per rank.
 

@@ -44,8 +44,23 @@ def _worker(rank, world, port, out, cases=TWO_RANK_CASES):
             cut = lambda X: X[span[0]:span[1]]
         err = ((block.double() - cut(full)).abs() / cut(den)).max().item() if block.shape == cut(full).shape else float("inf")
         results.append((kind == want, err, span[0], span[1], block.numel()))
+    # independent units: batch items, row blocks of a sparse operand, images of a convolution
+    g = torch.Generator(device="cuda").manual_seed(6)
+    Ab = torch.rand((37, 96, 64), device="cuda", generator=g) * 2 - 1
+    Bb = torch.rand((37, 64, 80), device="cuda", generator=g) * 2 - 1
+    (lo, hi), Cb = distributed.sharded_sgemm_batched(Ab, Bb)
+    err_b = (Cb.double() - torch.bmm(Ab[lo:hi].double(), Bb[lo:hi].double())).abs().max().item()
+    As = (torch.rand((700, 512), device="cuda", generator=g) * 2 - 1) * (torch.rand((700, 512), device="cuda", generator=g) < 0.02)
+    Bs = torch.rand((512, 384), device="cuda", generator=g) * 2 - 1
+    (r0, r1), Cs = distributed.sharded_sp_sgemm(As, Bs)
+    err_s = (Cs.double() - As[r0:r1].double() @ Bs.double()).abs().max().item()
+    x = torch.randn((9, 16, 12, 12), device="cuda", generator=g) * 0.1
+    w = torch.randn((24, 16, 3, 3), device="cuda", generator=g) * 0.1
+    (i0, i1), y = distributed.sharded_conv2d(x, w, 1, 1)
+    err_c = (y.double() - torch.nn.functional.conv2d(x[i0:i1].double(), w.double(), padding=1)).abs().max().item()
+    units = (hi - lo, r1 - r0, i1 - i0, err_b, err_s, err_c)
     gathered = [None] * world
-    dist.all_gather_object(gathered, results)
+    dist.all_gather_object(gathered, (results, units))
     if rank == 0:
         out.put(gathered)
     dist.barrier()
@@ -67,6 +82,8 @@ def test_two_ranks_nccl(cake):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    units = [u for _, u in res]
+    res = [r for r, _ in res]
     for per_rank in res:
         for ok_kind, err, lo, hi, _ in per_rank:
             assert ok_kind
@@ -74,6 +91,9 @@ def test_two_ranks_nccl(cake):
     # the two ranks' blocks tile the matrix
     for case in range(len(res[0])):
         assert res[0][case][2] == 0 and res[0][case][3] == res[1][case][2]
+    # batch items, sparse row blocks and images: every unit owned once, results right
+    assert sum(u[0] for u in units) == 37 and sum(u[1] for u in units) == 700 and sum(u[2] for u in units) == 9
+    assert all(u[3] <= 1e-3 and u[4] <= 1e-3 and u[5] <= 1e-4 for u in units), units
 
 
 def test_four_ranks_nccl_grid(cake):
@@ -92,6 +112,7 @@ def test_four_ranks_nccl_grid(cake):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    res = [r for r, _ in res]
     for per_rank in res:
         for ok_kind, err, lo, hi, _ in per_rank:
             assert ok_kind

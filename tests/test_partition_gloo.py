@@ -25,6 +25,15 @@ def test_blocks_tile_the_range():
     assert partition.row_block(8192, 8, 3) == (3072, 4096)
 
 
+def test_unit_blocks_tile_the_batch():
+    for units in (1, 7, 64, 4096):
+        for world in (1, 2, 3, 8):
+            cuts = [partition.unit_block(units, world, r) for r in range(world)]
+            assert cuts[0][0] == 0 and cuts[-1][1] == units
+            assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+            assert max(hi - lo for lo, hi in cuts) - min(hi - lo for lo, hi in cuts) <= 1
+
+
 def test_plan_follows_the_benchmark_shapes():
     assert partition.plan(8192, 8192, 8192, 2) == "rows"
     assert partition.plan(8192, 8192, 8192, 4) == "grid" and partition.grid_shape(8192, 8192, 8192, 4) == (2, 2)
