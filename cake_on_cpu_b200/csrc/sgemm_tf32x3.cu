@@ -567,7 +567,14 @@ int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int b
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
 
-inline int tile_width(int N) { return (N > 128) ? 256 : 128; }
+inline int tile_width(int N) {
+    static const int forced = [] {
+        const char* e = getenv("CAKEB200_BN");
+        return e ? atoi(e) : 0;
+    }();
+    if (forced == 128 || forced == 256) return forced;
+    return (N > 128) ? 256 : 128;
+}
 
 // Band height of the tile walk.  Tiles that run together should cover a patch of C with
 // few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
