@@ -189,6 +189,22 @@ int resolve_kernel(int kernel, long long M, long long N, long long K, long long 
 }
 
 int run_dense(DeviceState* st, GemmProblem& g, int kernel, cudaStream_t s, bool timed) {
+    // a product with a single column or a single row is a matrix-vector product: stream the matrix once
+    if (kernel != CAKEB200_KERNEL_TF32X3 && g.batch == 1 && !g.trans_a && !g.trans_b && !g.bias && g.out_p == 0 &&
+        ((g.N == 1 && g.ldb == 1 && g.ldc == 1) || (g.M == 1 && g.ldb == g.N && g.N > 1))) {
+        const bool column = g.N == 1;  // C (M x 1) = A x   else   C (1 x N) = B^T a, B read as column-major N x K
+        const int rows = column ? g.M : g.N;
+        int rc = ensure_scratch(st, sgemv_scratch_bytes(rows, g.K, st->sm_count));
+        if (rc) return rc;
+        int launches = 0;
+        rc = column ? launch_sgemv(g.A, g.B, g.C, g.M, g.K, g.lda, 0, g.accumulate, st->scratch, st->scratch_bytes, st->sm_count, s,
+                                   &launches)
+                    : launch_sgemv(g.B, g.A, g.C, g.N, g.K, g.N, 1, g.accumulate, st->scratch, st->scratch_bytes, st->sm_count, s,
+                                   &launches);
+        g_stats.kernel = CAKEB200_KERNEL_FFMA;
+        g_stats.launches += launches;
+        return rc;
+    }
     kernel = resolve_kernel(kernel, g.M, g.N, g.K, g.batch);
     g_stats.kernel = kernel;
     if (kernel == CAKEB200_KERNEL_FFMA) {

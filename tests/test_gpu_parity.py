@@ -457,6 +457,15 @@ def test_matrix_vector_product(cake, oracle):
         yr2 = y0.copy()
         cake.cake_sgemv(Ar, x, yr2, accumulate=True)
         assert (np.abs(yr2 - ref64) / scale).max() <= TOL
+    # cake_sgemm with one column or one row takes the same kernels
+    dev = lambda X: torch.from_numpy(X).cuda()
+    A, B = oracle.uniform((3000, 1500), 1), oracle.uniform((1500, 1), 2)
+    ref, _ = oracle.sgemm(A, B, 8, NA)
+    assert rel_err(cake.cake_sgemm(dev(A), dev(B)).cpu().numpy(), ref, A, B) <= TOL and cake.last_stats()["launches"] == 1
+    assert rel_err(cake.cake_sgemm(A, B), ref, A, B) <= TOL  # host operands: row bands, same kernel
+    A, B = oracle.uniform((1, 1500), 1), oracle.uniform((1500, 2000), 2)
+    ref, _ = oracle.sgemm(A, B, 8, NA)
+    assert rel_err(cake.cake_sgemm(dev(A), dev(B)).cpu().numpy(), ref, A, B) <= TOL and cake.last_stats()["launches"] == 2
     # twice the same call gives the same bits (fixed summation order)
     A, x = oracle.uniform((3000, 2000), 1), oracle.uniform((3000,), 2)
     assert np.array_equal(cake.cake_sgemv(A, x, col_major=True), cake.cake_sgemv(A, x, col_major=True))
