@@ -150,7 +150,8 @@ def reference_arm(args):
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "dense FP32 SGEMM M=K=N=%d, CPU row-block sample" % args.size},
+            "config": {"workload": "dense FP32 SGEMM M=K=N=%d, uniform(-1,1), seeded" % args.size, "kernel": "reference CPU cake_sgemm",
+                       "step": "one cake_sgemm call on a row block of the product (see cpu_baseline.sample)"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
