@@ -351,6 +351,7 @@ def test_implicit_convolution_geometries(cake, oracle):
         (3, 8, 14, 14, 16, 3, 3, 1, True), (2, 3, 8, 6, 5, 3, 3, 1, True), (2, 40, 12, 12, 130, 3, 3, 1, True),
         (2, 32, 10, 10, 64, 1, 1, 0, True), (1, 16, 9, 12, 24, 5, 3, 2, True), (2, 7, 6, 10, 9, 3, 5, 0, True),
         (5, 64, 56, 56, 64, 3, 3, 1, True), (2, 33, 16, 4, 17, 3, 3, 3, True), (1, 4, 30, 80, 8, 3, 3, 1, True),
+        (4, 8, 10, 8, 16, 3, 3, 1, True), (7, 20, 12, 8, 140, 3, 3, 1, True),
         (1, 64, 5, 300, 8, 3, 3, 1, False), (2, 8, 7, 7, 16, 3, 3, 1, False)]
     for (b, cin, H, W, cout, hf, wf, pad, implicit) in cases:
         x = oracle.normal((b, cin, H, W), 4, 0.1)
