@@ -930,7 +930,7 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
                      : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr);
 }
 
-// scratch = A hi/lo planes + transposed B hi/lo planes + split-K partials (worst case)
+// scratch = A hi/lo planes + transposed B hi/lo planes + slots for the partial tiles of the last wave (worst case)
 size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     const size_t Kp = (size_t) padded_k(K);
     const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
@@ -1100,7 +1100,7 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.lda = K; g.ldb = N; g.ldc = N;
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
-    // one K range per tile: split-K would need partial planes, i.e. more scratch
+    // whole-K tiles only: cutting tiles along K would need slots for partial tiles, i.e. more scratch
     rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr)
                    : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr);
     if (rc) return rc;

@@ -33,7 +33,7 @@ class OracleCntx(ctypes.Structure):
                 ("L2", _c_int), ("L3", _c_int), ("ncores", _c_int)]
 
 
-# the cache sizes the survey host reported; fixed so block sizes (and with them
+# cache sizes of an 8-core x86 host (L1 48 KiB, L2 2 MiB, L3 105 MiB); fixed so block sizes (and with them
 # the summation order) are the same wherever the tests run
 DEFAULT_CACHES = (49152, 2097152, 110100480, 8)
 

@@ -160,7 +160,7 @@ def test_profile_events_of_async_products(cake):
     assert (C.double() - ref).abs().max().item() < 1e-2
 
 
-def test_skinny_shapes_exercise_each_schedule_and_split_k(cake, oracle):
+def test_skinny_shapes_exercise_each_schedule_and_cut_tiles(cake, oracle):
     # 1/16-scale versions of the M-first, N-first and K-first benchmark shapes
     for (M, K, N, want) in [(4096, 64, 64, MKN), (64, 64, 4096, NKM), (256, 16384, 320, KMN)]:
         A, B = _inputs(oracle, M, K, N)

@@ -55,7 +55,7 @@ def test_set_schedule(oracle):
 
 
 def test_benchmark_shapes_derive_expected_schedules(oracle):
-    # schedules the reference derives on its 8-core survey host for the benchmark shapes
+    # schedules the reference derives on an 8-core host with these cache sizes for the benchmark shapes
     want = {(3000, 3000, 3000): MKN, (4096, 4096, 4096): KMN, (8192, 8192, 8192): KMN,
             (65536, 1024, 1024): MKN, (1024, 1024, 65536): NKM, (1024, 262144, 1024): KMN,
             (64, 576, 200704): KMN, (96, 96, 96): MKN}
