@@ -16,7 +16,7 @@ shared library is missing, importing the operators raises.
 from .api import (  # noqa: F401
     KMN, MKN, NKM, NA, KERNEL_AUTO, KERNEL_TF32X3, KERNEL_FFMA,
     BlkDims, Cntx, CakeError, Stats,
-    cake_sgemm, cake_sgemm_ex, cake_sgemv, cake_sgemm_async, cake_sgemm_batched, cake_sp_sgemm, cake_conv2d, im2col,
+    cake_sgemm, cake_sgemm_ex, cake_sgemv, cake_sgemm_async, cake_sgemm_batched, cake_sp_sgemm, cake_conv2d, conv_plan, im2col,
     cake_query_cntx, init_block_dims, derive_schedule, set_schedule,
     cake_sgemm_packed_A_size, cake_sgemm_packed_B_size, cake_sgemm_packed_C_size,
     pack_A, pack_B, pack_C, unpack_C, unpack_A, unpack_B,

@@ -33,6 +33,14 @@ class Stats(ctypes.Structure):
         return {k: getattr(self, k) for k, _ in self._fields_}
 
 
+class ConvPlan(ctypes.Structure):
+    """cakeb200_conv_plan: how a convolution is laid out on the tensor-core path."""
+    _fields_ = [(n, _i) for n in ("route", "tiles", "channel_tile", "positions_tile", "k_slices", "stages", "ring", "smem_bytes")]
+
+    def as_dict(self):
+        return {k: getattr(self, k) for k, _ in self._fields_}
+
+
 class Cntx(ctypes.Structure):
     """cakeb200_cntx: the fields of cake_cntx_t the block-sizing formulas read
     (reference include/common.h:138-151)."""
@@ -81,6 +89,7 @@ for _n in ("pack_A", "unpack_A", "pack_B", "unpack_B", "pack_C", "unpack_C"):
 _SIGNATURES["cakeb200_profile_begin"] = (_i, [])
 _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i)])
 _SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
+_SIGNATURES["cakeb200_conv_plan_query"] = (_i, [_i] * 10 + [ctypes.POINTER(ConvPlan)])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
@@ -283,6 +292,13 @@ def cake_conv2d(x, w, stride=1, pad=0, out=None, kernel=KERNEL_AUTO, stream=None
     _check(lib().cakeb200_conv2d(_ptr(x), _ptr(w), _ptr(out), b, cin, H, W, cout, hf, wf, stride, pad, kernel,
                                  _stream_of(out, stream)))
     return out
+
+
+def conv_plan(batch, cin, H, W, cout, hf, wf, stride=1, pad=0, sm_count=148):
+    """Route and tiling cake_conv2d takes on the tensor-core path (host logic, no device needed)."""
+    out = ConvPlan()
+    _check(lib().cakeb200_conv_plan_query(batch, cin, H, W, cout, hf, wf, stride, pad, sm_count, ctypes.byref(out)))
+    return out.as_dict()
 
 
 def im2col(x, hf, wf, stride=1, pad=0, stream=None):

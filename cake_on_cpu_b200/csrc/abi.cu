@@ -750,6 +750,16 @@ int cakeb200_im2col(const float* in, float* col, int batch, int cin, int H, int 
     return CAKEB200_OK;
 }
 
+int cakeb200_conv_plan_query(int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad, int sm_count,
+                             cakeb200_conv_plan* out) {
+    if (!out || batch <= 0 || cin <= 0 || cout <= 0 || H <= 0 || W <= 0 || hf <= 0 || wf <= 0 || stride <= 0 || pad < 0 ||
+        H + 2 * pad < hf || W + 2 * pad < wf) {
+        set_error("bad convolution geometry");
+        return CAKEB200_ERR_ARG;
+    }
+    return conv_tf32x3_describe(batch, cin, H, W, cout, hf, wf, stride, pad, sm_count, out);
+}
+
 int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch, int cin, int H, int W, int cout,
                     int hf, int wf, int stride, int pad, int kernel, void* stream) {
     g_stats = cakeb200_stats();

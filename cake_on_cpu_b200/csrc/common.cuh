@@ -82,6 +82,8 @@ int launch_sgemv(const float* A, const float* x, float* y, int M, int K, int lda
 // stride-1 convolution as an implicit product (conv_tf32x3.cu); scratch holds the split filter planes
 bool conv_tf32x3_fits(const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad);
 size_t conv_tf32x3_scratch_bytes(int cin, int cout, int hf, int wf);
+int conv_tf32x3_describe(int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad, int sm_count,
+                         cakeb200_conv_plan* out);
 int launch_conv_tf32x3(const float* in, const float* filters, float* out, const float* bias, int batch, int cin, int H,
                        int W, int cout, int hf, int wf, int pad, void* scratch, size_t scratch_bytes, int* status_word,
                        int sm_count, cudaStream_t stream, int* launches);

@@ -538,6 +538,23 @@ bool plan(ConvArgs& a, const float* in, int batch, int cin, int H, int W, int co
 
 }  // namespace
 
+int conv_tf32x3_describe(int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad, int sm_count,
+                         cakeb200_conv_plan* out) {
+    ConvArgs a = {};
+    memset(out, 0, sizeof(*out));
+    out->route = 2;
+    if (!plan(a, nullptr, batch, cin, H, W, cout, hf, wf, stride, pad, sm_count > 0 ? sm_count : 148)) return CAKEB200_OK;
+    out->route = a.flat ? 1 : 0;
+    out->tiles = (int) a.tiles;
+    out->channel_tile = a.bn;
+    out->positions_tile = a.flat ? BM : a.rows_per_tile * a.Wo;
+    out->k_slices = a.kblocks;
+    out->stages = a.stages;
+    out->ring = a.ring;
+    out->smem_bytes = a.stages * a.stage_bytes + a.ring * a.raw_bytes + 1024 + 256;
+    return CAKEB200_OK;
+}
+
 bool conv_tf32x3_fits(const float* in, int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad) {
     ConvArgs a = {};
     return plan(a, in, batch, cin, H, W, cout, hf, wf, stride, pad, 148);

@@ -165,6 +165,24 @@ int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch
                     int H, int W, int cout, int hf, int wf, int stride, int pad,
                     int kernel, void* stream);
 
+/* How cakeb200_conv2d lays a convolution out on the tensor-core path (host logic only, needs no device):
+ * route 0 = implicit product, tiles of whole output rows of one image; 1 = implicit product, tiles of 128
+ * consecutive positions of the batch; 2 = im2col planes + the large-matrix kernel (strides, rows wider than
+ * 128 outputs, image areas that are not a multiple of 4 floats).  The other fields describe the implicit
+ * kernel's launch (0 for route 2).  The GPU counterpart of choosing m_c / k_c / n_c for the convolution's
+ * GEMM (reference examples/cake_conv.cpp:1028-1056 through init_block_dims). */
+typedef struct cakeb200_conv_plan {
+    int route;
+    int tiles;            /* tiles of positions x tiles of channels */
+    int channel_tile;     /* output channels per tile (N of the MMA) */
+    int positions_tile;   /* positions per tile (at most 128) */
+    int k_slices;         /* 32-deep slices of K per tile: ceil(cin / 32) * hf * wf */
+    int stages, ring;     /* split stages in tensor memory / shared memory, input boxes in flight */
+    int smem_bytes;
+} cakeb200_conv_plan;
+int cakeb200_conv_plan_query(int batch, int cin, int H, int W, int cout, int hf, int wf, int stride, int pad,
+                             int sm_count, cakeb200_conv_plan* out);
+
 /* im2col alone (reference examples/cake_conv.cpp:1178-1213): col[(cin,hf,wf)][(b,ho,wo)]. */
 int cakeb200_im2col(const float* in, float* col, int batch, int cin, int H, int W,
                     int hf, int wf, int stride, int pad, void* stream);

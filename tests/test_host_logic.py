@@ -94,3 +94,24 @@ def test_bad_arguments_are_reported_not_fatal(cake):
         cake.init_block_dims(0, 10, 10, 2, cx, NA)
     with pytest.raises(cake.CakeError):
         cake.init_block_dims(10, 10, 10, 2, cx, 7)
+
+
+def test_convolution_plan_routes_and_tilings():
+    """Host logic of the tensor-core convolution (no device needed): which route a geometry takes and how the
+    implicit kernel tiles it.  Shared memory must stay within the 227 KB a CTA may use."""
+    import cake_on_cpu_b200 as cake
+    first = cake.conv_plan(64, 64, 56, 56, 64, 3, 3, 1, 1)
+    assert first["route"] == 0 and first["positions_tile"] == 112 and first["channel_tile"] == 64
+    assert first["tiles"] == 64 * 28 and first["k_slices"] == 2 * 9
+    second = cake.conv_plan(64, 256, 14, 14, 512, 3, 3, 1, 1)
+    assert second["route"] == 1 and second["tiles"] == 98 * 4 and second["channel_tile"] == 128 and second["k_slices"] == 72
+    assert cake.conv_plan(4, 16, 9, 9, 8, 3, 3, 2, 0)["route"] == 2      # stride 2
+    assert cake.conv_plan(1, 64, 5, 300, 8, 3, 3, 1, 1)["route"] == 2    # rows wider than a tile
+    assert cake.conv_plan(2, 8, 7, 7, 16, 3, 3, 1, 1)["route"] == 2      # 49 floats per channel: not 16-byte steps
+    for geometry in [(3, 8, 14, 14, 16, 3, 3, 1, 1), (2, 40, 12, 12, 130, 3, 3, 1, 1), (1, 4, 30, 80, 8, 3, 3, 1, 1),
+                     (7, 20, 12, 8, 140, 3, 3, 1, 1), (1, 3, 4, 4, 1, 1, 1, 1, 0)]:
+        p = cake.conv_plan(*geometry)
+        assert p["route"] in (0, 1) and 0 < p["smem_bytes"] <= 227 * 1024 and p["stages"] >= 2 and p["ring"] >= 2
+        assert p["positions_tile"] <= 128 and p["channel_tile"] % 16 == 0 and p["channel_tile"] <= 128
+    with pytest.raises(cake.CakeError):
+        cake.conv_plan(1, 1, 2, 2, 1, 3, 3, 1, 0)  # filter larger than the padded image
