@@ -160,27 +160,6 @@ def reference_arm(args):
 
 # ----------------------------------------------------------------- GPU arm
 
-def bind_to_gpu_cpus(torch, local):
-    """With several ranks per host, run this rank (and allocate its pinned host buffers) on the CPUs next to
-    its GPU: host-to-device copies from the far socket share the inter-socket link with every other rank."""
-    try:
-        import pynvml
-        pynvml.nvmlInit()
-        pr = torch.cuda.get_device_properties(local)
-        bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
-        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
-        words = (os.cpu_count() + 63) // 64
-        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
-        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
-        cpus &= os.sched_getaffinity(0)
-        if cpus:
-            os.sched_setaffinity(0, cpus)
-            return len(cpus)
-    except Exception:  # no NVML, no affinity information: run wherever the launcher put us
-        pass
-    return None
-
-
 def gpu_arm(args):
     import torch
     import cake_on_cpu_b200 as cake
@@ -193,7 +172,6 @@ def gpu_arm(args):
     if world != args.gpus and world > 1:
         raise SystemExit("--gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
     torch.cuda.set_device(local)
-    numa = bind_to_gpu_cpus(torch, local) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -298,8 +276,7 @@ def gpu_arm(args):
                                     ("%d x %d grid of GPUs: row blocks of A x column blocks of B, no exchange" % (pr, pc)),
                        "l2": "operands (%.0f MB per GPU) exceed the 126 MB L2; no flush between steps" %
                              ((rows * K + K * cols + rows * cols) * 4 / 1e6),
-                       "step": "operand split pass + contraction kernel",
-                       **({"host_cpus_per_rank": numa} if numa else {})},
+                       "step": "operand split pass + contraction kernel"},
             "clocks": clocks,
             "e2e": {"value": flops * e2e_steps / float(e2e_s.item()) / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": (rows * K + K * cols) * 4, "d2h_bytes_per_step": rows * cols * 4,
