@@ -9,7 +9,9 @@
 // packing does -- lay the operands out the way the multiplier wants them -- on the way
 // into shared memory: each value is split into its TF32 hi and lo parts and written into
 // 128-byte-swizzled K-major tiles (B is transposed by the choice of which thread writes
-// what).  One tcgen05.mma issuer consumes the tiles; the accumulator of one product is a
+// what); when tensor memory has room next to the two accumulators (N <= 192) the split A
+// operand is stored there instead (tcgen05.st, a thread per row) and costs no shared-memory
+// bandwidth when the multiplier reads it.  One tcgen05.mma issuer consumes the tiles; the accumulator of one product is a
 // 128 x N block of tensor memory; four warps drain it while the next product is already
 // being multiplied into the second block.
 //
@@ -41,15 +43,27 @@ namespace {
 using namespace ptx;
 
 constexpr int BM = 128, BK = 32, UMMA_K = 8;
-constexpr int PROD_WARPS = 16, EPI_WARPS = 4;
+constexpr int PROD_WARPS = 16, EPI_WARPS = 4, EPI_GROUPS = 1;  // a second epilogue group (one per accumulator) was tried: no gain
 constexpr int PROD_THREADS = PROD_WARPS * 32;
-constexpr int FIRST_EPI_WARP = 2, FIRST_PROD_WARP = FIRST_EPI_WARP + EPI_WARPS;
+constexpr int FIRST_EPI_WARP = 2, FIRST_PROD_WARP = FIRST_EPI_WARP + EPI_GROUPS * EPI_WARPS;
 constexpr int NUM_THREADS = 32 * (FIRST_PROD_WARP + PROD_WARPS);  // MMA, loader, 4 epilogue, 16 producer warps
 constexpr int A_ITER = (BM * 8 + PROD_THREADS - 1) / PROD_THREADS;    // float4 chunks of A per producer thread and stage
 constexpr int B_ITER = (256 * 8 + PROD_THREADS - 1) / PROD_THREADS;   // float4 chunks of B (N up to 256)
-constexpr int EPI_BYTES = EPI_WARPS * 32 * 32 * 4;
+constexpr int EPI_BYTES = EPI_GROUPS * EPI_WARPS * 32 * 32 * 4;
 constexpr int MAX_SMEM = 227 * 1024;
 constexpr int MAX_RING = 8;
+
+// Role timers (diagnostic build only, -DCAKEB200_ROLE_TIMERS): CTA 0 adds up the clock cycles its roles
+// spend waiting and working into status_word[16 + 2 * slot] (64-bit counters).
+#ifdef CAKEB200_ROLE_TIMERS
+#define TIMER_DECL long long _t0 = 0
+#define TIMER_START() _t0 = clock64()
+#define TIMER_ADD(slot) do { if (blockIdx.x == 0) atomicAdd((unsigned long long*) (a.status_word + 16) + (slot), (unsigned long long) (clock64() - _t0)); } while (0)
+#else
+#define TIMER_DECL
+#define TIMER_START()
+#define TIMER_ADD(slot)
+#endif
 
 struct SmallArgs {
     const float* A;
@@ -69,10 +83,13 @@ struct SmallArgs {
     int stages;        // split stages
     int ring;          // raw stages filled by TMA (0: producers read global memory)
     int raw_a_bytes, raw_b_bytes, raw_bytes;
+    int raw_tx;        // bytes the two TMA boxes of a raw stage deliver: (M + npad) * 128
     int acc_stride;    // tensor-memory columns between the two accumulators (multiple of 32)
     int tmem_cols;     // power of two >= 2 * acc_stride
     uint32_t idesc;
     int a_vec;         // rows of A may be read as float4 (direct mode)
+    int a_tmem;        // the split A operand lives in tensor memory (first column a_col0), not in shared memory
+    int a_col0;
     int* status_word;
 };
 
@@ -133,31 +150,51 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
+            TIMER_DECL;
             for (int item = blockIdx.x; ok && item < a.batch; item += gridDim.x, local++) {
                 const int buf = local & 1;
+                TIMER_START();
                 ok = mbar_wait(acc_empty_bar(buf), ((local >> 1) & 1) ^ 1, abort_flag, a.status_word, 200 + buf);
+                TIMER_ADD(0);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t) (buf * a.acc_stride);
                 uint32_t accumulate = 0;
                 for (int kb = 0; kb < a.kblocks; kb++) {
+                    TIMER_START();
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, a.status_word, 300 + stage);
+                    TIMER_ADD(1);
                     if (!ok) break;
+                    TIMER_START();
                     tcgen05_fence_after();
                     const uint32_t base = smem_u32(tiles + stage * a.stage_bytes);
-                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
-                    const uint64_t a_lo = make_kmajor_sw128_desc(base + a.a_plane);
                     const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * a.a_plane);
                     const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * a.a_plane + a.b_plane);
+                    if (a.a_tmem) {
+                        const uint32_t t_hi = tmem_base + (uint32_t) (a.a_col0 + stage * 2 * BK), t_lo = t_hi + BK;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
-                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, a.idesc, accumulate);
-                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, a.idesc, 1);
-                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, a.idesc, 1);
-                        accumulate = 1;
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                            const uint32_t col = (uint32_t) (k * UMMA_K);
+                            umma_tf32_ts(d_tmem, t_lo + col, b_hi + adv, a.idesc, accumulate);
+                            umma_tf32_ts(d_tmem, t_hi + col, b_lo + adv, a.idesc, 1);
+                            umma_tf32_ts(d_tmem, t_hi + col, b_hi + adv, a.idesc, 1);
+                            accumulate = 1;
+                        }
+                    } else {
+                        const uint64_t a_hi = make_kmajor_sw128_desc(base);
+                        const uint64_t a_lo = make_kmajor_sw128_desc(base + a.a_plane);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, a.idesc, accumulate);
+                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, a.idesc, 1);
+                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, a.idesc, 1);
+                            accumulate = 1;
+                        }
                     }
                     umma_commit(empty_bar(stage));
+                    TIMER_ADD(2);
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
@@ -172,10 +209,13 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             bool ok = true;
             for (int item = blockIdx.x; ok && item < a.batch; item += gridDim.x) {
                 for (int kb = 0; kb < a.kblocks; kb++) {
+                    TIMER_DECL;
+                    TIMER_START();
                     ok = mbar_wait(raw_empty_bar(r), phase ^ 1, abort_flag, a.status_word, 500 + r);
+                    TIMER_ADD(3);
                     if (!ok) break;
                     const uint32_t dst = smem_u32(raws + r * a.raw_bytes);
-                    mbar_expect_tx(raw_full_bar(r), (uint32_t) (a.raw_a_bytes + a.raw_b_bytes));
+                    mbar_expect_tx(raw_full_bar(r), (uint32_t) a.raw_tx);
                     tma_load_3d(dst, &map_a, kb * BK, 0, item, raw_full_bar(r));
                     tma_load_3d(dst + (uint32_t) a.raw_a_bytes, &map_b, 0, kb * BK, item, raw_full_bar(r));
                     if (++r == R) { r = 0; phase ^= 1; }
@@ -197,13 +237,23 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const int sub_r = lane >> 3, sub_c = lane & 7;
         const bool c_vec = (a.ldc % 4 == 0) && (a.stride_c % 4 == 0) && (((uintptr_t) a.C) % 16 == 0);
         const int chunks = (a.npad + 31) / 32;
-        int local = 0;
+        // Epilogue group g (of EPI_GROUPS) handles the CTA's products g, g + EPI_GROUPS, ...; with one group the
+        // accumulators alternate, with two each accumulator would have its own group.
+        const int grp = (warp - FIRST_EPI_WARP) / EPI_WARPS;
+        const bool poller = (warp - FIRST_EPI_WARP) % EPI_WARPS == 0 && lane == 0;
         bool ok = true;
-        for (int item = blockIdx.x; ok && item < a.batch; item += gridDim.x, local++) {
+        for (int local = grp; ok; local += EPI_GROUPS) {
+            const long long item_ll = (long long) blockIdx.x + (long long) local * gridDim.x;
+            if (item_ll >= a.batch) break;
+            const int item = (int) item_ll;
             const int buf = local & 1;
-            if (warp == FIRST_EPI_WARP && lane == 0)
+            TIMER_DECL;
+            TIMER_START();
+            if (poller)
                 sync_flags[1 + buf] = mbar_wait(acc_full_bar(buf), (local >> 1) & 1, abort_flag, a.status_word, 400 + buf) ? 1 : 0;
-            named_barrier_sync(2, EPI_WARPS * 32);
+            named_barrier_sync(2 + grp, EPI_WARPS * 32);
+            if (warp == FIRST_EPI_WARP && lane == 0) TIMER_ADD(4);
+            TIMER_START();
             ok = sync_flags[1 + buf] != 0;
             if (!ok) break;
             tcgen05_fence_after();
@@ -259,6 +309,7 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 }
                 __syncwarp();
             }
+            if (warp == FIRST_EPI_WARP && lane == 0) TIMER_ADD(5);
         }
     } else {
         // ----------------------------------------------------------- producers
@@ -296,17 +347,94 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         // One thread polls the mbarriers; the other 511 sleep on a hardware barrier instead of
         // spending issue slots on polling.
         auto wait_both = [&](bool with_raw) {
+            TIMER_DECL;
+            TIMER_START();
             if (t == 0) {
                 bool mine = true;
                 if (with_raw) mine = mbar_wait(raw_full_bar(r), raw_phase, abort_flag, a.status_word, 600 + r);
+                TIMER_ADD(6);
                 if (mine) mine = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, a.status_word, 100 + stage);
                 sync_flags[0] = mine ? 1 : 0;
+                TIMER_ADD(7);
             }
             named_barrier_sync(1, PROD_THREADS);
             return sync_flags[0] != 0;
         };
 
-        if (R > 0) {
+        if (R > 0 && a.a_tmem) {
+            // A goes to tensor memory, B to shared memory.  Producer warps 0-7 take A: a thread owns one row
+            // (its tensor-memory lane: warp % 4 selects the 32 lanes a warp may write) and 16 of the 32 k of a
+            // stage, read from the 128-byte-swizzled raw box (conflict-free 16-byte loads although consecutive
+            // lanes are consecutive rows).  Producer warps 8-15 take B as in the other mode.
+            const int pw = t >> 5;
+            const bool a_side = pw < 8;
+            const int quarter = warp & 3, half = (pw >> 2) & 1, row = quarter * 32 + lane;
+            constexpr int B_THREADS = PROD_THREADS / 2, B_IT = (192 * 8 + B_THREADS - 1) / B_THREADS;  // N up to 192
+            const int tb = t - B_THREADS;
+            uint32_t b_src[B_IT], b_dst[B_IT];
+#pragma unroll
+            for (int it = 0; it < B_IT; it++) {
+                const int idx = (a_side ? 0 : tb) + it * B_THREADS, chunk = idx / a.npad, n = idx - chunk * a.npad;
+                b_src[it] = (uint32_t) (chunk * 4 * a.npad + n) * 4u;
+                b_dst[it] = (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4);
+            }
+            const uint32_t b_row = (uint32_t) a.npad * 4u;
+            for (int item = blockIdx.x; ok && item < a.batch; item += gridDim.x) {
+                for (int kb = 0; kb < a.kblocks; kb++) {
+                    ok = wait_both(true);
+                    if (!ok) break;
+                    TIMER_DECL;
+                    TIMER_START();
+                    const uint32_t base = smem_u32(tiles + stage * a.stage_bytes);
+                    const uint32_t raw_a = smem_u32(raws + r * a.raw_bytes), raw_b = raw_a + (uint32_t) a.raw_a_bytes;
+                    if (a_side) {
+                        tcgen05_fence_after();  // the MMAs that read this slice of tensor memory have completed
+                        float v[16], h[16], l[16];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const int c = half * 4 + q;
+                            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (row < a.M) x = ld_shared_v4(raw_a + (uint32_t) row * 128u + (uint32_t) ((c ^ (row & 7)) << 4));
+                            v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j++) split_tf32(v[j], h[j], l[j]);
+                        const uint32_t dst = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (a.a_col0 + stage * 2 * BK);
+                        tmem_st16(dst + (uint32_t) (half * 16), h);
+                        tmem_st16(dst + (uint32_t) (BK + half * 16), l);
+                        tmem_st_wait();
+                        tcgen05_fence_before();
+                    } else {
+                        float vb[B_IT][4];
+#pragma unroll
+                        for (int it = 0; it < B_IT; it++)
+                            if (tb + it * B_THREADS < b_chunks) {
+#pragma unroll
+                                for (int j = 0; j < 4; j++) vb[it][j] = ld_shared_f32(raw_b + b_src[it] + (uint32_t) j * b_row);
+                            }
+#pragma unroll
+                        for (int it = 0; it < B_IT; it++)
+                            if (tb + it * B_THREADS < b_chunks) {
+                                float h[4], l[4];
+#pragma unroll
+                                for (int j = 0; j < 4; j++) split_tf32(vb[it][j], h[j], l[j]);
+                                st_shared_v4(base + b_dst[it], h[0], h[1], h[2], h[3]);
+                                st_shared_v4(base + b_dst[it] + (uint32_t) a.b_plane, l[0], l[1], l[2], l[3]);
+                            }
+                        fence_proxy_async_smem();
+                    }
+                    if (t == 0) TIMER_ADD(8);
+                    named_barrier_sync(1, PROD_THREADS);
+                    if (t == 0) {
+                        mbar_arrive(full_bar(stage));
+                        mbar_arrive(raw_empty_bar(r));
+                        TIMER_ADD(9);
+                    }
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                    if (++r == R) { r = 0; raw_phase ^= 1; }
+                }
+            }
+        } else if (R > 0) {
             // per-thread offsets of its chunks: where to read in the raw boxes, where to write in the split planes
             uint32_t a_src[A_ITER], a_dst[A_ITER], b_src[B_ITER], b_dst[B_ITER];
 #pragma unroll
@@ -326,6 +454,8 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 for (int kb = 0; kb < a.kblocks; kb++) {
                     ok = wait_both(true);
                     if (!ok) break;
+                    TIMER_DECL;
+                    TIMER_START();
                     const uint32_t base = smem_u32(tiles + stage * a.stage_bytes);
                     const uint32_t raw_a = smem_u32(raws + r * a.raw_bytes), raw_b = raw_a + (uint32_t) a.raw_a_bytes;
                     // all reads of the stage first, so that their latencies overlap
@@ -360,11 +490,13 @@ sgemm_small_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                             st_shared_v4(base + b_dst[it], h[0], h[1], h[2], h[3]);
                             st_shared_v4(base + b_dst[it] + (uint32_t) a.b_plane, l[0], l[1], l[2], l[3]);
                         }
+                    if (t == 0) TIMER_ADD(8);
                     fence_proxy_async_smem();
                     named_barrier_sync(1, PROD_THREADS);
                     if (t == 0) {
                         mbar_arrive(full_bar(stage));
                         mbar_arrive(raw_empty_bar(r));
+                        TIMER_ADD(9);
                     }
                     if (++stage == S) { stage = 0; phase ^= 1; }
                     if (++r == R) { r = 0; raw_phase ^= 1; }
@@ -486,6 +618,7 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
     a.raw_a_bytes = g.M * 128;
     a.raw_b_bytes = a.npad * 128;
     a.raw_bytes = (a.raw_a_bytes + a.raw_b_bytes + 127) / 128 * 128;
+    a.raw_tx = (g.M + a.npad) * 128;
     const bool tma_ok = (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (g.stride_a % 4 == 0) && (g.stride_b % 4 == 0) &&
                         (((uintptr_t) g.A | (uintptr_t) g.B) % 16 == 0) && getenv("CAKEB200_SMALL_DIRECT") == nullptr;
     // two split stages (one being multiplied, one being filled); the rest of shared memory goes to the
@@ -493,6 +626,25 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
     // 2 / 3 / 4 boxes -> 0.145 / 0.126 / 0.124 ms for 4096 products; a third split stage instead: 0.139 ms)
     a.stages = 2;
     a.ring = tma_ok ? std::min(MAX_RING, (MAX_SMEM - fixed - a.stages * a.stage_bytes) / a.raw_bytes) : 0;
+    // With room in tensor memory next to the two accumulators (N up to 192) the split A operand goes there:
+    // shared memory then holds only B's planes and raw boxes (A's box 128-byte swizzled, in 1 KiB units).
+    if (tma_ok && a.acc_stride <= 192 && getenv("CAKEB200_SMALL_A_SMEM") == nullptr) {
+        SmallArgs t = a;
+        t.a_tmem = 1;
+        t.a_col0 = 2 * t.acc_stride;
+        t.tmem_cols = 512;
+        t.a_plane = 0;
+        t.stage_bytes = 2 * t.b_plane;
+        t.raw_a_bytes = (g.M * 128 + 1023) / 1024 * 1024;
+        t.raw_bytes = t.raw_a_bytes + t.raw_b_bytes;
+        t.stages = std::min(4, (512 - t.a_col0) / (2 * BK));
+        t.ring = std::min(MAX_RING, (MAX_SMEM - fixed - t.stages * t.stage_bytes) / t.raw_bytes);
+        while (t.ring < 3 && t.stages > 2) {
+            t.stages--;
+            t.ring = std::min(MAX_RING, (MAX_SMEM - fixed - t.stages * t.stage_bytes) / t.raw_bytes);
+        }
+        if (t.ring >= 2 && t.stages >= 2) a = t;
+    }
     if (a.ring < 2) {
         a.ring = 0;
         a.stages = std::min(6, (MAX_SMEM - fixed) / a.stage_bytes);
@@ -514,7 +666,7 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
         const unsigned long long sb[2] = {(unsigned long long) g.ldb * 4, (unsigned long long) (g.stride_b > 0 ? g.stride_b : (long long) g.K * g.ldb) * 4};
         const unsigned bb[3] = {(unsigned) a.npad, (unsigned) BK, 1};
         int rc;
-        if ((rc = encode_tiled_f32(&map_a, g.A, 3, da, sa, ba, false))) return rc;
+        if ((rc = encode_tiled_f32(&map_a, g.A, 3, da, sa, ba, a.a_tmem != 0))) return rc;
         if ((rc = encode_tiled_f32(&map_b, g.B, 3, db, sb, bb, false))) return rc;
     }
     const int smem = a.stages * a.stage_bytes + a.ring * a.raw_bytes + fixed;
@@ -522,6 +674,17 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
     const int grid = std::min(g.batch, sm_count);
     sgemm_small_tf32x3_kernel<<<grid, NUM_THREADS, smem, stream>>>(map_a, map_b, a);
     CAKE_CUDA_OK(cudaGetLastError());
+#ifdef CAKEB200_ROLE_TIMERS
+    {
+        unsigned long long h[16];
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(h, status_word + 16, sizeof(h), cudaMemcpyDeviceToHost);
+        cudaMemset(status_word + 16, 0, sizeof(h));
+        fprintf(stderr, "small-batch role timers (cycles, CTA 0): mma[wait_acc %llu wait_full %llu issue %llu] loader[wait %llu] "
+                "epilogue[wait %llu work %llu] producer0[wait_raw %llu +wait_empty %llu convert %llu +publish %llu] slices/CTA %d\n",
+                h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], (a.batch + grid - 1) / grid * a.kblocks);
+    }
+#endif
     return CAKEB200_OK;
 }
 

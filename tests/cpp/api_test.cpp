@@ -89,6 +89,30 @@ int main(int argc, char* argv[]) {
         expect(cake_gemm_small(a.data(), b.data(), c.data(), m, m, m, p, &x, cntx, NA), "cake_gemm_small took the product");
         expect(cake_sgemm_checker(a.data(), b.data(), c.data(), m, m, m) == 0, "cake_gemm_small result");
     }
+    // matrix-vector driver of the reference's example (examples/cake_gemv.cpp:771-813): column-major A, C added to
+    {
+        const int m = 1000, k = 700;
+        std::vector<float> a((size_t) m * k), x(k), y(m, 0.25f), want(m, 0.25f);
+        rand_init(a.data(), m, k);
+        rand_init(x.data(), k, 1);
+        expect(cake_sgemv(a.data(), x.data(), y.data(), m, k, p, cntx) > 0, "cake_sgemv returned a time");
+        for (int kk = 0; kk < k; kk++)
+            for (int mm = 0; mm < m; mm++) want[mm] += a[(size_t) kk * m + mm] * x[kk];
+        double worst = 0;
+        for (int mm = 0; mm < m; mm++) worst = std::max(worst, (double) fabsf(want[mm] - y[mm]));
+        expect(worst < 1e-3, "cake_sgemv result");
+    }
+    // a batch of small products (tensor-core kernel for a batch this large)
+    {
+        const int m = 96, batch = 200;
+        std::vector<float> a((size_t) batch * m * m), b((size_t) batch * m * m), c((size_t) batch * m * m, -7.f);
+        rand_init(a.data(), batch * m, m);
+        rand_init(b.data(), batch * m, m);
+        expect(cake_sgemm_small_batched(a.data(), b.data(), c.data(), m, m, m, batch, p, cntx) > 0, "cake_sgemm_small_batched");
+        for (int i : {0, 77, 199})
+            expect(cake_sgemm_checker(a.data() + (size_t) i * m * m, b.data() + (size_t) i * m * m, c.data() + (size_t) i * m * m,
+                                      m, m, m) == 0, "batched item result");
+    }
     expect(set_schedule(NA, 4000, 100, 100) == MKN && set_schedule(NA, 100, 100, 4000) == KMN &&
            set_schedule(NA, 100, 4000, 100) == NKM, "set_schedule");
     free(cntx);

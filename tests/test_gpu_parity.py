@@ -404,11 +404,14 @@ def test_batched_small_on_tensor_cores(cake, oracle):
     """The batched kernel that splits its operands in shared memory: full and ragged tiles, K not a multiple
     of the stage depth, N at the 256 limit, more products than SMs (several per CTA, both accumulators in use)."""
     shapes = [(300, 96, 96, 96), (7, 128, 64, 256), (333, 33, 17, 70), (40, 100, 200, 48), (2, 1, 1, 1), (150, 128, 37, 130),
-              (1, 64, 100, 64), (300, 96, 96, 96)]
+              (1, 64, 100, 64), (200, 33, 64, 48), (37, 128, 96, 192), (300, 96, 96, 96), (300, 96, 96, 96)]
     for case, (batch, M, K, N) in enumerate(shapes):
         # the last case repeats the first with the producers reading global memory themselves instead of the TMA ring
         if case == len(shapes) - 1:
             os.environ["CAKEB200_SMALL_DIRECT"] = "1"
+        # ... and the one before it with the split A operand in shared memory instead of tensor memory
+        if case == len(shapes) - 2:
+            os.environ["CAKEB200_SMALL_A_SMEM"] = "1"
         A, B = oracle.uniform((batch, M, K), 1), oracle.uniform((batch, K, N), 2)
         C = np.full((batch, M, N), np.nan, np.float32)
         cake.cake_sgemm_batched(A, B, C, kernel=cake.KERNEL_TF32X3)
@@ -422,6 +425,7 @@ def test_batched_small_on_tensor_cores(cake, oracle):
         den = np.linalg.norm(A, axis=2)[:, :, None] * np.linalg.norm(B, axis=1)[:, None, :]
         assert (np.abs(C - ref64) / np.maximum(den, 1e-30)).max() <= TOL
     os.environ.pop("CAKEB200_SMALL_DIRECT", None)
+    os.environ.pop("CAKEB200_SMALL_A_SMEM", None)
     # AUTO takes the tensor-core kernel for a large batch of well-filled tiles, FFMA for a handful of tiny ones
     A, B = oracle.uniform((300, 96, 96), 1), oracle.uniform((300, 96, 96), 2)
     cake.cake_sgemm_batched(A, B)
