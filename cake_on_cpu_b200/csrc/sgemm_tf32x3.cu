@@ -626,10 +626,19 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     const double tile_us = 1.17 * kblocks, slot_us = 0.09, fixed_us = 8.0;
     int best_s = 1;
     double best = tile_us;
+    // CTAs that work on the same K range share panels through L2 only while they stay close to each other
+    // along K; over pieces of many hundred slices they drift apart (measured: +24 % at 910 slices per piece,
+    // +29 % at 1024, nothing at 512), which the model charges to long pieces
+    auto drift = [](double slices) { return 1.0 + 0.3 * std::min(1.0, std::max(0.0, (slices - 512.0) / 512.0)); };
+    best = tile_us * drift(kblocks);
     for (int s = 2; s <= s_max; s++) {
         const long long rounds = ((long long) R * s + sm_count - 1) / sm_count;
-        const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
+        const double cost = tile_us * drift((double) kblocks / s) * rounds / s + slot_us * R * s + fixed_us;
         if (cost < best * 0.97) { best = cost; best_s = s; }
+    }
+    if (const char* e = getenv("CAKEB200_PIECES")) {  // experiments: force the number of K pieces per leftover tile
+        const int forced = atoi(e);
+        if (forced >= 1 && (long long) forced * R <= 4LL * sm_count + 8 && forced <= kblocks) best_s = forced;
     }
     if (best_s == 1) return p;
     const int s = best_s;
@@ -679,6 +688,7 @@ struct DevicePlan {
     const TilePieces* pieces = nullptr;
     cudaEvent_t last_use = nullptr;
     unsigned long long stamp = 0;
+    bool pinned = false;  // recorded into a CUDA graph: the table must stay where it is for good
 };
 constexpr int PLAN_SLOTS = 16, PLAN_DEVICES = 64;
 DevicePlan g_plans[PLAN_DEVICES][PLAN_SLOTS];
@@ -692,7 +702,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
     std::lock_guard<std::mutex> lock(g_plan_mutex);
     const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn};
     DevicePlan* slots = g_plans[dev];
-    DevicePlan* victim = &slots[0];
+    DevicePlan* victim = nullptr;
     for (int i = 0; i < PLAN_SLOTS; i++) {
         if (slots[i].valid && slots[i].key == key) {
             slots[i].stamp = ++g_plan_clock;
@@ -700,7 +710,19 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
             return CAKEB200_OK;
         }
         if (!slots[i].valid) { victim = &slots[i]; break; }
-        if (slots[i].stamp < victim->stamp) victim = &slots[i];
+        if (!slots[i].pinned && (!victim || slots[i].stamp < victim->stamp)) victim = &slots[i];
+    }
+    if (!victim) {
+        set_error("every cached tile plan of this device is part of a captured CUDA graph (16 shapes)");
+        return CAKEB200_ERR_ARG;
+    }
+    {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) cudaGetLastError();
+        if (capturing != cudaStreamCaptureStatusNone) {
+            set_error("first use of a shape during stream capture: call it once outside the capture (the tile plan is uploaded then)");
+            return CAKEB200_ERR_ARG;
+        }
     }
     const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, bn);
     const size_t units_b = align_up(hp.units.size() * sizeof(int4) + 16, 256);
@@ -811,7 +833,13 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
         CAKE_CUDA_OK(cudaGetLastError());
         if (launches) (*launches)++;
     }
-    if (a.units) CAKE_CUDA_OK(cudaEventRecord(plan->last_use, stream));
+    if (a.units) {
+        // inside a stream capture the table becomes part of the graph: it is pinned instead of tracked by an event
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) cudaGetLastError();
+        if (capturing != cudaStreamCaptureStatusNone) plan->pinned = true;
+        else CAKE_CUDA_OK(cudaEventRecord(plan->last_use, stream));
+    }
     return CAKEB200_OK;
 }
 

@@ -59,6 +59,40 @@ def _dense(M, K, N, kernel):
     return run
 
 
+def _dense_stream(n, graph):
+    """Products enqueued back to back on one stream (no host synchronisation between them), eagerly or as a
+    replayed CUDA graph of ten products: what a caller that keeps the GPU fed sees for a small product."""
+    def run(reps):
+        g = torch.Generator(device="cuda").manual_seed(1)
+        A, B, C = _uniform(g, n, n), _uniform(g, n, n), torch.empty((n, n), device="cuda")
+        s = torch.cuda.Stream()
+        per = 10
+        with torch.cuda.stream(s):
+            def enqueue():
+                for _ in range(per):
+                    api.cake_sgemm_async(A.data_ptr(), B.data_ptr(), C.data_ptr(), n, n, n, 0, api.NA, api.KERNEL_TF32X3, s.cuda_stream)
+            enqueue()
+            s.synchronize()
+            if graph:
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg, stream=s):
+                    enqueue()
+                enqueue = cg.replay
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            best = float("inf")
+            for _ in range(max(reps, 1)):
+                e0.record(s)
+                for _ in range(10):
+                    enqueue()
+                e1.record(s)
+                s.synchronize()
+                best = min(best, e0.elapsed_time(e1) / (10 * per))
+        flops = 2.0 * n ** 3
+        return {"ms": best, "flops": flops, "tflops": flops / best / 1e9, "bound": "tensor", "frac": flops / best / 1e9 / TENSOR_3XTF32,
+                "mode": "CUDA graph of 10 products" if graph else "asynchronous calls back to back"}
+    return run
+
+
 def _batched(batch, n, kernel=api.KERNEL_AUTO):
     def run(reps):
         g = torch.Generator(device="cuda").manual_seed(1)
@@ -143,6 +177,9 @@ def _pack(n, which):
 CONFIGS = {}
 for _n in (1024, 2048, 3000, 4096, 8192, 16384, 32768):
     CONFIGS["square_%d" % _n] = _dense(_n, _n, _n, api.KERNEL_AUTO)
+for _n in (1024, 2048):
+    CONFIGS["square_%d_stream" % _n] = _dense_stream(_n, False)
+    CONFIGS["square_%d_graph" % _n] = _dense_stream(_n, True)
 CONFIGS["square_8192_ffma"] = _dense(8192, 8192, 8192, api.KERNEL_FFMA)
 CONFIGS["rect_m_first"] = _dense(65536, 1024, 1024, api.KERNEL_AUTO)
 CONFIGS["rect_n_first"] = _dense(1024, 1024, 65536, api.KERNEL_AUTO)

@@ -101,7 +101,11 @@ int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K
                    int accumulate, int sched, int kernel, void* stream);
 
 /* Same, but only enqueues on `stream` (device pointers required, no host copies,
- * no synchronisation).  For callers that time or overlap the work themselves. */
+ * no synchronisation).  For callers that time or overlap the work themselves.
+ * It can be recorded into a CUDA graph by stream capture once the same shape has
+ * been called outside a capture (that call sizes the scratch arena and uploads
+ * the tile plan); a later call with a shape that needs a larger arena moves the
+ * arena and invalidates graphs recorded before, so call the largest shape first. */
 int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K,
                          int accumulate, int sched, int kernel, void* stream);
 

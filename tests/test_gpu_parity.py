@@ -160,6 +160,32 @@ def test_profile_events_of_async_products(cake):
     assert (C.double() - ref).abs().max().item() < 1e-2
 
 
+def test_async_products_capture_into_a_cuda_graph(cake, oracle):
+    """After one ordinary call (which sizes the scratch arena and uploads the tile plan) the asynchronous entry
+    point only enqueues kernels, so a stream capture records it; replaying the graph gives the same bits."""
+    import torch
+    for (M, K, N, kernel) in [(1024, 1024, 1024, cake.KERNEL_TF32X3), (300, 200, 260, cake.KERNEL_FFMA)]:
+        A, B = _inputs(oracle, M, K, N)
+        ref, _ = oracle.sgemm(A, B, 8, NA)
+        dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+        dC = torch.zeros((M, N), device="cuda")
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            cake.cake_sgemm_async(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, N, K, 0, NA, kernel, s.cuda_stream)
+            s.synchronize()
+            eager = dC.clone()
+            dC.zero_()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                for _ in range(3):
+                    cake.cake_sgemm_async(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, N, K, 0, NA, kernel, s.cuda_stream)
+            assert not dC.any()  # capturing ran nothing
+            graph.replay()
+            s.synchronize()
+        assert torch.equal(dC, eager)
+        assert rel_err(dC.cpu().numpy(), ref, A, B) <= TOL
+
+
 def test_skinny_shapes_exercise_each_schedule_and_cut_tiles(cake, oracle):
     # 1/16-scale versions of the M-first, N-first and K-first benchmark shapes
     for (M, K, N, want) in [(4096, 64, 64, MKN), (64, 64, 4096, NKM), (256, 16384, 320, KMN)]:
