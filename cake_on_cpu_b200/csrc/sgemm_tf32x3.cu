@@ -626,14 +626,11 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     const double tile_us = 1.17 * kblocks, slot_us = 0.09, fixed_us = 8.0;
     int best_s = 1;
     double best = tile_us;
-    // CTAs that work on the same K range share panels through L2 only while they stay close to each other
-    // along K; over pieces of many hundred slices they drift apart (measured: +24 % at 910 slices per piece,
-    // +29 % at 1024, nothing at 512), which the model charges to long pieces
-    auto drift = [](double slices) { return 1.0 + 0.3 * std::min(1.0, std::max(0.0, (slices - 512.0) / 512.0)); };
-    best = tile_us * drift(kblocks);
+    // (Pieces of very different lengths were timed on 1024 x 262144 x 1024, 32 tiles: 4, 9 and 18 pieces per
+    // tile give 2.64, 2.57 and 2.58 ms, so beyond filling the SMs the choice of s hardly matters.)
     for (int s = 2; s <= s_max; s++) {
         const long long rounds = ((long long) R * s + sm_count - 1) / sm_count;
-        const double cost = tile_us * drift((double) kblocks / s) * rounds / s + slot_us * R * s + fixed_us;
+        const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
         if (cost < best * 0.97) { best = cost; best_s = s; }
     }
     if (const char* e = getenv("CAKEB200_PIECES")) {  // experiments: force the number of K pieces per leftover tile
