@@ -1,6 +1,8 @@
 """Times the benchmark configurations of the CAKE SGEMM path on one GPU.
 
     python -m cake_on_cpu_b200.workloads [--config NAME ...] [--reps R] [--list]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m cake_on_cpu_b200.workloads --distributed {square_8192,rect_m_first,rect_n_first,rect_k_first}
 
 Each configuration prints one JSON line: device time of the whole library call
 (CUDA events on the calling stream, operands resident in device memory, best of
@@ -201,12 +203,76 @@ CONFIGS["unpack_C_8192"] = _pack(8192, "C")
 DEFAULT = [k for k in CONFIGS if k not in ("square_32768", "sparse_50_zero_skipping", "sparse_10_zero_skipping")]
 
 
+def _distributed(name, reps):
+    """One product over all ranks of a torchrun launch (NCCL): every rank holds only its own share of the
+    operands (row block, column block, grid block or K slice) before the timed region; the K split ends with the
+    reduce-scatter that leaves every rank with its row block of C.  Device time, maximum over ranks."""
+    import os
+    import torch.distributed as dist
+    from . import distributed, partition
+    shapes = {"square_8192": (8192, 8192, 8192), "rect_m_first": (65536, 1024, 1024), "rect_n_first": (1024, 1024, 65536),
+              "rect_k_first": (1024, 262144, 1024)}
+    M, K, N = shapes[name]
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    kind = partition.plan(M, N, K, world)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    if kind == "k":
+        k0, k1 = partition.k_block(K, world, rank)
+        A, B = _uniform(g, M, k1 - k0), _uniform(g, k1 - k0, N)
+        out = torch.empty((M // world, N), device="cuda") if M % world == 0 else None
+
+        def step():
+            partial = api.cake_sgemm(A, B)
+            if out is not None:
+                dist.reduce_scatter_tensor(out, partial)
+            else:
+                dist.all_reduce(partial)
+    else:
+        r0, r1, c0, c1 = (partition.grid_block(M, N, K, world, rank) if kind == "grid" else
+                          partition.row_block(M, world, rank) + (0, N) if kind == "rows" else
+                          (0, M) + partition.col_block(N, world, rank))
+        A, B = _uniform(g, r1 - r0, K), _uniform(g, K, c1 - c0)
+        C = torch.empty((r1 - r0, c1 - c0), device="cuda")
+
+        def step():
+            api.cake_sgemm(A, B, C)
+    for _ in range(3):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(max(reps, 3)):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        best = min(best, float(t.item()))
+    if rank == 0:
+        flops = 2.0 * M * N * K
+        print(json.dumps({"config": name, "ranks": world, "split": kind, "ms": round(best, 4), "flops": flops,
+                          "tflops": round(flops / best / 1e9, 2), "exchange": "reduce-scatter of the partial products" if kind == "k" else "none"}),
+              flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", nargs="*", default=None)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--distributed", default=None, help="time one dense shape over the ranks of a torchrun launch")
     args = ap.parse_args(argv)
+    if args.distributed:
+        api.lib()
+        _distributed(args.distributed, args.reps)
+        return 0
     if args.list:
         print("\n".join(CONFIGS))
         return 0
