@@ -119,10 +119,18 @@ def _sparse(n, density, kernel):
         ms = _timed(lambda: api.cake_sp_sgemm(A, B, C, kernel=kernel), reps)
         st = api.last_stats()
         flops = 2.0 * nnz * n
-        nbytes = n * n / 8 + 4.0 * nnz + 4.0 * n * n + 4.0 * n * n
-        return {"ms": ms, "nnz": nnz, "flops": flops, "tflops": flops / ms / 1e9, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
-                "ran": "dense tcgen05" if st["kernel"] == api.KERNEL_TF32X3 else "zero skipping", "bound": "hbm",
-                "frac": nbytes / ms / 1e6 / HBM_GBS}
+        dense = st["kernel"] == api.KERNEL_TF32X3
+        res = {"ms": ms, "nnz": nnz, "flops": flops, "tflops": flops / ms / 1e9,
+               "ran": "dense tcgen05 on the operand as given" if dense else "zero skipping (compaction + gather)"}
+        if dense:
+            # every element is multiplied, zeros included: the tensor pipe bounds it
+            rate = 2.0 * n ** 3 / ms / 1e9
+            res.update({"bound": "tensor", "dense_tflops": rate, "frac": rate / TENSOR_3XTF32})
+        else:
+            # every nonzero of A pulls one row of B (N floats) through L2; no measured L2 peak to divide by
+            gather = 4.0 * nnz * n
+            res.update({"bound": "l2 gather", "gather_bytes": gather, "gbs": gather / ms / 1e6, "frac": None})
+        return res
     return run
 
 
