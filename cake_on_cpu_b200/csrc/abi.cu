@@ -399,17 +399,28 @@ int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, in
 
     Operand oa, ob, oc;
     int rc;
+    static const bool host_timing = getenv("CAKEB200_DEBUG_TIMING") != nullptr;
+    timespec t0, t1, t2, t3;
+    if (host_timing) clock_gettime(CLOCK_MONOTONIC, &t0);
     CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
     if ((rc = stage_in(st, 0, oa, A, (size_t) M * K * 4, true, s))) return rc;
     if ((rc = stage_in(st, 1, ob, B, (size_t) K * N * 4, true, s))) return rc;
     if ((rc = stage_in(st, 2, oc, C, (size_t) M * N * 4, g.accumulate != 0, s))) return rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    if (host_timing) clock_gettime(CLOCK_MONOTONIC, &t1);
     g.A = (const float*) oa.dev; g.B = (const float*) ob.dev; g.C = (float*) oc.dev;
     if ((rc = run_dense(st, g, kernel, s, true))) return rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
     if ((rc = stage_out(oc, s))) return rc;
     CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    if (host_timing) clock_gettime(CLOCK_MONOTONIC, &t2);
     if ((rc = check_status_word(st, s))) return rc;
+    if (host_timing) {
+        clock_gettime(CLOCK_MONOTONIC, &t3);
+        auto us = [](const timespec& a, const timespec& b) { return (b.tv_sec - a.tv_sec) * 1e6 + (b.tv_nsec - a.tv_nsec) * 1e-3; };
+        fprintf(stderr, "cakeb200 blocking call, host side: operands %.1f us, enqueue %.1f us, wait + status %.1f us\n", us(t0, t1),
+                us(t1, t2), us(t2, t3));
+    }
     g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
     g_stats.ms_prepass = (g_stats.ms_prepass < 0.f) ? elapsed(st->ev[4], st->ev[5]) : 0.f;
     const float mid = elapsed(st->ev[1], st->ev[2]);
