@@ -90,6 +90,7 @@ _SIGNATURES["cakeb200_profile_begin"] = (_i, [])
 _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i)])
 _SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_conv_plan_query"] = (_i, [_i] * 10 + [ctypes.POINTER(ConvPlan)])
+_SIGNATURES["cakeb200_selftest_bounded_wait"] = (_i, [_i, _vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 

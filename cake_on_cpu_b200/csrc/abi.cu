@@ -647,6 +647,20 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
     return CAKEB200_OK;
 }
 
+int cakeb200_selftest_bounded_wait(int limit_us, void* stream) {
+    g_stats = cakeb200_stats();
+    if (limit_us < 1 || limit_us > 1000000) {
+        set_error("limit must be between 1 us and 1 s");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = (cudaStream_t) stream;
+    int rc = launch_bounded_wait_selftest(st->status_word, limit_us, s);
+    if (rc) return rc;
+    return check_status_word(st, s);  // expected: CAKEB200_ERR_DEVICE_TIMEOUT, "where" 900
+}
+
 int cakeb200_sgemv(const float* A, const float* x, float* y, int M, int K, int col_major, int accumulate, void* stream) {
     g_stats = cakeb200_stats();
     if (!A || !x || !y) {

@@ -72,6 +72,8 @@ int ensure_scratch(DeviceState* st, size_t bytes);
 // exact-FP32 FFMA path (sgemm_ffma.cu)
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);  // untransposed operands only
 int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream);
+// one CTA runs a bounded wait that must give up (sgemm_tf32x3.cu)
+int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream);
 // batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)
 bool small_tf32x3_fits(int M, int N, int K);
 int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_count, cudaStream_t stream);

@@ -1013,6 +1013,36 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 
 }  // namespace cakeb200
 
+// ------------------------------------------------- self-test of the bounded wait
+//
+// One CTA waits on an mbarrier that nothing ever arrives at, with a limit of `limit_us`
+// microseconds, through the same wait routine the product kernels use.  The wait must give
+// up, record where in the status word and let the kernel return normally; the host then
+// reports CAKEB200_ERR_DEVICE_TIMEOUT and the context stays usable.  This is how the
+// containment of a stalled pipeline is exercised without stalling anything for real.
+namespace cakeb200 {
+namespace {
+__global__ void bounded_wait_selftest_kernel(int* status_word, long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status_word, 900, limit_ns);
+    __syncthreads();
+}
+}  // namespace
+
+int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status_word, (long long) limit_us * 1000);
+    CAKE_CUDA_OK(cudaGetLastError());
+    return CAKEB200_OK;
+}
+}  // namespace cakeb200
+
 // ------------------------------------------------- entry point that allocates nothing
 //
 // Some callers may not allocate device memory at the moment they need a product:

@@ -48,8 +48,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
 // barrier did not flip within WAIT_LIMIT_NS or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status_word, int where) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
+                                              int where, long long limit_ns) {
     // short waits are the common case: poll a while before touching the (slow) global timer
 #pragma unroll 1
     for (int i = 0; i < 64; i++)
@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 1023) == 0) {
             if (*abort_flag) return false;
-            if ((long long) (global_ns() - t0) > WAIT_LIMIT_NS) {
+            if ((long long) (global_ns() - t0) > limit_ns) {
                 *abort_flag = 1;
                 if (atomicCAS(status_word, 0, 1) == 0) {
                     status_word[1] = where;
@@ -70,6 +70,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_word, int where) {
+    return mbar_wait_for(bar, parity, abort_flag, status_word, where, WAIT_LIMIT_NS);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {

@@ -143,6 +143,14 @@ int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls);
 int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int N, int K,
                            int batch, int kernel, void* stream);
 
+/* Self-test of the fault containment: one CTA waits, through the wait routine of the
+ * tensor-core kernels, on a barrier that nothing ever signals; after `limit_us`
+ * microseconds (1 .. 1e6) the wait gives up, the kernel returns normally and the call
+ * reports CAKEB200_ERR_DEVICE_TIMEOUT with "where 900" in the error text.  The device
+ * context stays usable.  (The reference stops the process with exit(1) on its errors,
+ * reference src/cake_sgemm.cpp:49-52.) */
+int cakeb200_selftest_bounded_wait(int limit_us, void* stream);
+
 /* y (+)= A x for an M x K matrix.  col_major != 0: A[k*M + m], the layout of the
  * reference's matrix-vector driver; else row-major A[m*K + k], the N = 1 case of
  * cake_sgemm.  accumulate != 0 adds to y, which is what the reference's driver

@@ -502,6 +502,24 @@ def test_matrix_vector_product(cake, oracle):
     assert np.array_equal(cake.cake_sgemv(A, x, col_major=True), cake.cake_sgemv(A, x, col_major=True))
 
 
+def test_a_stalled_wait_gives_up_and_the_context_survives(cake, oracle):
+    """The device-side waits are bounded.  The self-test kernel waits on a barrier nothing signals (limit 2 ms):
+    the call must come back with the time-out status, and the next product must run as if nothing had happened."""
+    import time
+    cake.cake_sgemm(*_inputs(oracle, 64, 64, 64))  # the first call of a process creates the device state
+    t0 = time.perf_counter()
+    rc = cake.lib().cakeb200_selftest_bounded_wait(2000, None)
+    waited = time.perf_counter() - t0
+    assert rc == -4, rc  # CAKEB200_ERR_DEVICE_TIMEOUT
+    assert b"where 900" in cake.lib().cakeb200_last_error()
+    assert 0.0015 <= waited < 0.5, waited
+    A, B = _inputs(oracle, 300, 200, 260)
+    ref, _ = oracle.sgemm(A, B, 8, NA)
+    for kernel in (cake.KERNEL_TF32X3, cake.KERNEL_FFMA):
+        assert rel_err(cake.cake_sgemm(A, B, kernel=kernel), ref, A, B) <= TOL
+    assert cake.lib().cakeb200_selftest_bounded_wait(0, None) == -1  # argument error, nothing launched
+
+
 def test_errors_are_status_codes(cake):
     A = np.zeros((4, 4), np.float32)
     with pytest.raises(ValueError):
