@@ -91,6 +91,15 @@ _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctyp
 _SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_conv_plan_query"] = (_i, [_i] * 10 + [ctypes.POINTER(ConvPlan)])
 _SIGNATURES["cakeb200_selftest_bounded_wait"] = (_i, [_i, _vp])
+_pi = ctypes.POINTER(_i)
+_SIGNATURES["cakeb200_kshard_rows"] = (_i, [_i, _i, _i, _pi, _pi])
+_SIGNATURES["cakeb200_kshard_supported"] = (_i, [_i, _i, _i, _i])
+_SIGNATURES["cakeb200_kshard_create"] = (_i, [_i, _i, _i, _i, ctypes.POINTER(_vp), _vp])
+_SIGNATURES["cakeb200_kshard_connect_ipc"] = (_i, [_vp, _vp])
+_SIGNATURES["cakeb200_kshard_connect_local"] = (_i, [_vp, ctypes.POINTER(_vp)])
+_SIGNATURES["cakeb200_kshard_partial"] = (_i, [_vp, _vp, _i, _vp, _i, _i, _vp])
+_SIGNATURES["cakeb200_kshard_finish"] = (_i, [_vp, _vp, _i, _vp])
+_SIGNATURES["cakeb200_kshard_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
@@ -415,6 +424,75 @@ def cake_sgemm_noalloc(A, B, C=None, stream=None):
         C = _empty_like_kind(A, (M, N))
     _check(lib().cakeb200_sgemm_noalloc(_ptr(A), _ptr(B), _ptr(C), M, N, K, _stream_of(C, stream)))
     return C
+
+
+IPC_HANDLE_BYTES = 64
+
+
+def kshard_rows(M, world, rank):
+    """[lo, hi) of the rows of C that `rank` owns in a K-sharded product (whole 128-row tiles)."""
+    lo, hi = _i(), _i()
+    _check(lib().cakeb200_kshard_rows(M, world, rank, ctypes.byref(lo), ctypes.byref(hi)))
+    return lo.value, hi.value
+
+
+def kshard_supported(M, N, K_local, sm_count=0):
+    """Whether the K-sharded exchange takes a product of this shape per rank (few tiles, deep K).
+    sm_count > 0 answers without a device."""
+    return bool(lib().cakeb200_kshard_supported(M, N, K_local, sm_count))
+
+
+class KShard:
+    """One rank's end of a product whose K is sharded over the GPUs of a box: this rank's
+    partial rows go straight into the owners' memory while its tiles are summed, and the
+    owner adds the slots of all ranks in rank order.  `handle` is what the other ranks
+    need (64 bytes) for `connect`; `KShard.connect_local` wires objects of one process."""
+
+    def __init__(self, world, rank, M, N):
+        self.world, self.rank, self.M, self.N = world, rank, M, N
+        self._h = _vp()
+        buf = (ctypes.c_ubyte * IPC_HANDLE_BYTES)()
+        _check(lib().cakeb200_kshard_create(world, rank, M, N, ctypes.byref(self._h), buf))
+        self.handle = bytes(buf)
+        self.rows = kshard_rows(M, world, rank)
+
+    def connect(self, handles):
+        """handles: the `handle` of every rank, in rank order (one bytes object of world x 64, or a list)."""
+        blob = handles if isinstance(handles, (bytes, bytearray)) else b"".join(handles)
+        if len(blob) != self.world * IPC_HANDLE_BYTES:
+            raise ValueError("expected one 64-byte handle per rank")
+        arr = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+        _check(lib().cakeb200_kshard_connect_ipc(self._h, arr))
+
+    @staticmethod
+    def connect_local(objects):
+        arr = (_vp * len(objects))(*[o._h.value for o in objects])
+        for o in objects:
+            _check(lib().cakeb200_kshard_connect_local(o._h, arr))
+
+    def partial(self, A_k, B_k, stream=None):
+        """A_k: this rank's columns of A (M x Kr, rows may be strided), B_k: the same rows of B (Kr x N)."""
+        if A_k.stride(1) != 1 or B_k.stride(1) != 1:
+            raise TypeError("operands need unit stride along their rows")
+        M, Kr = A_k.shape
+        if (M, B_k.shape[0], B_k.shape[1]) != (self.M, Kr, self.N):
+            raise ValueError("operand shapes do not match this product")
+        _check(lib().cakeb200_kshard_partial(self._h, _vp(A_k.data_ptr()), A_k.stride(0), _vp(B_k.data_ptr()), B_k.stride(0),
+                                             Kr, _stream_of(A_k, stream)))
+
+    def finish(self, out=None, wait_limit_us=0, stream=None):
+        """This rank's rows of C (rows[0]:rows[1]); blocks until they are complete."""
+        import torch
+        lo, hi = self.rows
+        if out is None:
+            out = torch.empty((hi - lo, self.N), dtype=torch.float32, device="cuda")
+        _check(lib().cakeb200_kshard_finish(self._h, _ptr(out), wait_limit_us, _stream_of(out, stream)))
+        return out
+
+    def close(self):
+        if self._h:
+            lib().cakeb200_kshard_destroy(self._h)
+            self._h = _vp()
 
 
 def profile_begin():

@@ -661,6 +661,215 @@ int cakeb200_selftest_bounded_wait(int limit_us, void* stream) {
     return check_status_word(st, s);  // expected: CAKEB200_ERR_DEVICE_TIMEOUT, "where" 900
 }
 
+// ---- K-sharded product over the GPUs of one box: exchange object
+
+struct cakeb200_kshard {
+    int world = 0, rank = 0, M = 0, N = 0, device = -1;
+    int row_lo[MAX_RANKS + 1] = {};
+    long long slot_floats = 0;
+    size_t bytes = 0;
+    char* peer[MAX_RANKS] = {};    // peer[rank] is this rank's own buffer
+    bool ipc_opened[MAX_RANKS] = {};
+    bool connected = false;
+    int epoch = 0;
+};
+
+namespace {
+constexpr size_t KSHARD_HEADER = 1024;   // flags of the source ranks at byte 0, counter of finished CTAs at byte 128
+constexpr size_t KSHARD_DONE_AT = 128;
+
+void kshard_row_block(int M, int world, int rank, int* lo, int* hi) {
+    const long long tiles = (M + 127) / 128;
+    const long long a = tiles * rank / world * 128, b = tiles * (rank + 1) / world * 128;
+    *lo = (int) std::min<long long>(a, M);
+    *hi = (rank == world - 1) ? M : (int) std::min<long long>(b, M);
+}
+}  // namespace
+
+int cakeb200_kshard_rows(int M, int world, int rank, int* lo, int* hi) {
+    if (M < 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || !lo || !hi) {
+        set_error("kshard_rows: bad argument");
+        return CAKEB200_ERR_ARG;
+    }
+    kshard_row_block(M, world, rank, lo, hi);
+    return CAKEB200_OK;
+}
+
+int cakeb200_kshard_supported(int M, int N, int K_local, int sm_count) {
+    if (sm_count <= 0) {
+        DeviceState* st = device_state();
+        if (!st) return 0;
+        sm_count = st->sm_count;
+    }
+    return tf32x3_all_tiles_in_pieces(M, N, K_local, CAKEB200_SCHED_KMN, sm_count) ? 1 : 0;
+}
+
+int cakeb200_kshard_create(int world, int rank, int M, int N, cakeb200_kshard** out, unsigned char* ipc_handle) {
+    if (!out || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || M < 1 || N < 1) {
+        set_error("kshard_create: bad argument (world 1..%d)", MAX_RANKS);
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cakeb200_kshard* x = new cakeb200_kshard();
+    x->world = world; x->rank = rank; x->M = M; x->N = N; x->device = st->device;
+    int most = 0;
+    for (int r = 0; r < world; r++) {
+        int lo, hi;
+        kshard_row_block(M, world, r, &lo, &hi);
+        x->row_lo[r] = lo;
+        x->row_lo[r + 1] = hi;
+        most = std::max(most, hi - lo);
+    }
+    x->slot_floats = ((long long) most * N + 3) / 4 * 4;
+    x->bytes = KSHARD_HEADER + (size_t) 2 * world * x->slot_floats * sizeof(float);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, x->bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, KSHARD_HEADER);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess && ipc_handle) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == CAKEB200_IPC_HANDLE_BYTES, "size of an IPC handle");
+        cudaIpcMemHandle_t h;
+        e = cudaIpcGetMemHandle(&h, p);
+        if (e == cudaSuccess) memcpy(ipc_handle, &h, sizeof(h));
+    }
+    if (e != cudaSuccess) {
+        set_error("kshard_create: %s", cudaGetErrorString(e));
+        if (p) cudaFree(p);
+        delete x;
+        return CAKEB200_ERR_CUDA;
+    }
+    x->peer[rank] = (char*) p;
+    x->connected = (world == 1);
+    *out = x;
+    return CAKEB200_OK;
+}
+
+int cakeb200_kshard_connect_ipc(cakeb200_kshard* x, const unsigned char* handles) {
+    if (!x || !handles) {
+        set_error("kshard_connect_ipc: null argument");
+        return CAKEB200_ERR_ARG;
+    }
+    for (int r = 0; r < x->world; r++) {
+        if (r == x->rank || x->peer[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t) r * CAKEB200_IPC_HANDLE_BYTES, sizeof(h));
+        void* p = nullptr;
+        CAKE_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        x->peer[r] = (char*) p;
+        x->ipc_opened[r] = true;
+    }
+    x->connected = true;
+    return CAKEB200_OK;
+}
+
+int cakeb200_kshard_connect_local(cakeb200_kshard* x, cakeb200_kshard* const* all) {
+    if (!x || !all) {
+        set_error("kshard_connect_local: null argument");
+        return CAKEB200_ERR_ARG;
+    }
+    for (int r = 0; r < x->world; r++) {
+        if (!all[r] || all[r]->world != x->world || all[r]->rank != r || all[r]->M != x->M || all[r]->N != x->N ||
+            all[r]->device != x->device) {
+            set_error("kshard_connect_local: object %d does not belong to this product", r);
+            return CAKEB200_ERR_ARG;
+        }
+        x->peer[r] = all[r]->peer[r];
+    }
+    x->connected = true;
+    return CAKEB200_OK;
+}
+
+int cakeb200_kshard_partial(cakeb200_kshard* x, const float* A, int lda, const float* B, int ldb, int K_local, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!x || !A || !B) {
+        set_error("kshard_partial: null argument");
+        return CAKEB200_ERR_ARG;
+    }
+    if (!x->connected) {
+        set_error("kshard_partial: the ranks are not connected yet");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(x->M, x->N, K_local)) return CAKEB200_ERR_ARG;
+    if (lda < K_local || ldb < x->N || !on_device(A) || !on_device(B)) {
+        set_error("kshard_partial: needs device operands with lda >= K and ldb >= N");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    if (st->device != x->device) {
+        set_error("kshard_partial: called on device %d, created on device %d", st->device, x->device);
+        return CAKEB200_ERR_ARG;
+    }
+    if (!tf32x3_all_tiles_in_pieces(x->M, x->N, K_local, CAKEB200_SCHED_KMN, st->sm_count)) {
+        set_error("kshard_partial: shape %d x %d x %d is not one this path takes (cakeb200_kshard_supported)", x->M, K_local, x->N);
+        return CAKEB200_ERR_ARG;
+    }
+    cudaStream_t s = (cudaStream_t) stream;
+    int rc;
+    if ((rc = ensure_scratch(st, tf32x3_scratch_bytes(x->M, x->N, K_local, st->sm_count)))) return rc;
+    x->epoch++;
+    const int set = x->epoch & 1;
+    OwnerSlots os = {};
+    os.world = x->world;
+    os.epoch = x->epoch;
+    os.done = (unsigned*) (x->peer[x->rank] + KSHARD_DONE_AT);
+    for (int o = 0; o < x->world; o++) {
+        os.base[o] = (float*) (x->peer[o] + KSHARD_HEADER) + ((long long) set * x->world + x->rank) * x->slot_floats;
+        os.flag[o] = (int*) x->peer[o] + x->rank;
+        os.row_lo[o] = x->row_lo[o];
+    }
+    os.row_lo[x->world] = x->row_lo[x->world];
+    GemmProblem g = {};
+    g.A = A; g.B = B; g.C = nullptr;
+    g.M = x->M; g.N = x->N; g.K = K_local;
+    g.lda = lda; g.ldb = ldb; g.ldc = x->N;
+    g.batch = 1;
+    g.order = CAKEB200_SCHED_KMN;
+    g.owners = &os;
+    g_stats.kernel = CAKEB200_KERNEL_TF32X3;
+    g_stats.sched = g.order;
+    return launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats, nullptr);
+}
+
+int cakeb200_kshard_finish(cakeb200_kshard* x, float* C_block, int wait_limit_us, void* stream) {
+    if (!x || x->epoch == 0) {
+        set_error("kshard_finish: no product in flight");
+        return CAKEB200_ERR_ARG;
+    }
+    const int rows = x->row_lo[x->rank + 1] - x->row_lo[x->rank];
+    if (rows > 0 && (!C_block || !on_device(C_block))) {
+        set_error("kshard_finish: needs a device pointer for this rank's rows");
+        return CAKEB200_ERR_ARG;
+    }
+    if (wait_limit_us < 0 || wait_limit_us > 60 * 1000000) {
+        set_error("kshard_finish: limit must be between 0 (default, 2 s) and 60 s");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = (cudaStream_t) stream;
+    const int set = x->epoch & 1;
+    const float* slots = (const float*) (x->peer[x->rank] + KSHARD_HEADER) + (long long) set * x->world * x->slot_floats;
+    const long long limit_ns = wait_limit_us ? (long long) wait_limit_us * 1000 : 2000000000LL;
+    int rc = launch_sum_owner_slots(slots, x->slot_floats, x->world, C_block, (long long) rows * x->N,
+                                    (const int*) x->peer[x->rank], x->epoch, limit_ns, st->status_word, st->sm_count, s);
+    if (rc) return rc;
+    g_stats.launches += 1;
+    return check_status_word(st, s);
+}
+
+int cakeb200_kshard_destroy(cakeb200_kshard* x) {
+    if (!x) return CAKEB200_OK;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < x->world; r++)
+        if (x->ipc_opened[r]) cudaIpcCloseMemHandle(x->peer[r]);
+    if (x->peer[x->rank]) cudaFree(x->peer[x->rank]);
+    cudaGetLastError();
+    delete x;
+    return CAKEB200_OK;
+}
+
 int cakeb200_sgemv(const float* A, const float* x, float* y, int M, int K, int col_major, int accumulate, void* stream) {
     g_stats = cakeb200_stats();
     if (!A || !x || !y) {

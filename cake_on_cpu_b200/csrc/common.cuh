@@ -43,6 +43,24 @@ struct GemmProblem {
     // trans_b -> B points at an N x K row-major matrix (ldb >= K); the product is op(A) * op(B)
     int trans_a, trans_b;
     const float* bias;  // length N, added to every row of the result (nullptr: none)
+    // 3xTF32 path only, K-sharded product over several GPUs: when set, the rows of the result are not
+    // stored at C but sent to the ranks that own them (see OwnerSlots)
+    const struct OwnerSlots* owners;
+};
+
+// Where the rows of one rank's partial product go when K is sharded over the GPUs of a box.  Rows
+// [row_lo[o], row_lo[o+1]) of the result belong to rank o; this rank's partial sums of those rows are
+// stored, dense with N columns, from base[o] on, which is memory of rank o's GPU (mapped into this
+// process) reserved for this source rank.  When every row has been stored, flag[o] (also in rank o's
+// memory) is set to `epoch`.
+constexpr int MAX_RANKS = 8;
+struct OwnerSlots {
+    float* base[MAX_RANKS];
+    int* flag[MAX_RANKS];
+    int row_lo[MAX_RANKS + 1];
+    int world;
+    int epoch;
+    unsigned* done;  // counter in this GPU's memory: CTAs of the storing kernel that have finished
 };
 
 // Per-device state: scratch arena that grows on demand and is reused between calls.
@@ -109,6 +127,14 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
                          long long out_image_stride = 0);
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
                         int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
+// true when the tile plan of this shape cuts every tile into K pieces, so that the kernel that sums the
+// pieces is the only one that stores rows of the result (the condition for GemmProblem::owners)
+bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count);
+// K-sharded product, second half (kshard.cu): wait (bounded) for every rank's flag, then
+// out[i] = sum over source ranks r of slots[r * slot_floats + i], i < count, in rank order
+int launch_sum_owner_slots(const float* slots, long long slot_floats, int world, float* out, long long count,
+                           const int* flags, int epoch, long long limit_ns, int* status_word, int sm_count,
+                           cudaStream_t stream);
 
 
 #ifdef __CUDACC__

@@ -497,6 +497,51 @@ reduce_pieces_kernel(const float* __restrict__ partials, const TilePieces* __res
     }
 }
 
+// The same sum for a K-sharded product: the rows of every summed tile go to the rank that owns them,
+// over NVLink, with plain stores into that rank's memory (the slot reserved there for this rank), as
+// soon as the tile is summed.  The CTA that finishes last tells every owner that this rank's rows are
+// complete.  Nothing here waits: the owners wait (bounded) in sum_owner_slots_kernel.
+template <int BN>
+__global__ void __launch_bounds__(256)
+reduce_pieces_to_owners_kernel(const float* __restrict__ partials, const TilePieces* __restrict__ tiles, int M, int N,
+                               const OwnerSlots os) {
+    const TilePieces t = tiles[blockIdx.x];
+    const float* base = partials + (long long) t.first_slot * (BM * BN);
+    const int rows_per = BM / (int) gridDim.y, r_lo = (int) blockIdx.y * rows_per;
+    const bool vec = (N % 4 == 0);
+    for (int i = threadIdx.x; i < rows_per * BN / 4; i += blockDim.x) {
+        const int r = r_lo + i / (BN / 4), c = (i % (BN / 4)) * 4;
+        const int row = t.tm * BM + r, col = t.tn * BN + c;
+        if (row >= M || col >= N) continue;
+        float4 s = *reinterpret_cast<const float4*>(base + (long long) r * BN + c);
+        for (int p = 1; p < t.count; p++) {
+            const float4 v = *reinterpret_cast<const float4*>(base + (long long) p * (BM * BN) + (long long) r * BN + c);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        int o = 0;
+        while (o + 1 < os.world && row >= os.row_lo[o + 1]) o++;
+        float* dst = os.base[o] + (long long) (row - os.row_lo[o]) * N + col;
+        if (vec) {
+            *reinterpret_cast<float4*>(dst) = s;  // N % 4 == 0 and col % 4 == 0: whole and 16-byte aligned
+        } else {
+            const float e[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (col + j < N) dst[j] = e[j];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();  // this CTA's rows are visible to the owners before it is counted
+        const unsigned total = gridDim.x * gridDim.y;
+        if (atomicAdd(os.done, 1u) == total - 1) {
+            *os.done = 0;  // ready for the next product on this stream
+            __threadfence_system();
+            for (int o = 0; o < os.world; o++) *reinterpret_cast<volatile int*>(os.flag[o]) = os.epoch;
+        }
+    }
+}
+
 // ------------------------------------------------------------- host side
 
 typedef CUresult (*encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -807,6 +852,10 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     // CTA (32768^3: 400 ms in one launch, 313 ms in ranges of 8192, at the cost of re-reading C three times).
     const int total_kb = a.kblocks;
     const int range_kb = (total_kb > 512 && tiles >= 4LL * sm_count && g.out_p == 0) ? 256 : total_kb;
+    if (g.owners && !(range_kb == total_kb && a.units && plan->num_pieces > 0 && plan->dp_tiles == 0)) {
+        set_error("sgemm_tf32x3: a K-sharded product needs a shape whose tiles are all cut into K pieces");
+        return CAKEB200_ERR_ARG;
+    }
     if (range_kb < total_kb) {
         a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
         grid = (int) std::min<long long>(tiles, sm_count);
@@ -824,7 +873,11 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
     CAKE_CUDA_OK(cudaGetLastError());
     if (launches) (*launches)++;
-    if (a.units && plan->num_pieces > 0) {
+    if (g.owners) {
+        reduce_pieces_to_owners_kernel<BN><<<dim3(plan->num_pieces, 16), 256, 0, stream>>>(partials, plan->pieces, g.M, g.N, *g.owners);
+        CAKE_CUDA_OK(cudaGetLastError());
+        if (launches) (*launches)++;
+    } else if (a.units && plan->num_pieces > 0) {
         reduce_pieces_kernel<BN><<<dim3(plan->num_pieces, 16), 256, 0, stream>>>(partials, plan->pieces, g.C, g.M, g.N, g.ldc, g.accumulate,
                                                                       g.out_p, g.out_image_stride, g.bias);
         CAKE_CUDA_OK(cudaGetLastError());
@@ -960,6 +1013,15 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     const size_t Kp = (size_t) padded_k(K);
     const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
     return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
+}
+
+bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
+    if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return false;
+    const int bn = tile_width(N), kblocks = (K + BK - 1) / BK;
+    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    if (tiles >= sm_count) return false;
+    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, bn);
+    return hp.dp_tiles == 0 && !hp.pieces.empty();
 }
 
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word, int sm_count,

@@ -7,7 +7,12 @@ calls the library on its share and nothing is exchanged.
 Rows (or columns) of C are independent, so each rank multiplies its block with
 the library and nothing is exchanged.  Only the deep-K shape is different: K is
 cut, every rank produces a full-size partial product, and the partials are
-summed with a reduce-scatter so that rank r ends up with its row block of C.
+summed so that rank r ends up with its row block of C.  Where the library's
+K-shard exchange takes the shape (few tiles, deep K: the case this split exists
+for) the sum needs no collective: while a rank sums its tiles it stores the rows
+straight into the owners' memory over NVLink and each owner adds the slots in
+rank order (api.KShard).  Other shapes, and `exchange="nccl"`, use an NCCL
+reduce-scatter.
 The reference has no distributed layer; its K-first schedule splits a block of
 rows over cores in the same way (reference src/cake_sgemm_k_first.cpp:85-129).
 """
@@ -22,11 +27,39 @@ def _local(a, b, kernel):
     return api.cake_sgemm(a.contiguous(), b.contiguous(), out, kernel=kernel)
 
 
-def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
+_exchanges = {}
+
+
+def _exchange(M, N, world, rank, group):
+    """The K-shard exchange object of this shape, created and connected on first use (collective)."""
+    key = (M, N, world, id(group))
+    x = _exchanges.get(key)
+    if x is None:
+        x = api.KShard(world, rank, M, N)
+        mine = torch.tensor(list(x.handle), dtype=torch.uint8, device="cuda")
+        every = torch.empty(world * api.IPC_HANDLE_BYTES, dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(every, mine, group=group)
+        x.connect(bytes(every.cpu().numpy().tobytes()))
+        _exchanges[key] = x
+    return x
+
+
+def release(group=None):
+    """Free the exchange buffers (collective: no rank may still be storing into another's)."""
+    if dist.is_initialized() and _exchanges:
+        torch.cuda.synchronize()
+        dist.barrier(group)
+    for x in _exchanges.values():
+        x.close()
+    _exchanges.clear()
+
+
+def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None, exchange="auto"):
     """A (M x K) and B (K x N) are CUDA tensors present on every rank.  Returns
     (kind, span, block): kind 'rows' -> span (lo, hi), block = C[lo:hi, :]; 'cols' ->
     C[:, lo:hi]; 'grid' -> span (r0, r1, c0, c1), block = C[r0:r1, c0:c1]; 'k' ->
-    C[lo:hi, :] after the reduce-scatter."""
+    C[lo:hi, :] after the partial products have been summed.  exchange: 'auto' (stores into
+    the owners' memory where the library takes the shape, else NCCL), 'stores', 'nccl'."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     M, K = A.shape
@@ -53,6 +86,17 @@ def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None):
         # the column block of B is read where it lies (leading dimension N), no copy
         return kind, (r0, r1, c0, c1), api.cake_sgemm_ex(A[r0:r1], B[:, c0:c1], kernel=kernel)
     k0, k1 = partition.k_block(K, world, rank)
+    if exchange not in ("auto", "stores", "nccl"):
+        raise ValueError("exchange must be 'auto', 'stores' or 'nccl'")
+    if exchange != "nccl" and world > 1 and kernel != api.KERNEL_FFMA:
+        # every rank evaluates every rank's share, so all of them take the same route
+        shares = [partition.k_block(K, world, r) for r in range(world)]
+        if all(api.kshard_supported(M, N, b - a) for a, b in shares):
+            x = _exchange(M, N, world, rank, group)
+            x.partial(A[:, k0:k1], B[k0:k1])  # column range of A read where it lies (leading dimension K)
+            return kind, x.rows, x.finish()
+        if exchange == "stores":
+            raise ValueError("the K-shard exchange does not take this shape")
     partial = _local(A[:, k0:k1], B[k0:k1], kernel)
     r0, r1 = partition.row_block(M, world, rank)
     block, span = reduce_scatter(partial, r0, r1)

@@ -151,6 +151,45 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
  * reference src/cake_sgemm.cpp:49-52.) */
 int cakeb200_selftest_bounded_wait(int limit_us, void* stream);
 
+/* ---- One product with K sharded over the GPUs of one box, one process per GPU.
+ *
+ * For shapes whose M and N are too small to give every GPU its own rows or columns of C
+ * (deep, narrow products such as 1024 x 262144 x 1024).  Rank r holds columns
+ * [k0, k1) of A and the same rows of B, multiplies them, and while its tiles are being
+ * summed stores each row of the partial result straight into the memory of the rank
+ * that owns that row (plain stores over NVLink into a slot reserved for rank r); the
+ * owner then adds the `world` slots in rank order.  Nothing but those rows crosses the
+ * link, no library collective is involved, and the result does not depend on timing.
+ * This is the reference's K-first core split (src/cake_sgemm_k_first.cpp:85-129: every
+ * core adds its share of K into a private copy of the block, the copies are combined
+ * afterwards) with GPUs in place of cores.
+ *
+ * Rows are owned in whole 128-row tiles: cakeb200_kshard_rows gives [lo, hi) of a rank.
+ * Call order on every rank: create -> exchange the 64-byte handles between the
+ * processes by any means -> connect_ipc -> any number of (partial, finish) pairs, the
+ * same number on every rank, all on one stream -> a barrier of the caller's -> destroy.
+ * cakeb200_kshard_finish blocks until this rank's rows are complete; it waits at most
+ * `wait_limit_us` (0: 2 s) for the other ranks and otherwise returns
+ * CAKEB200_ERR_DEVICE_TIMEOUT with "where 910" and the missing rank in the error text,
+ * leaving the context usable.  cakeb200_kshard_supported tells (without a device when
+ * sm_count > 0) whether a shape is one this path takes: products with few tiles and a
+ * deep K; others return CAKEB200_ERR_ARG from cakeb200_kshard_partial and are summed
+ * with a reduce-scatter by the caller.  world <= 8.
+ *
+ * cakeb200_kshard_connect_local wires up objects that all live in this process on one
+ * device, so that the whole exchange can be exercised on a single GPU: run `partial` for
+ * every rank, then `finish` for every rank. */
+#define CAKEB200_IPC_HANDLE_BYTES 64
+typedef struct cakeb200_kshard cakeb200_kshard;
+int cakeb200_kshard_rows(int M, int world, int rank, int* lo, int* hi);
+int cakeb200_kshard_supported(int M, int N, int K_local, int sm_count);
+int cakeb200_kshard_create(int world, int rank, int M, int N, cakeb200_kshard** out, unsigned char* ipc_handle);
+int cakeb200_kshard_connect_ipc(cakeb200_kshard* x, const unsigned char* handles /* world x 64 bytes, by rank */);
+int cakeb200_kshard_connect_local(cakeb200_kshard* x, cakeb200_kshard* const* all /* world objects, by rank */);
+int cakeb200_kshard_partial(cakeb200_kshard* x, const float* A, int lda, const float* B, int ldb, int K_local, void* stream);
+int cakeb200_kshard_finish(cakeb200_kshard* x, float* C_block, int wait_limit_us, void* stream);
+int cakeb200_kshard_destroy(cakeb200_kshard* x);
+
 /* y (+)= A x for an M x K matrix.  col_major != 0: A[k*M + m], the layout of the
  * reference's matrix-vector driver; else row-major A[m*K + k], the N = 1 case of
  * cake_sgemm.  accumulate != 0 adds to y, which is what the reference's driver

@@ -115,3 +115,20 @@ def test_convolution_plan_routes_and_tilings():
         assert p["positions_tile"] <= 128 and p["channel_tile"] % 16 == 0 and p["channel_tile"] <= 128
     with pytest.raises(cake.CakeError):
         cake.conv_plan(1, 1, 2, 2, 1, 3, 3, 1, 0)  # filter larger than the padded image
+
+
+def test_kshard_rows_match_the_partition_module_and_shape_query_needs_no_device():
+    from cake_on_cpu_b200 import api, partition
+    for M in (1, 127, 128, 129, 300, 1000, 1024, 5000):
+        for world in (1, 2, 3, 4, 8):
+            blocks = [api.kshard_rows(M, world, r) for r in range(world)]
+            assert blocks == [partition.row_block(M, world, r) for r in range(world)]
+            assert blocks[0][0] == 0 and blocks[-1][1] == M
+            assert all(blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
+    # few tiles and a deep K: taken; many tiles or a shallow K: not
+    assert api.kshard_supported(1024, 1024, 32768, sm_count=148)
+    assert api.kshard_supported(512, 256, 8192, sm_count=148)
+    assert not api.kshard_supported(8192, 8192, 1024, sm_count=148)
+    assert not api.kshard_supported(256, 256, 256, sm_count=148)
+    with pytest.raises(api.CakeError):
+        api.kshard_rows(100, 9, 0)  # more ranks than the exchange has slots for

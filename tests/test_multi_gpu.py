@@ -1,5 +1,6 @@
 """One process per GPU over NCCL: row split, column split, the 2 x 2 grid and the K split
-with its reduce-scatter, each checked against a float64 product.  Needs two (four) GPUs;
+(summed by stores into the owners' memory and, for comparison, by a reduce-scatter), each
+checked against a float64 product.  Needs two (four) GPUs;
 skipped on a single-GPU box (the host logic is covered on CPU by test_partition_gloo.py)."""
 import os
 import socket
@@ -43,6 +44,11 @@ def _worker(rank, world, port, out, cases=TWO_RANK_CASES):
         else:
             cut = lambda X: X[span[0]:span[1]]
         err = ((block.double() - cut(full)).abs() / cut(den)).max().item() if block.shape == cut(full).shape else float("inf")
+        if kind == "k":
+            # the same product summed by NCCL instead of by stores into the owners' memory
+            _, span2, block2 = distributed.sharded_sgemm(A, B, exchange="nccl")
+            err2 = ((block2.double() - full[span2[0]:span2[1]]).abs() / den[span2[0]:span2[1]]).max().item()
+            err = max(err, err2)
         results.append((kind == want, err, span[0], span[1], block.numel()))
     # independent units: batch items, row blocks of a sparse operand, images of a convolution
     g = torch.Generator(device="cuda").manual_seed(6)
@@ -63,6 +69,7 @@ def _worker(rank, world, port, out, cases=TWO_RANK_CASES):
     dist.all_gather_object(gathered, (results, units))
     if rank == 0:
         out.put(gathered)
+    distributed.release()
     dist.barrier()
     dist.destroy_process_group()
 
