@@ -213,8 +213,9 @@ DEFAULT = [k for k in CONFIGS if k not in ("square_32768", "sparse_50_zero_skipp
 
 def _distributed(name, reps):
     """One product over all ranks of a torchrun launch (NCCL): every rank holds only its own share of the
-    operands (row block, column block, grid block or K slice) before the timed region; the K split ends with the
-    reduce-scatter that leaves every rank with its row block of C.  Device time, maximum over ranks."""
+    operands (row block, column block, grid block or K slice) before the timed region; the K split is timed twice,
+    with the partial rows stored into the owners' memory by the summing kernel and with an NCCL reduce-scatter,
+    either of which leaves every rank with its row block of C.  Device time, maximum over ranks."""
     import os
     import torch.distributed as dist
     from . import distributed, partition
@@ -232,12 +233,24 @@ def _distributed(name, reps):
         A, B = _uniform(g, M, k1 - k0), _uniform(g, k1 - k0, N)
         out = torch.empty((M // world, N), device="cuda") if M % world == 0 else None
 
-        def step():
+        def step_nccl():
             partial = api.cake_sgemm(A, B)
             if out is not None:
                 dist.reduce_scatter_tensor(out, partial)
             else:
                 dist.all_reduce(partial)
+
+        steps = [("reduce-scatter of the partial products (NCCL)", step_nccl)]
+        shares = [partition.k_block(K, world, r) for r in range(world)]
+        if world > 1 and all(api.kshard_supported(M, N, b - a) for a, b in shares):
+            x = distributed._exchange(M, N, world, rank, None)
+            mine = torch.empty((x.rows[1] - x.rows[0], N), device="cuda")
+
+            def step_stores():
+                x.partial(A, B)
+                x.finish(mine)
+
+            steps.insert(0, ("rows stored into the owners' memory while the tiles are summed, owners add the slots", step_stores))
     else:
         r0, r1, c0, c1 = (partition.grid_block(M, N, K, world, rank) if kind == "grid" else
                           partition.row_block(M, world, rank) + (0, N) if kind == "rows" else
@@ -247,25 +260,28 @@ def _distributed(name, reps):
 
         def step():
             api.cake_sgemm(A, B, C)
-    for _ in range(3):
-        step()
+
+        steps = [("none", step)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    best = float("inf")
-    for _ in range(max(reps, 3)):
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        step()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        best = min(best, float(t.item()))
-    if rank == 0:
-        flops = 2.0 * M * N * K
-        print(json.dumps({"config": name, "ranks": world, "split": kind, "ms": round(best, 4), "flops": flops,
-                          "tflops": round(flops / best / 1e9, 2), "exchange": "reduce-scatter of the partial products" if kind == "k" else "none"}),
-              flush=True)
+    for exchange, step in steps:
+        for _ in range(3):
+            step()
+        best = float("inf")
+        for _ in range(max(reps, 3)):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            best = min(best, float(t.item()))
+        if rank == 0:
+            flops = 2.0 * M * N * K
+            print(json.dumps({"config": name, "ranks": world, "split": kind, "ms": round(best, 4), "flops": flops,
+                              "tflops": round(flops / best / 1e9, 2), "exchange": exchange}), flush=True)
+    distributed.release()
     dist.barrier()
     dist.destroy_process_group()
 
