@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--size", type=int, default=8192, help="M = K = N (default: the headline 8192)")
     ap.add_argument("--kernel", default="tf32x3", choices=["tf32x3", "ffma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     return ap.parse_args()
 
 
@@ -67,7 +68,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -101,7 +102,7 @@ def cpu_threads_and_ctx(ref):
     return ctx, info
 
 
-def time_reference(size, steps, warmup, budget_s=150.0):
+def time_reference(size, steps, warmup, budget_s=200.0):
     """Reference CPU cake_sgemm (oracle/_ref) on a bounded row sample of the size^3 product."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
@@ -127,9 +128,10 @@ def time_reference(size, steps, warmup, budget_s=150.0):
     A = O.uniform((probe_rows, K), 1)
     t_probe = run(A, B)
     rate = 2.0 * probe_rows * K * N / max(t_probe, 1e-9)
-    per_step_target = min(2.0, budget_s / max(steps + warmup, 1))
+    # the whole product per step when the run then still ends within the budget, else a block of its rows
+    per_step_target = budget_s / max(steps + warmup, 1)
     rows = int(min(size, max(128, rate * per_step_target / (2.0 * K * N))))
-    rows = max(128, rows // 128 * 128)
+    rows = size if rows >= size else max(128, rows // 128 * 128)
     A = O.uniform((rows, K), 1)
     for _ in range(warmup):
         run(A, B)
@@ -137,8 +139,9 @@ def time_reference(size, steps, warmup, budget_s=150.0):
     total = sum(times)
     tflops = 2.0 * rows * K * N * steps / total / 1e12
     return {"value": tflops, "unit": UNIT, "cores": cores, "kind": kind,
-            "sample": "%d x %d x %d row block of the %d^3 product per step, %d steps (+%d warm-up); time = value "
-                      "returned by cake_sgemm (packing included); host context %s" % (rows, K, N, size, steps, warmup, info),
+            "sample": "%s per step, %d steps (+%d warm-up); time = value returned by cake_sgemm (packing included); "
+                      "host context %s" % ("the whole %d^3 product" % size if rows == size else
+                                           "%d x %d x %d row block of the %d^3 product" % (rows, K, N, size), steps, warmup, info),
             "ms_per_step": total / steps * 1e3}
 
 
@@ -151,7 +154,7 @@ def reference_arm(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "dense FP32 SGEMM M=K=N=%d, uniform(-1,1), seeded" % args.size, "kernel": "reference CPU cake_sgemm",
-                       "step": "one cake_sgemm call on a row block of the product (see cpu_baseline.sample)"},
+                       "step": "one cake_sgemm call (see cpu_baseline.sample)"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -160,11 +163,25 @@ def reference_arm(args):
 
 # ----------------------------------------------------------------- GPU arm
 
+def sampled_parity(torch, A_rows, B_cols, C_block, seed, side=32):
+    """Largest deviation of side x side entries of this rank's block of C from a float64 recomputation:
+    (normalised by ||A[m,:]|| ||B[:,n]||, absolute, entries)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    rows = torch.as_tensor(np.sort(rng.choice(C_block.shape[0], min(side, C_block.shape[0]), replace=False)), device="cuda")
+    cols = torch.as_tensor(np.sort(rng.choice(C_block.shape[1], min(side, C_block.shape[1]), replace=False)), device="cuda")
+    a, b = A_rows[rows].double(), B_cols[:, cols].double()
+    d = (C_block[rows][:, cols].double() - a @ b).abs()
+    den = a.norm(dim=1)[:, None] * b.norm(dim=0)[None, :]
+    return (d / den.clamp_min(1e-30)).max().item(), d.max().item(), rows.numel() * cols.numel()
+
+
 def gpu_arm(args):
+    import numpy as np
     import torch
     import cake_on_cpu_b200 as cake
-    from cake_on_cpu_b200 import build
-    from cake_on_cpu_b200.partition import grid_block, grid_shape
+    from cake_on_cpu_b200 import build, distributed, seeded
+    from cake_on_cpu_b200.partition import grid_block, grid_shape, k_block, row_block
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -180,6 +197,18 @@ def gpu_arm(args):
         build.build()
     cake.lib()
 
+    def reduce_max(v):
+        t = torch.tensor([float(v)], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(v):
+        t = torch.tensor([float(v)], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
     size = args.size
     M = K = N = size
     # rank (i, j) of a pr x pc grid owns C[r0:r1, c0:c1]; nothing is exchanged (pc = 1: plain row blocks, B replicated)
@@ -188,10 +217,12 @@ def gpu_arm(args):
     rows, cols = r1 - r0, c1 - c0
     kernel = cake.KERNEL_TF32X3 if args.kernel == "tf32x3" else cake.KERNEL_FFMA
 
-    g = torch.Generator(device="cuda").manual_seed(1234)
-    A = (torch.rand((M, K), device="cuda", generator=g) * 2 - 1)[r0:r1].contiguous()
-    B = (torch.rand((K, N), device="cuda", generator=g) * 2 - 1)[:, c0:c1].contiguous()
-    C = torch.empty((rows, cols), device="cuda")
+    # the seeded streams of the benchmark configurations: A = stream 1, B = stream 2, uniform(-1, 1)
+    A_full = seeded.uniform((M, K), 1)
+    B_full = seeded.uniform((K, N), 2)
+    A = A_full[r0:r1].contiguous()
+    B = B_full[:, c0:c1].contiguous()
+    C = torch.full((rows, cols), float("nan"), device="cuda")
     stream = torch.cuda.current_stream()
 
     def step():
@@ -202,6 +233,9 @@ def gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # measured issue rate of the tensor pipe (outside every timed region)
+    tf32_rate, tf32_ms = cake.tf32_peak(5.0) if args.kernel == "tf32x3" else (None, None)
+
     # first call allocates the scratch arena (blocking entry point), then warm up
     cake.cake_sgemm(A, B, C, kernel=kernel)
     launches_per_step = cake.last_stats()["launches"]
@@ -209,52 +243,63 @@ def gpu_arm(args):
         step()
     barrier()
 
+    # K steps are timed as one region; the region is repeated so that the clock sampler sees the load for long
+    # enough, and the median region is the one reported
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    # per-kernel CUDA events inside the timed region (recorded on the launching stream, no synchronisation)
-    cake.profile_begin()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    prof_pre_ms, prof_kern_ms, prof_calls = cake.profile_end()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    if dist is not None:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_total = float(ms.item())
+    regions = []
+    for rep in range(max(args.repeats, 1)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        cake.profile_begin()  # per-kernel CUDA events inside the timed region (launching stream, no synchronisation)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        prof_pre_ms, prof_kern_ms, prof_calls = cake.profile_end()
+        calls = max(prof_calls, 1)
+        regions.append((reduce_max(e0.elapsed_time(e1)), reduce_max(prof_kern_ms / calls), reduce_max(prof_pre_ms / calls)))
     clocks = sampler.stop() if rank == 0 else None
+    regions.sort()
+    ms_total, kern_ms_avg, pre_ms_avg = regions[len(regions) // 2]
 
-    # the contraction kernel alone: average launch duration over the timed region itself
-    # (only the first 256 steps carry events)
-    calls = max(prof_calls, 1)
-    kern = torch.tensor([prof_kern_ms / calls], device="cuda")
-    pre = torch.tensor([prof_pre_ms / calls], device="cuda")
-    if dist is not None:
-        dist.all_reduce(kern, op=dist.ReduceOp.MAX)
-    kern_ms_avg = float(kern.item())
+    # parity, outside the timed region: 1024 entries of this rank's block against float64, worst over ranks
+    err_n, err_a, entries = sampled_parity(torch, A, B, C, 100 + rank)
+    parity_n, parity_a = reduce_max(err_n), reduce_max(err_a)
+    nan_blocks = reduce_sum(float(torch.isnan(C).any().item()))
 
-    # end to end through the public API: pinned host operands, copies inside the timed region
-    Ah = torch.empty((rows, K), pin_memory=True).copy_(A)
-    Bh = torch.empty((K, cols), pin_memory=True).copy_(B)
-    Ch = torch.empty((rows, cols), pin_memory=True)
+    # end to end through the public API: pinned host operands, copies inside the timed region.  One GPU: the
+    # reference's call, cake_sgemm on host pointers.  Several GPUs: row blocks of A and C, and every rank copies
+    # only its own 1/N of the rows of B from the host; the slices are gathered over NVLink into local memory.
+    er0, er1 = row_block(M, world, rank)
+    k0, k1 = k_block(K, world, rank)
+    Ah = torch.empty((er1 - er0, K), pin_memory=True).copy_(A_full[er0:er1])
+    Bh = torch.empty((k1 - k0, N), pin_memory=True).copy_(B_full[k0:k1])
+    Ch = torch.empty((er1 - er0, N), pin_memory=True)
+    del A_full
     e2e_steps = max(3, min(args.steps, 10))
-    cake.cake_sgemm(Ah.numpy(), Bh.numpy(), Ch.numpy(), kernel=kernel)
+
+    def e2e_step():
+        distributed.sharded_sgemm_host(Ah.numpy(), Bh.numpy(), Ch.numpy(), kernel=kernel)
+        return float(Ch[0, 0])
+
+    e2e_step()
+    e2e_stats = cake.last_stats()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        cake.cake_sgemm(Ah.numpy(), Bh.numpy(), Ch.numpy(), kernel=kernel)
-        _ = float(Ch[0, 0])
+        e2e_step()
     barrier()
-    e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
-    if dist is not None:
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_stats = cake.last_stats()
+    e2e_s = reduce_max(time.perf_counter() - t0)
+    e2e_n, e2e_a, _ = sampled_parity(torch, Ah.cuda(), B_full, Ch.cuda(), 200 + rank)
+    e2e_parity = reduce_max(e2e_n)
+    h2d = reduce_sum((Ah.numel() + Bh.numel()) * 4)
+    d2h = reduce_sum(Ch.numel() * 4)
 
     flops = 2.0 * M * N * K
+    ok = parity_n <= 1e-5 and e2e_parity <= 1e-5 and nan_blocks == 0
     if rank == 0:
         hbm, bf16_burst, bf16_sust, which = measured_peaks()
         peak = bf16_burst / 2 / 3 if args.kernel == "tf32x3" else 148 * 128 * 2 * 1.965e9 / 1e12
@@ -267,6 +312,18 @@ def gpu_arm(args):
         traffic = None
         if args.kernel == "tf32x3" and size == 8192:
             traffic = (5.22e9 + 0.25544e9) * (rows * cols) / float(M * N)
+        roofline = {"bound": "tensor", "kernel": "sgemm_tf32x3_kernel" if args.kernel == "tf32x3" else "sgemm_ffma_kernel",
+                    "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                    "peak_source": ("bf16 burst %.1f TFLOP/s of %s / 2 (TF32 rate) / 3 (MMAs per product)" % (bf16_burst, which))
+                    if args.kernel == "tf32x3" else "148 SMs x 128 lanes x 2 flop x 1.965 GHz",
+                    "frac_of_sustained": achieved / (bf16_sust / 6) if args.kernel == "tf32x3" else None,
+                    "kernel_ms": kern_ms_avg, "prepass_ms": pre_ms_avg, "traffic": traffic}
+        if tf32_rate:
+            # measured on this device just before the timed region: every SM issuing tcgen05.mma kind::tf32
+            # 128 x 256 x 8 back to back on resident shared-memory tiles (cakeb200_tf32_peak), no memory traffic
+            roofline["tf32_issue_rate"] = {"tflops": tf32_rate, "ms": tf32_ms, "third": tf32_rate / 3,
+                                           "frac_of_third": achieved / (tf32_rate / 3),
+                                           "how": "tcgen05.mma kind::tf32 128x256x8 issue-rate microbenchmark, measured"}
         line = {
             "metric": METRIC, "value": flops * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
@@ -276,19 +333,21 @@ def gpu_arm(args):
                                     ("%d x %d grid of GPUs: row blocks of A x column blocks of B, no exchange" % (pr, pc)),
                        "l2": "operands (%.0f MB per GPU) exceed the 126 MB L2; no flush between steps" %
                              ((rows * K + K * cols + rows * cols) * 4 / 1e6),
-                       "step": "operand split pass + contraction kernel"},
+                       "step": "operand split pass + contraction kernel",
+                       "timed_regions": "%d regions of %d steps, the median region is reported" % (len(regions), args.steps),
+                       "inputs": "counter-based streams: A = stream 1, B = stream 2 (cake_on_cpu_b200/seeded.py)"},
             "clocks": clocks,
-            "e2e": {"value": flops * e2e_steps / float(e2e_s.item()) / 1e12, "unit": UNIT,
-                    "h2d_bytes_per_step": (rows * K + K * cols) * 4, "d2h_bytes_per_step": rows * cols * 4,
-                    "ms_h2d": e2e_stats["ms_h2d"], "ms_d2h": e2e_stats["ms_d2h"], "steps": e2e_steps},
+            "parity": {"norm_err": parity_n, "abs_err": parity_a, "entries_per_rank": entries, "against": "float64",
+                       "e2e_norm_err": e2e_parity, "tolerance": 1e-5, "ok": ok},
+            "e2e": {"value": flops * e2e_steps / e2e_s / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps,
+                    "ms_h2d_last_rank0": e2e_stats["ms_h2d"], "ms_d2h_last_rank0": e2e_stats["ms_d2h"],
+                    "how": "cake_sgemm on pinned host operands" if world == 1 else
+                           "distributed.sharded_sgemm_host: row blocks of A and C; each rank copies 1/%d of the rows of B from "
+                           "the host, the slices are gathered over NVLink (NCCL all-gather) into local memory" % world},
             "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "sgemm_tf32x3_kernel" if args.kernel == "tf32x3" else "sgemm_ffma_kernel",
-                         "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "peak_source": ("bf16 burst %.1f TFLOP/s of %s / 2 (TF32 rate) / 3 (MMAs per product)" % (bf16_burst, which))
-                         if args.kernel == "tf32x3" else "148 SMs x 128 lanes x 2 flop x 1.965 GHz",
-                         "frac_of_sustained": achieved / (bf16_sust / 6) if args.kernel == "tf32x3" else None,
-                         "kernel_ms": kern_ms_avg, "prepass_ms": float(pre.item()),
-                         "traffic": traffic},
+            "roofline": roofline,
         }
         if world == 1 and not args.no_cpu_baseline:
             try:
@@ -299,8 +358,12 @@ def gpu_arm(args):
                                         "sample": "failed: %r" % (exc,)}
         print(json.dumps(line))
     if dist is not None:
+        distributed.release()
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("parity check failed: normalised error %.3e (device), %.3e (end to end), %d blocks with NaN"
+                         % (parity_n, e2e_parity, int(nan_blocks)))
 
 
 def main():

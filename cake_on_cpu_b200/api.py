@@ -71,6 +71,7 @@ _SIGNATURES = {
     "cakeb200_device_count": (_i, []),
     "cakeb200_query_cntx": (_i, [ctypes.POINTER(Cntx)]),
     "cakeb200_sgemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "cakeb200_sgemm_after": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "cakeb200_sgemm_async": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "cakeb200_sgemm_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "cakeb200_sp_sgemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
@@ -101,6 +102,9 @@ _SIGNATURES["cakeb200_kshard_partial"] = (_i, [_vp, _vp, _i, _vp, _i, _i, _vp])
 _SIGNATURES["cakeb200_kshard_finish"] = (_i, [_vp, _vp, _i, _vp])
 _SIGNATURES["cakeb200_kshard_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
+_pf = ctypes.POINTER(ctypes.c_float)
+_SIGNATURES["cakeb200_tf32_peak"] = (_i, [ctypes.c_float, _pf, _pf, _vp])
+_SIGNATURES["cakeb200_select_devices"] = (_i, [_pi, _i, _i, _i, _i, _i, _pi])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
 EXPORTED_SYMBOLS = sorted(_SIGNATURES)
@@ -140,6 +144,16 @@ def device_count():
     return lib().cakeb200_device_count()
 
 
+def select_devices(cc_major, current, p, cap=0, M=1 << 30):
+    """Device ordinals a host-pointer product with p > 1 is spread over by the C++ API
+    (cakeb200_select_devices; host logic, no device needed)."""
+    n = len(cc_major)
+    majors = (_i * n)(*cc_major)
+    out = (_i * max(n, 1))()
+    got = lib().cakeb200_select_devices(majors, n, current, p, cap, M, out)
+    return [out[k] for k in range(got)]
+
+
 def _is_torch(x):
     return type(x).__module__.startswith("torch")
 
@@ -163,6 +177,13 @@ def _empty_like_kind(ref, shape):
     return np.empty(shape, np.float32)
 
 
+def _need_shape(x, shape, what):
+    """Raise before any launch when a caller-supplied array does not have the shape the
+    kernels will read or write through its raw pointer."""
+    if tuple(x.shape) != tuple(shape):
+        raise ValueError("%s has shape %s, expected %s" % (what, tuple(x.shape), tuple(shape)))
+
+
 def _stream_of(x, stream):
     if stream is not None:
         return ctypes.c_void_p(int(stream))
@@ -175,7 +196,7 @@ def _stream_of(x, stream):
 # ------------------------------------------------------------------ the product
 
 def cake_sgemm(A, B, C=None, p=1, cake_cntx=None, packedA=False, packedB=False, alpha=1.0, beta=0.0, sch=NA,
-               kernel=KERNEL_AUTO, stream=None):
+               kernel=KERNEL_AUTO, stream=None, b_ready=None):
     """C = A @ B through the reference's operator interface
     (cake_sgemm, reference include/cake.h:12-14, src/cake_sgemm.cpp:9-175).
 
@@ -183,7 +204,9 @@ def cake_sgemm(A, B, C=None, p=1, cake_cntx=None, packedA=False, packedB=False, 
     reference: K-first overwrites C, M-first / N-first add A@B to C when
     ``beta != 0``.  ``sch`` picks the tile order (NA = derive from the shape).
     ``p`` and ``cake_cntx`` are accepted for signature parity; one process
-    drives one GPU here.  Returns C.
+    drives one GPU here.  ``b_ready`` (a ``torch.cuda.Event`` already recorded, or a
+    raw cudaEvent_t) makes the kernels wait until B is complete, see
+    cakeb200_sgemm_after.  Returns C.
     """
     if packedA or packedB:
         raise NotImplementedError("pre-packed operands go through the C++ API (include/cake.h)")
@@ -194,11 +217,19 @@ def cake_sgemm(A, B, C=None, p=1, cake_cntx=None, packedA=False, packedB=False, 
     if C is None:
         C = _empty_like_kind(A, (M, N))
         beta = 0.0
+    _need_shape(C, (M, N), "C")
     accumulate = 1 if (beta != 0 and sch in (MKN, NKM)) else 0
     if beta != 0 and sch == NA:
         # the schedule decides whether beta is honoured; resolve it the way the library will
         accumulate = 1 if last_schedule_for(M, N, K) != KMN else 0
-    _check(lib().cakeb200_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, accumulate, sch, kernel, _stream_of(C, stream)))
+    if stream is None and not (_is_torch(C) and C.is_cuda) and _is_torch(B) and B.is_cuda:
+        stream = _stream_of(B, None).value  # host result, device B: run on the stream that produces B
+    if b_ready is not None:
+        ev = ctypes.c_void_p(b_ready.cuda_event if hasattr(b_ready, "cuda_event") else int(b_ready))
+        _check(lib().cakeb200_sgemm_after(_ptr(A), _ptr(B), _ptr(C), M, N, K, accumulate, sch, kernel,
+                                          _stream_of(C, stream), ev))
+    else:
+        _check(lib().cakeb200_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, accumulate, sch, kernel, _stream_of(C, stream)))
     return C
 
 
@@ -256,8 +287,10 @@ def cake_sgemm_batched(A, B, C=None, kernel=KERNEL_AUTO, stream=None):
     path, reference include/cake.h:52-72, is one cake_sgemm per item)."""
     batch, M, K = A.shape
     _, _, N = B.shape
+    _need_shape(B, (batch, K, N), "B")
     if C is None:
         C = _empty_like_kind(A, (batch, M, N))
+    _need_shape(C, (batch, M, N), "C")
     _check(lib().cakeb200_sgemm_batched(_ptr(A), _ptr(B), _ptr(C), M, N, K, batch, kernel, _stream_of(C, stream)))
     return C
 
@@ -269,11 +302,13 @@ def cake_sgemv(A, x, y=None, col_major=False, accumulate=False, stream=None):
         K, M = A.shape
     else:
         M, K = A.shape
-    if x.shape[0] != K:
+    if (x.numel() if _is_torch(x) else x.size) != K:
         raise ValueError("vector length differs from the matrix")
     if y is None:
         y = _empty_like_kind(A, (M,))
         accumulate = False
+    if (y.numel() if _is_torch(y) else y.size) != M:
+        raise ValueError("y has %d elements, expected %d" % ((y.numel() if _is_torch(y) else y.size), M))
     _check(lib().cakeb200_sgemv(_ptr(A), _ptr(x), _ptr(y), M, K, int(bool(col_major)), int(bool(accumulate)),
                                 _stream_of(y, stream)))
     return y
@@ -283,9 +318,12 @@ def cake_sp_sgemm(A, B, C=None, kernel=KERNEL_FFMA, stream=None):
     """C = A @ B for a mostly-zero A (row-skipping product of the reference's
     sparse microkernel, reference src/kernels/haswell/sparse.cpp:7-131)."""
     M, K = A.shape
-    _, N = B.shape
+    K2, N = B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
     if C is None:
         C = _empty_like_kind(A, (M, N))
+    _need_shape(C, (M, N), "C")
     _check(lib().cakeb200_sp_sgemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, kernel, _stream_of(C, stream)))
     return C
 
@@ -299,6 +337,7 @@ def cake_conv2d(x, w, stride=1, pad=0, out=None, kernel=KERNEL_AUTO, stream=None
     Ho, Wo = (H + 2 * pad - hf) // stride + 1, (W + 2 * pad - wf) // stride + 1
     if out is None:
         out = _empty_like_kind(x, (b, cout, Ho, Wo))
+    _need_shape(out, (b, cout, Ho, Wo), "out")
     _check(lib().cakeb200_conv2d(_ptr(x), _ptr(w), _ptr(out), b, cin, H, W, cout, hf, wf, stride, pad, kernel,
                                  _stream_of(out, stream)))
     return out
@@ -358,6 +397,14 @@ def cake_sgemm_packed_C_size(M, N, p, x, cake_cntx, sch):
 
 def _pack(name, mat, packed, d0, d1, p, x, cake_cntx, stream):
     fn = getattr(lib(), "cakeb200_" + name)
+    _need_shape(mat, (d0, d1), "matrix")
+    kind = name[-1]
+    want = (cake_sgemm_packed_A_size(d0, d1, p, x, cake_cntx, x.sch) if kind == "A" else
+            cake_sgemm_packed_B_size(d0, d1, p, x, cake_cntx) if kind == "B" else
+            cake_sgemm_packed_C_size(d0, d1, p, x, cake_cntx, x.sch)) // 4
+    have = packed.numel() if _is_torch(packed) else packed.size
+    if have < want:
+        raise ValueError("packed buffer holds %d floats, the layout needs %d" % (have, want))
     _check(fn(_ptr(mat), _ptr(packed), d0, d1, p, ctypes.byref(x), ctypes.byref(cake_cntx), _stream_of(packed, stream)))
 
 
@@ -422,6 +469,9 @@ def cake_sgemm_noalloc(A, B, C=None, stream=None):
         raise ValueError("inner dimensions differ")
     if C is None:
         C = _empty_like_kind(A, (M, N))
+    if not (_is_torch(C) and C.is_cuda):
+        raise TypeError("cake_sgemm_noalloc takes CUDA tensors")
+    _need_shape(C, (M, N), "C")
     _check(lib().cakeb200_sgemm_noalloc(_ptr(A), _ptr(B), _ptr(C), M, N, K, _stream_of(C, stream)))
     return C
 
@@ -486,6 +536,8 @@ class KShard:
         lo, hi = self.rows
         if out is None:
             out = torch.empty((hi - lo, self.N), dtype=torch.float32, device="cuda")
+        if out.numel() != (hi - lo) * self.N:
+            raise ValueError("out has %d elements, expected %d" % (out.numel(), (hi - lo) * self.N))
         _check(lib().cakeb200_kshard_finish(self._h, _ptr(out), wait_limit_us, _stream_of(out, stream)))
         return out
 
@@ -493,6 +545,13 @@ class KShard:
         if self._h:
             lib().cakeb200_kshard_destroy(self._h)
             self._h = _vp()
+
+
+def tf32_peak(ms_target=0.0, stream=None):
+    """(TFLOP/s, ms): measured dense TF32 issue rate of the current device (cakeb200_tf32_peak)."""
+    t, ms = ctypes.c_float(), ctypes.c_float()
+    _check(lib().cakeb200_tf32_peak(ms_target, ctypes.byref(t), ctypes.byref(ms), ctypes.c_void_p(int(stream)) if stream else None))
+    return t.value, ms.value
 
 
 def profile_begin():

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcake_b200.so")
 
-SOURCES = ["abi.cu", "sgemm_ffma.cu", "sgemm_tf32x3.cu", "sgemm_small_tf32x3.cu", "conv_tf32x3.cu", "gemv.cu", "kshard.cu", "pack.cu", "sparse.cu", "conv.cu", "tiling.cpp", "host_api.cpp"]
+SOURCES = ["abi.cu", "sgemm_ffma.cu", "sgemm_tf32x3.cu", "sgemm_small_tf32x3.cu", "conv_tf32x3.cu", "gemv.cu", "kshard.cu", "peak_tf32.cu", "pack.cu", "sparse.cu", "conv.cu", "tiling.cpp", "host_api.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

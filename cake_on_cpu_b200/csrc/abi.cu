@@ -255,7 +255,7 @@ int ensure_pipeline(DeviceState* st) {
 // This is the GPU form of the reference's on-the-fly packing driver, which packs
 // block i+1 while block i is multiplied (src/cake_sgemm_k_first.cpp:633-813).
 int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float* C, GemmProblem g, int kernel,
-                         cudaStream_t s) {
+                         cudaStream_t s, cudaEvent_t b_ready) {
     const int M = g.M, N = g.N, K = g.K;
     int rc;
     static const bool debug_timing = getenv("CAKEB200_DEBUG_TIMING") != nullptr;
@@ -289,6 +289,9 @@ int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float*
         CAKE_CUDA_OK(cudaEventRecord(st->fence[1], st->copy_in));
         CAKE_CUDA_OK(cudaStreamWaitEvent(s, st->fence[1], 0));
     }
+    // B being completed by someone else (a gather from other GPUs): only the kernels wait for it,
+    // the rows of A keep arriving meanwhile
+    if (b_ready) CAKE_CUDA_OK(cudaStreamWaitEvent(s, b_ready, 0));
     if (kernel == CAKEB200_KERNEL_TF32X3) {
         if ((rc = tf32x3_split_B(dB, N, K, N, planes, s))) return rc;
         g_stats.launches++;
@@ -344,7 +347,7 @@ int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float*
 }
 
 int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
-               int kernel, void* stream, bool blocking) {
+               int kernel, void* stream, bool blocking, cudaEvent_t b_ready = nullptr) {
     g_stats = cakeb200_stats();
     if (!A || !B || !C) {
         set_error("null matrix pointer");
@@ -395,7 +398,8 @@ int sgemm_impl(const float* A, const float* B, float* C, int M, int N, int K, in
         return run_dense(st, g, kernel, s, false);
     }
 
-    if (!on_device(A) && !on_device(C) && M >= 1024) return sgemm_host_pipelined(st, A, B, C, g, kernel, s);
+    if (!on_device(A) && !on_device(C) && M >= 1024) return sgemm_host_pipelined(st, A, B, C, g, kernel, s, b_ready);
+    if (b_ready) CAKE_CUDA_OK(cudaStreamWaitEvent(s, b_ready, 0));
 
     Operand oa, ob, oc;
     int rc;
@@ -546,6 +550,40 @@ int cakeb200_query_cntx(cakeb200_cntx* out) {
     return CAKEB200_OK;
 }
 
+int cakeb200_tf32_peak(float ms_target, float* tflops, float* ms, void* stream) {
+    static std::mutex m;
+    static float cached[MAX_DEVICES] = {};
+    if (!tflops) {
+        set_error("cakeb200_tf32_peak: null result pointer");
+        return CAKEB200_ERR_ARG;
+    }
+    if (ms_target > 200.f) {
+        set_error("cakeb200_tf32_peak: at most 200 ms");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    if (ms_target <= 0.f) {
+        std::lock_guard<std::mutex> lock(m);
+        if (cached[st->device] > 0.f) {
+            *tflops = cached[st->device];
+            if (ms) *ms = 0.f;
+            return CAKEB200_OK;
+        }
+    }
+    float got = 0.f, took = 0.f;
+    int rc = measure_tf32_peak(st->status_word, st->sm_count, ms_target > 0.f ? ms_target : 2.0f, (cudaStream_t) stream, &got, &took);
+    if (rc) return rc;
+    if ((rc = check_status_word(st, (cudaStream_t) stream))) return rc;
+    {
+        std::lock_guard<std::mutex> lock(m);
+        cached[st->device] = got;
+    }
+    *tflops = got;
+    if (ms) *ms = took;
+    return CAKEB200_OK;
+}
+
 int cakeb200_profile_begin(void) {
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
@@ -577,6 +615,11 @@ int cakeb200_profile_end(float* ms_prepass, float* ms_kernel, int* calls) {
 int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
                    int kernel, void* stream) {
     return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, true);
+}
+
+int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,
+                         int kernel, void* stream, void* b_ready) {
+    return sgemm_impl(A, B, C, M, N, K, accumulate, sched, kernel, stream, true, (cudaEvent_t) b_ready);
 }
 
 int cakeb200_sgemm_async(const float* A, const float* B, float* C, int M, int N, int K, int accumulate, int sched,

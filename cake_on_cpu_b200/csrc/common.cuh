@@ -92,6 +92,8 @@ int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);  // untranspos
 int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream);
 // one CTA runs a bounded wait that must give up (sgemm_tf32x3.cu)
 int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream);
+// issue rate of dense TF32 MMAs on every SM (peak_tf32.cu)
+int measure_tf32_peak(int* status_word, int sm_count, float ms_target, cudaStream_t stream, float* tflops, float* ms_out);
 // batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)
 bool small_tf32x3_fits(int M, int N, int K);
 int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_count, cudaStream_t stream);

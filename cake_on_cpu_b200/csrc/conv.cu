@@ -32,7 +32,9 @@ int launch_im2col(const float* in, float* col, int batch, int cin, int H, int W,
     const int Ho = (H + 2 * pad - hf) / stride + 1, Wo = (W + 2 * pad - wf) / stride + 1;
     const long long total = (long long) cin * hf * wf * batch * Ho * Wo;
     if (total <= 0) return CAKEB200_OK;
-    const int blocks = (int) std::min<long long>((total + 255) / 256, 148LL * 64);
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    const int blocks = (int) std::min<long long>((total + 255) / 256, (long long) st->sm_count * 64);
     im2col_kernel<<<blocks, 256, 0, stream>>>(in, col, batch, cin, H, W, hf, wf, stride, pad, Ho, Wo);
     CAKE_CUDA_OK(cudaGetLastError());
     return CAKEB200_OK;

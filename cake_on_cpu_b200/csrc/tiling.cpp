@@ -162,4 +162,18 @@ size_t cakeb200_packed_C_size(int M, int N, int p, const cakeb200_blk_dims* x, c
     return (size_t) m_padded(M, p, x, cx, sched) * (size_t) n_padded(N, x, cx) * sizeof(float);
 }
 
+// Which devices a host-pointer product with p > 1 is spread over (host logic, no device needed).
+int cakeb200_select_devices(const int* cc_major, int n_devices, int current, int p, int cap, int M, int* out) {
+    if (!cc_major || !out || n_devices <= 0 || current < 0 || current >= n_devices) return 0;
+    int limit = p < 1 ? 1 : p;
+    if (cap > 0 && cap < limit) limit = cap;
+    const int by_rows = M / 512 > 1 ? M / 512 : 1;  // at least 512 rows of C per device
+    if (by_rows < limit) limit = by_rows;
+    int got = 0;
+    if (cc_major[current] == 10) out[got++] = current;
+    for (int d = 0; d < n_devices && got < limit; d++)
+        if (d != current && cc_major[d] == 10) out[got++] = d;
+    return got;
+}
+
 }  // extern "C"

@@ -52,6 +52,7 @@ def release(group=None):
     for x in _exchanges.values():
         x.close()
     _exchanges.clear()
+    _gather_state.clear()
 
 
 def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None, exchange="auto"):
@@ -101,6 +102,65 @@ def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None, exchange="auto"):
     r0, r1 = partition.row_block(M, world, rank)
     block, span = reduce_scatter(partial, r0, r1)
     return kind, span, block
+
+
+_gather_state = {}
+
+
+def sharded_sgemm_host(A_rows, B_rows, C_rows, kernel=api.KERNEL_AUTO, group=None):
+    """One product C = A @ B whose operands live in HOST memory, spread over the ranks by rows.
+
+    Rank r passes the rows of A and of C that it owns (``partition.row_block(M, world, r)``)
+    and ITS slice of the rows of B (``partition.k_block(K, world, r)``), as float32 numpy
+    arrays (pinned memory makes the copies asynchronous).  Every rank needs all of B, but each
+    row of B crosses PCIe once: a rank copies only its slice to the device and the slices are
+    gathered from the peers over NVLink into a B in the rank's own memory (NCCL all-gather on a
+    side stream), which the kernels then read locally.  While that gather runs, the rank's rows
+    of A are already arriving; the product is multiplied band by band as they land and the
+    result rows leave band by band (cakeb200_sgemm_after).  Per step and rank the host link
+    carries 4 * (rows * K + (K / world) * N) bytes in and 4 * rows * N bytes out; with B copied by
+    every rank it would carry 4 * (rows * K + K * N) bytes in.
+
+    The reference shares one packed B among all cores of a CB block in the same way
+    (reference src/cake_sgemm_k_first.cpp:85-129).  Returns C_rows.
+    """
+    import numpy as np
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    rows, K = A_rows.shape
+    N = B_rows.shape[1]
+    k0, k1 = partition.k_block(K, world, rank)
+    if B_rows.shape[0] != k1 - k0:
+        raise ValueError("this rank's slice of B must have %d rows (partition.k_block), got %d" % (k1 - k0, B_rows.shape[0]))
+    if tuple(C_rows.shape) != (rows, N):
+        raise ValueError("C_rows has the wrong shape")
+    if world == 1:
+        return api.cake_sgemm(A_rows, B_rows, C_rows, kernel=kernel)
+    key = (K, N, world, id(group))
+    st = _gather_state.get(key)
+    if st is None:
+        st = {"B": torch.empty((K, N), dtype=torch.float32, device="cuda"), "side": torch.cuda.Stream(),
+              "slice_in": torch.cuda.Event(), "ready": torch.cuda.Event()}
+        _gather_state[key] = st
+    Bd, side = st["B"], st["side"]
+    main = torch.cuda.current_stream()
+    Bd[k0:k1].copy_(torch.from_numpy(B_rows) if isinstance(B_rows, np.ndarray) else B_rows, non_blocking=True)
+    st["slice_in"].record(main)
+    shares = [partition.k_block(K, world, r) for r in range(world)]
+    with torch.cuda.stream(side):
+        side.wait_event(st["slice_in"])
+        if all(b - a == k1 - k0 for a, b in shares):
+            dist.all_gather_into_tensor(Bd, Bd[k0:k1], group=group)  # in place: this rank's slice already sits where it belongs
+        else:
+            for r, (a, b) in enumerate(shares):  # ragged slices: one broadcast per owner
+                if b > a:
+                    dist.broadcast(Bd[a:b], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
+        st["ready"].record(side)
+    if rows > 0:
+        api.cake_sgemm(A_rows, Bd, C_rows, kernel=kernel, stream=main.cuda_stream, b_ready=st["ready"])
+    else:
+        st["ready"].synchronize()
+    return C_rows
 
 
 def _rank_world(group):

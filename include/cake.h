@@ -113,12 +113,49 @@ void schedule_MKN(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p
 void schedule_NKM(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
                   blk_dims_t* x);
 
+/* The other K-first schedule entry points of the reference (include/cake.h:26-33).  _online, _2d
+ * and _2d_small take PLAIN A, B, C; their A_p / B_p / C_p arguments are the reference's per-core
+ * packing scratch, which has no role here (tiles are staged inside the kernel) and is left
+ * untouched.  _C_unpacked takes A and B packed for K-first and ADDS the product into C_p, a plain
+ * matrix with leading dimension x->N_padded (src/cake_sgemm_k_first.cpp:986-1104). */
+void schedule_KMN_online(float* A, float* B, float* C, float** A_p, float* B_p, float** C_p, int M, int N, int K,
+                         int p, cake_cntx_t* cake_cntx, blk_dims_t* x);
+void schedule_KMN_C_unpacked(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p,
+                             cake_cntx_t* cake_cntx, blk_dims_t* x);
+void schedule_KMN_2d(float* A, float* B, float* C, float* A_p, float* B_p, float** C_p, int M, int N, int K, int p,
+                     cake_cntx_t* cake_cntx, blk_dims_t* x);
+void schedule_KMN_2d_small(float* A, float* B, float* C, float* A_p, float* B_p, float** C_p, int M, int N, int K,
+                           int p, cake_cntx_t* cake_cntx, blk_dims_t* x);
+
+/* Packing-free schedules for small matrices (reference include/cake.h:57-69,
+ * src/cake_sgemm_small.cpp:7-236).  In the reference their microkernel call is commented out and
+ * they compute nothing; here they do what that microkernel is written for
+ * (src/kernels/haswell/dense.cpp:206-207): C += A*B with A stored by columns (A_p[k*M + m]), B and
+ * C plain row-major.  The _A_packed / _B_packed / _C_packed forms take that one operand in the
+ * layout of pack_A(NKM) / pack_B(MKN) / pack_C(KMN) and the other two plain row-major. */
+void schedule_KMN_small(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                        blk_dims_t* x);
+void schedule_MKN_small(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                        blk_dims_t* x);
+void schedule_NKM_small(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p, cake_cntx_t* cake_cntx,
+                        blk_dims_t* x);
+void schedule_NKM_small_A_packed(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p,
+                                 cake_cntx_t* cake_cntx, blk_dims_t* x);
+void schedule_MKN_small_B_packed(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p,
+                                 cake_cntx_t* cake_cntx, blk_dims_t* x);
+void schedule_KMN_small_C_packed(float* A_p, float* B_p, float* C_p, int M, int N, int K, int p,
+                                 cake_cntx_t* cake_cntx, blk_dims_t* x);
+
 /* Small-matrix path (reference include/cake.h:52-53, src/cake_sgemm.cpp:614-721).
  * Returns true and computes C = A*B with the exact-FP32 kernel, without any
  * operand pre-pass, when the product is too small to amortise one; returns
  * false (C untouched) otherwise. */
 bool cake_gemm_small(float* A, float* B, float* C, int M, int N, int K, int p, blk_dims_t* x,
                      cake_cntx_t* cake_cntx, enum sched sch, char* argv[] = NULL);
+
+/* Six-buffer form of the same (reference include/cake.h:71-72); the packed scratch is not used. */
+bool cake_gemm_small(float* A, float* A_p, float* B, float* B_p, float* C, float* C_p, int M, int N, int K, int p,
+                     blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch);
 
 /* Batch of independent small products, item i at A + i*M*K, B + i*K*N,
  * C + i*M*N.  The reference has no batched entry; its equivalent is one
@@ -165,6 +202,8 @@ void init_block_dims(int M, int N, int K, int p, blk_dims_t* x, cake_cntx_t* cak
                      char* argv[], float type_size = 4, int mcu = 0, int kcu = 0, int ncu = 0);
 void init_block_dims_2d(int M, int N, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch,
                         char* argv[], float type_size = 4, int mcu = 0, int kcu = 0, int ncu = 0);
+void init_block_dims_2d_small(int M, int N, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch,
+                              char* argv[], float type_size = 4);
 int grid_dims_2d(int M, int N, int K, int p, int ncores);
 
 /* ------------------------------------------------------------------ packing

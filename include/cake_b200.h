@@ -81,11 +81,28 @@ void cakeb200_get_stats(cakeb200_stats* out);
 /* Number of visible CUDA devices with compute capability 10.x. */
 int cakeb200_device_count(void);
 
+/* The devices a host-pointer product with p > 1 is spread over by the C++ API (in the reference p
+ * is the OpenMP thread count, src/cake_sgemm.cpp:19; here it bounds the GPUs).  cc_major[d] is the
+ * compute-capability major of visible device d; the result starts with `current` (when it is a
+ * 10.x device) and continues with the other 10.x devices in ordinal order, at most
+ * min(p, cap if cap > 0, M / 512) of them; returns how many were written to `out` (room for
+ * n_devices).  `cap` is the CAKE_NGPU environment variable in the C++ API.  Pure host logic. */
+int cakeb200_select_devices(const int* cc_major, int n_devices, int current, int p, int cap, int M, int* out);
+
 /* Fills a context for the current device: L1 = shared memory per SM,
  * L2 = device L2 bytes, L3 = min(HBM bytes, INT_MAX), ncores = visible devices,
  * mr x nr = 128 x 256 (the MMA tile).  Replaces cake_query_cntx()
  * (reference src/block_sizing.cpp:40-75). */
 int cakeb200_query_cntx(cakeb200_cntx* out);
+
+/* Measured dense TF32 tensor rate of the current device, TFLOP/s: every SM issues
+ * tcgen05.mma kind::tf32 128 x 256 x 8 back to back on operand tiles resident in shared
+ * memory for about `ms_target` milliseconds (<= 0: about 2 ms, and the result of an earlier
+ * call on this device is returned if there is one).  The 3xTF32 product issues three MMAs per
+ * FP32-class multiply-add, so its roofline is a third of this figure.  `ms` (optional) receives
+ * the duration of the measured launch.  Replaces the machine peak the reference hard-codes in
+ * its context (peak_flops = 600e9, reference src/block_sizing.cpp:49-50). */
+int cakeb200_tf32_peak(float ms_target, float* tflops, float* ms, void* stream);
 
 /* C = A*B (accumulate == 0) or C += A*B (accumulate != 0).
  * Replaces cake_sgemm() (reference src/cake_sgemm.cpp:9-175; prototype
@@ -99,6 +116,16 @@ int cakeb200_query_cntx(cakeb200_cntx* out);
  * while band i+1 is still being copied in and band i-1 is being copied out. */
 int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K,
                    int accumulate, int sched, int kernel, void* stream);
+
+/* cakeb200_sgemm for a B that is still being completed when the call is made: the kernels of the
+ * call wait for `b_ready` (a cudaEvent_t already recorded by the caller; NULL = nothing to wait for)
+ * in addition to the work queued on `stream`, while host rows of A start moving to the device at
+ * once.  For one product spread over several GPUs, where each GPU copies its own slice of B from the
+ * host and the slices are gathered from the peers over NVLink into a B in this GPU's memory
+ * (the reference shares one packed B among all its cores, reference
+ * src/cake_sgemm_k_first.cpp:85-129): the gather runs on another stream and records `b_ready`. */
+int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N, int K,
+                         int accumulate, int sched, int kernel, void* stream, void* b_ready);
 
 /* Same, but only enqueues on `stream` (device pointers required, no host copies,
  * no synchronisation).  For callers that time or overlap the work themselves.

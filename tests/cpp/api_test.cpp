@@ -79,6 +79,87 @@ int main(int argc, char* argv[]) {
         for (size_t i = 0; i < C1.size(); i++) worst = std::max(worst, (double) fabsf(C2[i] - C1[i] - 1.5f));
         expect(worst < 1e-3, "beta flag adds to C");
     }
+    // the other K-first drivers and their schedule entry points (reference include/cake.h:26-47): plain operands
+    {
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm_online(A.data(), B.data(), C.data(), M, N, K, p, cntx) > 0, "cake_sgemm_online");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "cake_sgemm_online result");
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm_2d(A.data(), B.data(), C.data(), M, N, K, p, cntx) > 0, "cake_sgemm_2d");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "cake_sgemm_2d result");
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm_2d_small(A.data(), B.data(), C.data(), M, N, K, p, cntx) > 0, "cake_sgemm_2d_small");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "cake_sgemm_2d_small result");
+        blk_dims_t x;
+        init_block_dims_2d(M, N, K, p, &x, cntx, KMN, NULL);
+        expect(x.pm * x.pn == p, "init_block_dims_2d grid");
+        std::fill(C.begin(), C.end(), -7.f);
+        schedule_KMN_online(A.data(), B.data(), C.data(), NULL, NULL, NULL, M, N, K, p, cntx, &x);
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN_online result");
+        std::fill(C.begin(), C.end(), -7.f);
+        schedule_KMN_2d(A.data(), B.data(), C.data(), NULL, NULL, NULL, M, N, K, p, cntx, &x);
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN_2d result");
+        blk_dims_t xs;
+        init_block_dims_2d_small(M, N, K, p, &xs, cntx, KMN, NULL);
+        expect(xs.pm * xs.pn == p && xs.m_c >= M / xs.pm && xs.n_c >= N / xs.pn && xs.k_c > 0, "init_block_dims_2d_small");
+        std::fill(C.begin(), C.end(), -7.f);
+        schedule_KMN_2d_small(A.data(), B.data(), C.data(), NULL, NULL, NULL, M, N, K, p, cntx, &xs);
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN_2d_small result");
+    }
+    // K-first on packed A and B adding into a plain C with the padded row pitch
+    {
+        blk_dims_t x;
+        init_block_dims(M, N, K, p, &x, cntx, KMN, NULL);
+        std::vector<float> A_p(cake_sgemm_packed_A_size(M, K, p, &x, cntx, KMN) / 4);
+        std::vector<float> B_p(cake_sgemm_packed_B_size(K, N, p, &x, cntx) / 4);
+        pack_A(A.data(), A_p.data(), M, K, p, &x, cntx, KMN);
+        pack_B(B.data(), B_p.data(), K, N, p, &x, cntx, KMN);
+        std::vector<float> C_wide((size_t) x.M_padded * x.N_padded, 0.f);
+        schedule_KMN_C_unpacked(A_p.data(), B_p.data(), C_wide.data(), M, N, K, p, cntx, &x);
+        for (int m = 0; m < M; m++) memcpy(&C[(size_t) m * N], &C_wide[(size_t) m * x.N_padded], (size_t) N * sizeof(float));
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN_C_unpacked result");
+    }
+    // packing-free small schedules: A stored by columns, C added to; and the forms with one packed operand
+    {
+        const int m = 111, k = 96, n = 211;
+        std::vector<float> a((size_t) m * k), at((size_t) k * m), b((size_t) k * n), c((size_t) m * n);
+        rand_init(a.data(), m, k);
+        rand_init(b.data(), k, n);
+        for (int i = 0; i < m; i++)
+            for (int j = 0; j < k; j++) at[(size_t) j * m + i] = a[(size_t) i * k + j];
+        blk_dims_t x;
+        typedef void (*small_fn)(float*, float*, float*, int, int, int, int, cake_cntx_t*, blk_dims_t*);
+        const small_fn plain[] = {schedule_KMN_small, schedule_MKN_small, schedule_NKM_small};
+        const enum sched order[] = {KMN, MKN, NKM};
+        for (int i = 0; i < 3; i++) {
+            init_block_dims(m, n, k, p, &x, cntx, order[i], NULL);
+            std::fill(c.begin(), c.end(), 0.f);
+            plain[i](at.data(), b.data(), c.data(), m, n, k, p, cntx, &x);
+            expect(cake_sgemm_checker(a.data(), b.data(), c.data(), n, m, k) == 0, "schedule_*_small result");
+        }
+        init_block_dims(m, n, k, p, &x, cntx, NKM, NULL);
+        std::vector<float> a_p(cake_sgemm_packed_A_size(m, k, p, &x, cntx, NKM) / 4);
+        pack_A(a.data(), a_p.data(), m, k, p, &x, cntx, NKM);
+        std::fill(c.begin(), c.end(), 0.f);
+        schedule_NKM_small_A_packed(a_p.data(), b.data(), c.data(), m, n, k, p, cntx, &x);
+        expect(cake_sgemm_checker(a.data(), b.data(), c.data(), n, m, k) == 0, "schedule_NKM_small_A_packed result");
+        init_block_dims(m, n, k, p, &x, cntx, MKN, NULL);
+        std::vector<float> b_p(cake_sgemm_packed_B_size(k, n, p, &x, cntx) / 4);
+        pack_B(b.data(), b_p.data(), k, n, p, &x, cntx, MKN);
+        std::fill(c.begin(), c.end(), 0.f);
+        schedule_MKN_small_B_packed(a.data(), b_p.data(), c.data(), m, n, k, p, cntx, &x);
+        expect(cake_sgemm_checker(a.data(), b.data(), c.data(), n, m, k) == 0, "schedule_MKN_small_B_packed result");
+        init_block_dims(m, n, k, p, &x, cntx, KMN, NULL);
+        std::vector<float> c_p(cake_sgemm_packed_C_size(m, n, p, &x, cntx, KMN) / 4, 0.f);
+        schedule_KMN_small_C_packed(a.data(), b.data(), c_p.data(), m, n, k, p, cntx, &x);
+        std::fill(c.begin(), c.end(), -7.f);
+        unpack_C(c.data(), c_p.data(), m, n, p, &x, cntx, KMN);
+        expect(cake_sgemm_checker(a.data(), b.data(), c.data(), n, m, k) == 0, "schedule_KMN_small_C_packed result");
+        // six-buffer form of the small-matrix entry point
+        std::fill(c.begin(), c.end(), -7.f);
+        expect(cake_gemm_small(a.data(), NULL, b.data(), NULL, c.data(), NULL, m, n, k, p, &x, cntx, NA), "cake_gemm_small (six buffers)");
+        expect(cake_sgemm_checker(a.data(), b.data(), c.data(), n, m, k) == 0, "cake_gemm_small (six buffers) result");
+    }
     // small-matrix entry point
     {
         const int m = 96;

@@ -1,0 +1,132 @@
+"""The dense configurations at their full sizes against the reference's OWN output.
+
+The unmodified reference (oracle/_ref, compiled from the reference's sources) computes
+cake_sgemm on the host cores of the GPU box from the seeded operands (A = stream 1,
+B = stream 2 of the counter-based generator); the library computes the same product on
+the GPU from the same operands, generated on the device by the same formula.  Gate, for
+both kernels: max |C - C_ref| / (||A[m,:]|| ||B[:,n]||) <= 1e-5 over every compared
+entry.  3000^3 and 8192^3 are compared in full; 16384^3 on a 1024-row slab against the
+reference plus 4096 entries against float64; 32768^3 (the reference would need minutes
+and 21 GB) on 4096 entries against float64 only.
+"""
+import numpy as np
+import pytest
+
+from _oracle import NA
+
+TOL = 1e-5
+
+
+def test_device_generator_equals_the_host_generator(oracle):
+    """The torch implementation of the seeded streams is the oracle's, element for element (CPU tensors here)."""
+    from cake_on_cpu_b200 import seeded
+    for seed, shape in ((1, (257, 1031)), (2, (3, 7)), (5, (1000, 999))):
+        assert np.array_equal(oracle.uniform(shape, seed), seeded.uniform(shape, seed, device="cpu").numpy())
+    assert np.array_equal(oracle.sparse((300, 301), 1, 3, 0.1), seeded.sparse_uniform((300, 301), 1, 3, 0.1, device="cpu").numpy())
+
+
+def _norms(A, B):
+    return A.double().norm(dim=1), B.double().norm(dim=0)
+
+
+def _gate(C, C_ref, an, bn):
+    """(normalised, absolute) largest deviation of C from C_ref, both CUDA tensors of the same shape."""
+    import torch
+    worst_n, worst_a = 0.0, 0.0
+    for r0 in range(0, C.shape[0], 1024):  # in row blocks: float64 temporaries of 16384 x 16384 would not be small
+        d = (C[r0:r0 + 1024].double() - C_ref[r0:r0 + 1024].double()).abs()
+        worst_a = max(worst_a, d.max().item())
+        worst_n = max(worst_n, (d / (an[r0:r0 + 1024, None] * bn[None, :]).clamp_min(1e-30)).max().item())
+    return worst_n, worst_a
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("size", [3000, 8192])
+def test_full_product_against_the_reference(cake, oracle, reference, size):
+    import torch
+    from cake_on_cpu_b200 import seeded
+    n = size
+    A, B = seeded.uniform((n, n), 1), seeded.uniform((n, n), 2)
+    Ah, Bh = oracle.uniform((n, n), 1), oracle.uniform((n, n), 2)
+    assert torch.equal(A[:64].cpu(), torch.from_numpy(Ah[:64])) and torch.equal(B[-64:].cpu(), torch.from_numpy(Bh[-64:]))
+    ctx, info = reference.query_ctx()
+    C_ref_h, seconds = reference.sgemm(Ah, Bh, info["ncores"], NA, ctx=ctx)
+    C_ref = torch.from_numpy(C_ref_h).cuda()
+    an, bn = _norms(A, B)
+    for kernel in (cake.KERNEL_TF32X3, cake.KERNEL_FFMA):
+        C = torch.full((n, n), float("nan"), device="cuda")
+        cake.cake_sgemm(A, B, C, kernel=kernel)
+        assert cake.last_stats()["kernel"] == kernel
+        err_n, err_a = _gate(C, C_ref, an, bn)
+        print("%d^3 kernel %d vs reference (%.2f s on %d host cores): normalised %.3e absolute %.3e"
+              % (n, kernel, seconds, info["ncores"], err_n, err_a))
+        assert err_n <= TOL
+    # the host-pointer route (what a caller of the reference's API passes) gives the same bits as the device route
+    Ch = np.empty((n, n), np.float32)
+    cake.cake_sgemm(Ah, Bh, Ch, kernel=cake.KERNEL_TF32X3)
+    Cd = torch.empty((n, n), device="cuda")
+    cake.cake_sgemm(A, B, Cd, kernel=cake.KERNEL_TF32X3)
+    err_n, _ = _gate(torch.from_numpy(Ch).cuda(), C_ref, an, bn)
+    assert err_n <= TOL
+
+
+def _sampled_float64(A, B, C, count, seed):
+    """Largest normalised / absolute deviation of `count` entries of C from a float64 recomputation."""
+    import torch
+    M, N = C.shape
+    side = int(np.ceil(np.sqrt(count)))
+    rng = np.random.default_rng(seed)
+    rows = torch.as_tensor(np.sort(rng.choice(M, side, replace=False)), device="cuda")
+    cols = torch.as_tensor(np.sort(rng.choice(N, side, replace=False)), device="cuda")
+    a, b = A[rows].double(), B[:, cols].double()
+    exact = a @ b
+    got = C[rows][:, cols].double()
+    den = a.norm(dim=1)[:, None] * b.norm(dim=0)[None, :]
+    d = (got - exact).abs()
+    return (d / den.clamp_min(1e-30)).max().item(), d.max().item(), side * side
+
+
+@pytest.mark.gpu
+def test_16384_slab_against_the_reference_and_samples_against_float64(cake, oracle, reference):
+    import torch
+    from cake_on_cpu_b200 import seeded
+    n, r0, rows = 16384, 5 * 1024 + 128, 1024
+    A, B = seeded.uniform((n, n), 1), seeded.uniform((n, n), 2)
+    C = torch.full((n, n), float("nan"), device="cuda")
+    cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+    err_n, err_a, cnt = _sampled_float64(A, B, C, 4096, 7)
+    print("16384^3: %d entries vs float64: normalised %.3e absolute %.3e" % (cnt, err_n, err_a))
+    assert cnt >= 4096 and err_n <= TOL
+    assert not torch.isnan(C).any().item()
+    Bh = B.cpu().numpy()
+    Ah = A[r0:r0 + rows].cpu().numpy()
+    assert np.array_equal(Bh[:4], oracle.uniform((4, n), 2))  # the device stream is the host stream
+    ctx, info = reference.query_ctx()
+    slab_ref, seconds = reference.sgemm(Ah, Bh, info["ncores"], NA, ctx=ctx)
+    an, bn = _norms(A[r0:r0 + rows], B)
+    err_n, err_a = _gate(C[r0:r0 + rows], torch.from_numpy(slab_ref).cuda(), an, bn)
+    print("16384^3 rows %d..%d vs reference (%.2f s): normalised %.3e absolute %.3e" % (r0, r0 + rows, seconds, err_n, err_a))
+    assert err_n <= TOL
+
+
+@pytest.mark.gpu
+def test_32768_samples_against_float64(cake):
+    import torch
+    from cake_on_cpu_b200 import seeded
+    n = 32768
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * (1 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    A, B = seeded.uniform((n, n), 1), seeded.uniform((n, n), 2)
+    C = torch.empty((n, n), device="cuda")
+    cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+    err_n, err_a, cnt = _sampled_float64(A, B, C, 4096, 11)
+    print("32768^3: %d entries vs float64: normalised %.3e absolute %.3e" % (cnt, err_n, err_a))
+    assert cnt >= 4096 and err_n <= TOL
+    # corners and edges are where tile clipping would show
+    edge = torch.as_tensor([0, 1, 127, 128, n - 129, n - 128, n - 2, n - 1], device="cuda")
+    exact = A[edge].double() @ B[:, edge].double()
+    den = A[edge].double().norm(dim=1)[:, None] * B[:, edge].double().norm(dim=0)[None, :]
+    assert ((C[edge][:, edge].double() - exact).abs() / den).max().item() <= TOL
+    del A, B, C
+    torch.cuda.empty_cache()

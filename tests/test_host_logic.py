@@ -33,7 +33,13 @@ def test_cpp_api_symbols_present(cake):
                  "derive_schedule(", "get_cache_dims(", "init_block_dims(", "grid_dims_2d(", "pack_A(", "pack_B(",
                  "pack_C(", "unpack_C(", "cake_sgemm_packed_A_size(", "cake_sgemm_packed_B_size(",
                  "cake_sgemm_packed_C_size(", "rand_init(", "cake_sgemm_checker(", "mat_equals(", "run_tests(",
-                 "cake_gemm_small("]:
+                 "cake_gemm_small(", "cake_sgemm_2d_small(", "cake_sgemm_test(", "schedule_KMN_online(",
+                 "schedule_KMN_C_unpacked(", "schedule_KMN_2d(", "schedule_KMN_2d_small(", "schedule_KMN_small(",
+                 "schedule_MKN_small(", "schedule_NKM_small(", "schedule_NKM_small_A_packed(",
+                 "schedule_MKN_small_B_packed(", "schedule_KMN_small_C_packed(", "init_block_dims_2d(",
+                 "init_block_dims_2d_small(",
+                 # both overloads of cake_gemm_small (reference include/cake.h:52-53 and :71-72)
+                 "cake_gemm_small(float*, float*, float*, int,", "cake_gemm_small(float*, float*, float*, float*, float*, float*,"]:
         assert name in out, name
 
 
@@ -132,3 +138,50 @@ def test_kshard_rows_match_the_partition_module_and_shape_query_needs_no_device(
     assert not api.kshard_supported(256, 256, 256, sm_count=148)
     with pytest.raises(api.CakeError):
         api.kshard_rows(100, 9, 0)  # more ranks than the exchange has slots for
+
+
+def test_wrong_shaped_outputs_are_rejected_before_any_launch(cake):
+    """The wrappers hand raw pointers to the kernels, so a caller-supplied array of the wrong
+    shape must be refused on the host (ValueError), not discovered by the device."""
+    A = np.zeros((16, 8), np.float32)
+    B = np.zeros((8, 12), np.float32)
+    small = np.zeros((16, 11), np.float32)
+    with pytest.raises(ValueError):
+        cake.cake_sgemm(A, B, small)
+    with pytest.raises(ValueError):
+        cake.cake_sp_sgemm(A, B, small)
+    with pytest.raises(ValueError):
+        cake.cake_sp_sgemm(A, np.zeros((9, 12), np.float32))
+    with pytest.raises(ValueError):
+        cake.cake_sgemv(A, np.zeros(8, np.float32), np.zeros(15, np.float32))
+    with pytest.raises(ValueError):
+        cake.cake_sgemv(A, np.zeros(9, np.float32))
+    with pytest.raises(ValueError):
+        cake.cake_sgemm_batched(np.zeros((3, 16, 8), np.float32), np.zeros((3, 8, 12), np.float32),
+                                np.zeros((3, 16, 11), np.float32))
+    with pytest.raises(ValueError):
+        cake.cake_conv2d(np.zeros((1, 2, 8, 8), np.float32), np.zeros((4, 2, 3, 3), np.float32), pad=1,
+                         out=np.zeros((1, 4, 8, 7), np.float32))
+    cx = cake.Cntx.make(*DEFAULT_CACHES)
+    x = cake.init_block_dims(16, 12, 8, 2, cx, KMN)
+    with pytest.raises(ValueError):
+        cake.pack_A(A, 16, 8, 2, x, cx, A_p=np.zeros(4, np.float32))
+    with pytest.raises(ValueError):
+        cake.pack_A(np.zeros((15, 8), np.float32), 16, 8, 2, x, cx)
+
+
+def test_device_selection_for_host_pointer_calls(cake):
+    """cakeb200_select_devices: current device first, then the other sm_100 devices in ordinal order,
+    bounded by p, the CAKE_NGPU cap and 512 rows of C per device."""
+    from cake_on_cpu_b200.api import select_devices
+    all10 = [10] * 8
+    assert select_devices(all10, 0, 8) == list(range(8))
+    assert select_devices(all10, 3, 4) == [3, 0, 1, 2]
+    assert select_devices(all10, 3, 8, cap=2) == [3, 0]
+    assert select_devices(all10, 5, 1) == [5]
+    assert select_devices(all10, 0, 8, M=1500) == [0, 1]
+    assert select_devices(all10, 0, 8, M=100) == [0]
+    # devices of another architecture are skipped, wherever they sit
+    assert select_devices([9, 10, 10, 8, 10], 2, 8) == [2, 1, 4]
+    assert select_devices([9, 10], 0, 2) == [1]
+    assert select_devices([], 0, 2) == []

@@ -64,7 +64,25 @@ def _worker(rank, world, port, out, cases=TWO_RANK_CASES):
     w = torch.randn((24, 16, 3, 3), device="cuda", generator=g) * 0.1
     (i0, i1), y = distributed.sharded_conv2d(x, w, 1, 1)
     err_c = (y.double() - torch.nn.functional.conv2d(x[i0:i1].double(), w.double(), padding=1)).abs().max().item()
-    units = (hi - lo, r1 - r0, i1 - i0, err_b, err_s, err_c)
+    # host operands: row blocks of A and C, every rank copies only its slice of B, the rest arrives from the peers
+    from cake_on_cpu_b200 import partition
+    err_h = 0.0
+    for (M, K, N) in ((2560, 1024, 1536), (2100, 1000, 520), (96, 64, 40)):  # even slices, ragged slices, tiny
+        gh = torch.Generator(device="cuda").manual_seed(8)
+        A = torch.rand((M, K), device="cuda", generator=gh) * 2 - 1
+        B = torch.rand((K, N), device="cuda", generator=gh) * 2 - 1
+        a0, a1 = partition.row_block(M, world, rank)
+        b0, b1 = partition.k_block(K, world, rank)
+        Ah = torch.empty((a1 - a0, K), pin_memory=True).copy_(A[a0:a1])
+        Bh = torch.empty((b1 - b0, N), pin_memory=True).copy_(B[b0:b1])
+        Ch = torch.full((a1 - a0, N), float("nan")).pin_memory()
+        for _ in range(2):  # twice: the gathered B of the first call is overwritten by the second
+            distributed.sharded_sgemm_host(Ah.numpy(), Bh.numpy(), Ch.numpy())
+        if a1 > a0:
+            exact = A[a0:a1].double() @ B.double()
+            den = A[a0:a1].double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
+            err_h = max(err_h, ((Ch.cuda().double() - exact).abs() / den).max().item())
+    units = (hi - lo, r1 - r0, i1 - i0, err_b, err_s, err_c, err_h)
     gathered = [None] * world
     dist.all_gather_object(gathered, (results, units))
     if rank == 0:
@@ -101,6 +119,7 @@ def test_two_ranks_nccl(cake):
     # batch items, sparse row blocks and images: every unit owned once, results right
     assert sum(u[0] for u in units) == 37 and sum(u[1] for u in units) == 700 and sum(u[2] for u in units) == 9
     assert all(u[3] <= 1e-3 and u[4] <= 1e-3 and u[5] <= 1e-4 for u in units), units
+    assert all(u[6] <= 1e-5 for u in units), units
 
 
 def test_four_ranks_nccl_grid(cake):
@@ -119,6 +138,7 @@ def test_four_ranks_nccl_grid(cake):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    assert all(u[6] <= 1e-5 for _, u in res), [u for _, u in res]
     res = [r for r, _ in res]
     for per_rank in res:
         for ok_kind, err, lo, hi, _ in per_rank:
@@ -129,13 +149,15 @@ def test_four_ranks_nccl_grid(cake):
         assert sum(per_rank[case][4] for per_rank in res) == M * N
 
 
-def test_cpp_api_splits_rows_over_visible_gpus(cake, tmp_path):
-    """cake_sgemm(p > 1) with host pointers: one host thread per device inside the call."""
+@pytest.mark.parametrize("shape", [(2304, 256, 640), (4100, 1111, 1300)])
+def test_cpp_api_splits_rows_over_visible_gpus(cake, tmp_path, shape):
+    """cake_sgemm(p > 1) with host pointers: one host thread per device inside the call; each device copies
+    its own slice of B from the host and fetches the other slices from its peers (on one GPU: the plain call)."""
     import numpy as np
     import ctypes
     L = ctypes.CDLL(cake.library_path())
     rng = np.random.default_rng(3)
-    M, K, N = 2304, 256, 640
+    M, K, N = shape
     A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
     B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
     C = np.full((M, N), np.nan, np.float32)

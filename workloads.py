@@ -1,8 +1,8 @@
 """Times the benchmark configurations of the CAKE SGEMM path on one GPU.
 
-    python -m cake_on_cpu_b200.workloads [--config NAME ...] [--reps R] [--list]
+    python workloads.py [--config NAME ...] [--reps R] [--list]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m cake_on_cpu_b200.workloads --distributed {square_8192,rect_m_first,rect_n_first,rect_k_first}
+        workloads.py --distributed {square_8192,rect_m_first,rect_n_first,rect_k_first}
 
 Each configuration prints one JSON line: device time of the whole library call
 (CUDA events on the calling stream, operands resident in device memory, best of
@@ -18,11 +18,13 @@ sparse A at several densities, the two convolutions and the packing routines.
 """
 import argparse
 import json
+import os
 import sys
 
 import torch
 
-from . import api
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from cake_on_cpu_b200 import api  # noqa: E402
 
 HBM_GBS = 6551.4          # measured copy bandwidth of this pool's B200s
 TENSOR_3XTF32 = 274.5     # measured BF16 burst 1647.2 / 2 / 3, TFLOP/s
@@ -218,7 +220,7 @@ def _distributed(name, reps):
     either of which leaves every rank with its row block of C.  Device time, maximum over ranks."""
     import os
     import torch.distributed as dist
-    from . import distributed, partition
+    from cake_on_cpu_b200 import distributed, partition
     shapes = {"square_8192": (8192, 8192, 8192), "rect_m_first": (65536, 1024, 1024), "rect_n_first": (1024, 1024, 65536),
               "rect_k_first": (1024, 262144, 1024)}
     M, K, N = shapes[name]
