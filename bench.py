@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--size", type=int, default=8192, help="M = K = N (default: the headline 8192)")
     ap.add_argument("--kernel", default="tf32x3", choices=["tf32x3", "ffma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-bind", action="store_true", help="do not bind the process to the CPUs next to its GPU")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     return ap.parse_args()
 
@@ -189,6 +190,7 @@ def gpu_arm(args):
     if world != args.gpus and world > 1:
         raise SystemExit("--gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
     torch.cuda.set_device(local)
+    near_cpus = None if args.no_bind else distributed.bind_near_gpu(local)  # pinned buffers next to this rank's GPU
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -343,6 +345,7 @@ def gpu_arm(args):
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps,
                     "ms_h2d_last_rank0": e2e_stats["ms_h2d"], "ms_d2h_last_rank0": e2e_stats["ms_d2h"],
+                    "host_cpus_bound": (len(near_cpus) if near_cpus else 0),
                     "how": "cake_sgemm on pinned host operands" if world == 1 else
                            "distributed.sharded_sgemm_host: row blocks of A and C; each rank copies 1/%d of the rows of B from "
                            "the host, the slices are gathered over NVLink (NCCL all-gather) into local memory" % world},

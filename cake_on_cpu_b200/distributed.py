@@ -104,6 +104,28 @@ def sharded_sgemm(A, B, kernel=api.KERNEL_AUTO, group=None, exchange="auto"):
     return kind, span, block
 
 
+def bind_near_gpu(device_index):
+    """Keep this process's host threads, and with them the pinned buffers it allocates from now on,
+    on the CPUs next to GPU `device_index` (the affinity NVML reports for it), so that host-to-device
+    copies do not cross the socket interconnect.  Reads settings only; returns the CPU set chosen, or
+    None when NVML or the affinity call is not available or the set would be empty."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        pick = near & allowed
+        if not pick:
+            return None
+        os.sched_setaffinity(0, pick)
+        return sorted(pick)
+    except Exception:
+        return None
+
+
 _gather_state = {}
 
 
