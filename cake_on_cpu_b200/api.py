@@ -104,6 +104,8 @@ _SIGNATURES["cakeb200_kshard_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _pf = ctypes.POINTER(ctypes.c_float)
 _SIGNATURES["cakeb200_tf32_peak"] = (_i, [ctypes.c_float, _pf, _pf, _vp])
+_SIGNATURES["cakeb200_set_option"] = (_i, [ctypes.c_char_p, _i])
+_SIGNATURES["cakeb200_get_option"] = (_i, [ctypes.c_char_p])
 _SIGNATURES["cakeb200_select_devices"] = (_i, [_pi, _i, _i, _i, _i, _i, _pi])
 _SIGNATURES["cakeb200_sgemm_noalloc"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _vp])
 
@@ -552,6 +554,15 @@ def tf32_peak(ms_target=0.0, stream=None):
     t, ms = ctypes.c_float(), ctypes.c_float()
     _check(lib().cakeb200_tf32_peak(ms_target, ctypes.byref(t), ctypes.byref(ms), ctypes.c_void_p(int(stream)) if stream else None))
     return t.value, ms.value
+
+
+def set_option(name, value):
+    """Override one choice of the large-matrix kernel (cakeb200_set_option); 0 restores the rule."""
+    _check(lib().cakeb200_set_option(name.encode(), int(value)))
+
+
+def get_option(name):
+    return lib().cakeb200_get_option(name.encode())
 
 
 def profile_begin():

@@ -18,17 +18,33 @@
 //                    the persistent CTAs take tiles;
 //   * microkernel -> tcgen05.mma kind::tf32, 128 x BN x 8 per instruction.
 //
-// One CTA per SM, six warps: warp 0 issues TMA loads, warp 1 issues the MMAs
-// and owns the tensor-memory allocation, warps 2-5 drain finished accumulators
-// (tcgen05.ld) to global memory while the next tile is already being
-// multiplied into the second accumulator buffer.
+// One CTA per SM, three warp groups: in the first, warp 0 issues TMA loads and warp 1 issues
+// the MMAs and owns the tensor-memory allocation; the eight warps of the other two drain accumulators
+// (tcgen05.ld) while the MMAs already fill the other accumulator buffer.
 //
-// Every wait on an mbarrier is bounded: when a wait runs out, the kernel
-// records where in a status word, stops issuing work, waits (bounded) for its
-// own loads in flight, frees its tensor memory and returns.
+// Accumulation in chunks of K.  The tensor core adds into tensor memory with
+// truncation, so the error of one long accumulation grows linearly with K (at
+// K = 8192 and uniform(-1, 1) operands about 6e-3 absolute, six times the 1e-3
+// that the reference's own checker allows, src/util.cpp:139-169).  A tile's K range
+// is therefore cut into chunks (CHUNK_KB slices of 32): each chunk is accumulated
+// from zero in one of the two buffers, and the drain warps fold finished chunks
+// into a running sum held in registers with round-to-nearest FP32 adds, so only
+// the chunk length, not K, sets the truncation error.  The fold overlaps the MMAs
+// of the next chunk; the last chunk is added on the way out to global memory.
+// Reading an accumulator out of tensor memory occupies the tensor pipe for about 2300
+// cycles (tcgen05.ld delivers ~57 bytes per clock per SM and the MMAs wait meanwhile;
+// loads of 32 or 64 columns, one or two in flight, all cost the same), so every fold
+// costs the time of 17 MMAs and the chunk length trades accuracy for speed.  Measured
+// at 8192^3, uniform(-1, 1), largest absolute error over 64 rows / kernel time: chunks
+// of 128 / 256 / 512 / 1024 of K and one unbroken accumulation give 1.4e-4 / 2.7e-4 /
+// 5.3e-4 / 1.1e-3 / 1.0e-2 and 5.43 / 4.81 / 4.44 / 4.26 / 4.19 ms.  Rule: 512 up to
+// K = 4096 (3000^3 then stays below 1e-3 everywhere), 1024 above (1 to 2 % of the
+// kernel time, error a fifth of the unbroken accumulation's); the "chunk_kb" option
+// sets it (8: below 1e-3 at 8192^3 as well, for 15 % of the kernel time).
 #include <cuda.h>
 
 #include <stdlib.h>
+#include <string.h>
 #include <mutex>
 #include <vector>
 
@@ -43,7 +59,9 @@ using namespace ptx;
 constexpr int BM = 128;          // rows of C per tile = TMEM lanes
 constexpr int BK = 32;           // K per pipeline stage: 32 floats = one 128-byte swizzle row
 constexpr int UMMA_K = 8;        // K of one tcgen05.mma kind::tf32
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 384;   // warp group 0: TMA warp, MMA warp, two idle warps; groups 1 and 2: drain warps
+constexpr int EPI_WARPS = 8;      // two per quarter of the tensor-memory lanes, each taking half of the columns
+constexpr int CHUNK_KB = 16;      // default chunk: 16 slices of 32 = 512 of K (twice that for K above 4096)
 
 template <int BN>
 struct Cfg {
@@ -52,7 +70,7 @@ struct Cfg {
     static constexpr int B_BYTES = BN * BK * 4;   // one plane of B per stage
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
-    static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;  // one 32 x 32 patch per epilogue warp
+    static constexpr int EPI_BYTES = EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 patch per drain warp
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
 };
 
@@ -71,6 +89,7 @@ struct Tf32x3Args {
     int tiles_m, tiles_n;
     int kblocks;             // 32-deep slices of K of this launch
     int kb_first;            // first slice (a deep product is run as several launches over ranges of K)
+    int chunk_kb;            // slices of 32 accumulated in tensor memory before they are folded into the running sum
     int order, band;         // tile walk, see tile_coords
     int accumulate;          // for tiles stored straight to C
     int out_p;               // > 0: N axis is (image, position), see GemmProblem::out_p
@@ -97,6 +116,12 @@ __device__ __forceinline__ bool work_piece(const Tf32x3Args& a, int it, WorkPiec
     const int4 p = a.units[u];
     w.tile = p.x; w.kb0 = p.y; w.kb1 = p.z; w.slot = p.w;
     return true;
+}
+
+// Accumulator hand-overs of one piece: its K range in chunks (an empty range still hands over once, zeros).
+__device__ __forceinline__ int piece_chunks(const WorkPiece& w, int chunk_kb) {
+    const int n = w.kb1 - w.kb0;
+    return n <= 0 ? 1 : (n + chunk_kb - 1) / chunk_kb;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -130,7 +155,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full_bar(b), 1);
-            mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+            mbar_init(acc_empty_bar(b), EPI_WARPS);  // one arrival per drain warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -148,6 +173,11 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
 
     WorkPiece w;
 
+    // Registers follow the roles: the drain warps each hold half a row of the running sum (up to 128
+    // values) next to a 32-column load, the other warp group needs a handful.  The launch gives every
+    // thread 168; group 0 hands most of its share back and groups 1 and 2 take it.
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer
         if (lane == 0) {
@@ -186,149 +216,189 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
             int stage = 0;
             uint32_t phase = 0;
-            int local = 0;
+            int local = 0, handover = 0;
             bool ok = true;
             for (; ok && work_piece(args, local, w); local++) {
-                const int kb0 = w.kb0, kb1 = w.kb1;
-                const int buf = local & 1;
-                const uint32_t acc_phase = (local >> 1) & 1;
-                ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
-                if (!ok) break;
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
-                uint32_t accumulate = 0;
-                for (int kb = kb0; kb < kb1; kb++) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
+                const int chunks = piece_chunks(w, args.chunk_kb);
+                for (int ci = 0; ok && ci < chunks; ci++, handover++) {
+                    const int kb0 = w.kb0 + ci * args.chunk_kb, kb1 = min(w.kb1, kb0 + args.chunk_kb);
+                    const int buf = handover & 1;
+                    const uint32_t acc_phase = (handover >> 1) & 1;
+                    ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
                     if (!ok) break;
                     tcgen05_fence_after();
-                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
-                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
-                    const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
-                    const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
-                    const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
+                    const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
+                    uint32_t accumulate = 0;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                        const uint64_t a_hi = make_kmajor_sw128_desc(base);
+                        const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
+                        const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
+                        const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
-                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
-                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
-                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
-                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
-                        accumulate = 1;
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
+                            const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                            accumulate = 1;
+                        }
+                        umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
-                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (!ok) break;
+                    umma_commit(acc_full_bar(buf));  // chunk complete
                 }
-                if (!ok) break;
-                umma_commit(acc_full_bar(buf));  // accumulator complete
             }
         }
+    }
     } else {
-        // ----------------------------------------------------------- epilogue
-        // tcgen05.ld hands each thread one row of the accumulator (32 columns per load), so
-        // storing from those registers would touch 32 different rows per instruction.  Every
-        // 32 x 32 chunk therefore goes through a swizzled shared-memory patch of the warp and
-        // comes back with eight lanes per row: a store instruction then covers 4 rows x 128
-        // contiguous bytes.
-        const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
-        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) quarter * 4096u;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ----------------------------------------------------------- drain warps
+        // Eight warps: warp w may only touch tensor-memory lanes [32 * (w % 4), +32), so two warps
+        // share each quarter of the rows and take half of the columns each.  A thread owns one
+        // row of its half: COLS / 32 loads of 32 columns.  Chunks that are not the last of their
+        // piece are folded into `sum`; the last one is added to `sum` and stored.
+        // tcgen05.ld hands each thread one row of the accumulator, so storing from those
+        // registers would touch 32 different rows per instruction.  Every 32 x 32 block
+        // therefore goes through a swizzled shared-memory patch of the warp and comes back with
+        // eight lanes per row: a store instruction then covers 4 rows x 128 contiguous bytes.
+        constexpr int COLS = BN / 2, LOADS = COLS / 32;
+        const int ew = warp - 4;
+        const int quarter = warp & 3, half = ew >> 2;
+        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) ew * 4096u;
         const int sub_r = lane >> 3, sub_c = lane & 7;
         const bool c_vec = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
         const bool p_vec = (args.out_p % 4 == 0) && (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
-        int local = 0;
+        float sum[COLS];
+        int local = 0, handover = 0;
         bool ok = true;
         for (; ok && work_piece(args, local, w); local++) {
             int tm, tn;
             tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
-            const int buf = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
-            ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
-            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
-            if (!ok) break;
-            tcgen05_fence_after();
+            const int chunks = piece_chunks(w, args.chunk_kb);
             const bool empty_range = w.kb0 >= w.kb1;  // a piece with no K range contributes zeros
-            const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
-            const int row0 = tm * BM + quarter * 32;
-            // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
-            // beyond the matrix are zeros computed from zero-filled operand tiles)
-            float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN : nullptr;
-            float v[32];
-            if (!empty_range) {
-                tmem_ld32(t_addr, v);
-            } else {
+            for (int ci = 0; ok && ci < chunks; ci++, handover++) {
+                const int buf = handover & 1;
+                const uint32_t acc_phase = (handover >> 1) & 1;
+                ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
+                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN + half * COLS);
+                float v[32];
+                if (ci + 1 < chunks) {
+                    // fold: sum (+)= chunk, round to nearest.  A tensor-memory load queues behind the MMAs
+                    // already issued (microseconds), so two loads are in flight per wait: four waits in a
+                    // row took longer than a chunk of 256 of K and stalled the MMAs.
+                    float v2[64];
 #pragma unroll
-                for (int j = 0; j < 32; j++) v[j] = 0.0f;
-            }
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                if (!empty_range) tmem_ld_wait();
+                    for (int c = 0; c < LOADS; c += 2) {
+                        tmem_ld64(t_addr + (uint32_t) (c * 32), v2);
+                        tmem_ld_wait();
+                        if (ci == 0) {
 #pragma unroll
-                for (int j = 0; j < 8; j++)
-                    st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
-                                 v[4 * j + 2], v[4 * j + 3]);
-                __syncwarp();
-                if (!empty_range) {
-                    if (c + 1 < BN / 32) {
-                        tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);  // lands while this chunk is stored
-                    } else {
-                        // the accumulator has been read out: hand the buffer back before the stores
-                        tcgen05_fence_before();
-                        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                            for (int j = 0; j < 64; j++) sum[c * 32 + j] = v2[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 64; j++) sum[c * 32 + j] += v2[j];
+                        }
                     }
+                    tcgen05_fence_before();
+                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                    continue;
                 }
-                const int col = tn * BN + c * 32 + sub_c * 4;
+                // last chunk of the piece: out it goes
+                const int row0 = tm * BM + quarter * 32;
+                // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
+                // beyond the matrix are zeros computed from zero-filled operand tiles)
+                float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN + half * COLS : nullptr;
+                if (!empty_range) {
+                    tmem_ld32(t_addr, v);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int r = i * 4 + sub_r;
-                    float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
-                    const int row = row0 + r;
-                    if (args.bias != nullptr && slot == nullptr) {
-                        if (col < args.N) o.x += __ldg(args.bias + col);
-                        if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
-                        if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
-                        if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
+                    for (int j = 0; j < 32; j++) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int c = 0; c < LOADS; c++) {
+                    if (!empty_range) tmem_ld_wait();
+                    if (ci > 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] += sum[c * 32 + j];
                     }
-                    if (slot != nullptr) {
-                        *reinterpret_cast<float4*>(slot + (long long) r * BN + c * 32 + sub_c * 4) = o;
-                    } else if (row < args.M && col < args.N) {
-                        if (args.out_p > 0) {
-                            // convolution output: columns are (image, position); rows are output channels
-                            const int img = col / args.out_p, pos = col - img * args.out_p;
-                            float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
-                            if (p_vec && pos + 4 <= args.out_p && col + 4 <= args.N) {
-                                *reinterpret_cast<float4*>(dst) = o;
-                            } else {
-                                const float e[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                                for (int j = 0; j < 4; j++) {
-                                    const int cj = col + j;
-                                    if (cj < args.N) {
-                                        const int im = cj / args.out_p, ps = cj - im * args.out_p;
-                                        args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = e[j];
+                    for (int j = 0; j < 8; j++)
+                        st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                                     v[4 * j + 2], v[4 * j + 3]);
+                    __syncwarp();
+                    if (!empty_range) {
+                        if (c + 1 < LOADS) {
+                            tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);  // lands while this block is stored
+                        } else {
+                            // the accumulator has been read out: hand the buffer back before the stores
+                            tcgen05_fence_before();
+                            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                        }
+                    }
+                    const int col = tn * BN + half * COLS + c * 32 + sub_c * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int r = i * 4 + sub_r;
+                        float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
+                        const int row = row0 + r;
+                        if (args.bias != nullptr && slot == nullptr) {
+                            if (col < args.N) o.x += __ldg(args.bias + col);
+                            if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
+                            if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
+                            if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
+                        }
+                        if (slot != nullptr) {
+                            *reinterpret_cast<float4*>(slot + (long long) r * BN + c * 32 + sub_c * 4) = o;
+                        } else if (row < args.M && col < args.N) {
+                            if (args.out_p > 0) {
+                                // convolution output: columns are (image, position); rows are output channels
+                                const int img = col / args.out_p, pos = col - img * args.out_p;
+                                float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
+                                if (p_vec && pos + 4 <= args.out_p && col + 4 <= args.N) {
+                                    *reinterpret_cast<float4*>(dst) = o;
+                                } else {
+                                    const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) {
+                                        const int cj = col + j;
+                                        if (cj < args.N) {
+                                            const int im = cj / args.out_p, ps = cj - im * args.out_p;
+                                            args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = e[j];
+                                        }
                                     }
                                 }
-                            }
-                        } else {
-                            float* dst = args.C + (long long) row * args.ldc + col;
-                            if (c_vec && col + 4 <= args.N) {
-                                if (args.accumulate) {
-                                    const float4 old = *reinterpret_cast<const float4*>(dst);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *reinterpret_cast<float4*>(dst) = o;
                             } else {
-                                const float e[4] = {o.x, o.y, o.z, o.w};
+                                float* dst = args.C + (long long) row * args.ldc + col;
+                                if (c_vec && col + 4 <= args.N) {
+                                    if (args.accumulate) {
+                                        const float4 old = *reinterpret_cast<const float4*>(dst);
+                                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                    }
+                                    *reinterpret_cast<float4*>(dst) = o;
+                                } else {
+                                    const float e[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-                                for (int j = 0; j < 4; j++)
-                                    if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
+                                    for (int j = 0; j < 4; j++)
+                                        if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
+                                }
                             }
                         }
                     }
+                    __syncwarp();  // the patch is rewritten by the next block
                 }
-                __syncwarp();  // the patch is rewritten by the next chunk
-            }
-            if (empty_range) {
-                tcgen05_fence_before();
-                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                if (empty_range) {
+                    tcgen05_fence_before();
+                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                }
             }
         }
     }
@@ -612,12 +682,16 @@ int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int b
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
 
+// Choices the selector may override per shape (0 = the rule below): tile width, band height of the
+// tile walk, K pieces per tile of the ragged last wave, chunk length of the accumulation.  Set through
+// cakeb200_set_option / the tuning cache; the rules are what an untuned shape gets.
+struct Tunables {
+    int bn = 0, band = 0, pieces = 0, chunk_kb = 0;
+};
+Tunables g_tune;
+
 inline int tile_width(int N) {
-    static const int forced = [] {
-        const char* e = getenv("CAKEB200_BN");
-        return e ? atoi(e) : 0;
-    }();
-    if (forced == 128 || forced == 256) return forced;
+    if (g_tune.bn == 128 || g_tune.bn == 256) return g_tune.bn;
     return (N > 128) ? 256 : 128;
 }
 
@@ -625,14 +699,9 @@ inline int tile_width(int N) {
 // few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
 // the tall and the wide benchmark shapes alike (12 and 16 were equal on squares and up
 // to 20 % slower on the 65536 x 1024 x 1024 and 1024 x 1024 x 65536 products).
-// CAKEB200_BAND overrides it for experiments.
 int band_for(int order, int tiles_m, int tiles_n, int bn, int sm_count) {
     (void) bn; (void) sm_count;
-    static const int forced = [] {
-        const char* e = getenv("CAKEB200_BAND");
-        return e ? atoi(e) : 0;
-    }();
-    const int band = forced > 0 ? forced : 8;
+    const int band = g_tune.band > 0 ? g_tune.band : 8;
     return std::max(1, std::min(band, order == CAKEB200_SCHED_NKM ? tiles_n : tiles_m));
 }
 
@@ -678,10 +747,8 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
         const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
         if (cost < best * 0.97) { best = cost; best_s = s; }
     }
-    if (const char* e = getenv("CAKEB200_PIECES")) {  // experiments: force the number of K pieces per leftover tile
-        const int forced = atoi(e);
-        if (forced >= 1 && (long long) forced * R <= 4LL * sm_count + 8 && forced <= kblocks) best_s = forced;
-    }
+    if (g_tune.pieces >= 1 && (long long) g_tune.pieces * R <= 4LL * sm_count + 8 && g_tune.pieces <= kblocks)
+        best_s = g_tune.pieces;  // the selector's choice for this shape
     if (best_s == 1) return p;
     const int s = best_s;
     p.dp_tiles = (int) T - R;
@@ -713,10 +780,10 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
 // the last kernel that read it has finished (event), so asynchronous callers may queue
 // many products ahead.
 struct PlanKey {
-    int tiles_m, tiles_n, kblocks, order, sm_count, bn;
+    int tiles_m, tiles_n, kblocks, order, sm_count, bn, band, pieces;  // band, pieces: the overrides in force (0 = rule)
     bool operator==(const PlanKey& o) const {
         return tiles_m == o.tiles_m && tiles_n == o.tiles_n && kblocks == o.kblocks && order == o.order &&
-               sm_count == o.sm_count && bn == o.bn;
+               sm_count == o.sm_count && bn == o.bn && band == o.band && pieces == o.pieces;
     }
 };
 struct DevicePlan {
@@ -742,7 +809,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
     CAKE_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= PLAN_DEVICES) dev = 0;
     std::lock_guard<std::mutex> lock(g_plan_mutex);
-    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn};
+    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn, g_tune.band, g_tune.pieces};
     DevicePlan* slots = g_plans[dev];
     DevicePlan* victim = nullptr;
     for (int i = 0; i < PLAN_SLOTS; i++) {
@@ -825,6 +892,7 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
+    a.chunk_kb = g_tune.chunk_kb > 0 ? g_tune.chunk_kb : (a.kblocks <= 128 ? CHUNK_KB : 2 * CHUNK_KB);
     a.order = g.order;
     a.band = band_for(g.order, a.tiles_m, a.tiles_n, BN, sm_count);
     a.accumulate = g.accumulate;
@@ -1004,8 +1072,8 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
         int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, stream, &plan);
         if (rc) return rc;
     }
-    return (N > 128) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr)
-                     : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr);
+    return (tile_width(N) == 256) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr)
+                                  : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr);
 }
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + slots for the partial tiles of the last wave (worst case)
@@ -1074,6 +1142,43 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 }
 
 }  // namespace cakeb200
+
+// ------------------------------------------------- options of the large-matrix kernel
+extern "C" int cakeb200_set_option(const char* name, int value) {
+    using namespace cakeb200;
+    if (!name || value < 0) {
+        set_error("cakeb200_set_option: null name or negative value");
+        return CAKEB200_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    if (!strcmp(name, "tile_n")) {
+        if (value != 0 && value != 128 && value != 256) {
+            set_error("cakeb200_set_option: tile_n is 0, 128 or 256");
+            return CAKEB200_ERR_ARG;
+        }
+        g_tune.bn = value;
+    } else if (!strcmp(name, "band")) {
+        g_tune.band = value;
+    } else if (!strcmp(name, "k_pieces")) {
+        g_tune.pieces = value;
+    } else if (!strcmp(name, "chunk_kb")) {
+        g_tune.chunk_kb = value;
+    } else {
+        set_error("cakeb200_set_option: unknown option '%s' (tile_n, band, k_pieces, chunk_kb)", name);
+        return CAKEB200_ERR_ARG;
+    }
+    return CAKEB200_OK;
+}
+
+extern "C" int cakeb200_get_option(const char* name) {
+    using namespace cakeb200;
+    if (!name) return -1;
+    if (!strcmp(name, "tile_n")) return g_tune.bn;
+    if (!strcmp(name, "band")) return g_tune.band;
+    if (!strcmp(name, "k_pieces")) return g_tune.pieces;
+    if (!strcmp(name, "chunk_kb")) return g_tune.chunk_kb;
+    return -1;
+}
 
 // ------------------------------------------------- self-test of the bounded wait
 //

@@ -127,6 +127,21 @@ int cakeb200_sgemm(const float* A, const float* B, float* C, int M, int N, int K
 int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N, int K,
                          int accumulate, int sched, int kernel, void* stream, void* b_ready);
 
+/* Overrides of the large-matrix kernel's own choices, process-wide, 0 = back to the library's rule:
+ *   "tile_n"   128 or 256: columns of C per tile;
+ *   "band"     tile rows (columns for N-first) per band of the tile walk (rule: 8);
+ *   "k_pieces" K ranges each tile of the ragged last wave is cut into (rule: a cost model);
+ *   "chunk_kb" 32-deep slices of K accumulated in tensor memory before they are folded into the
+ *              FP32 running sum (rule: 16, i.e. 512 of K, up to K = 4096 and 32 above; a value >= K / 32 means one unbroken
+ *              accumulation, whose truncation error grows with K).
+ * They take the place of the block sizes a caller of the reference forces with mcu / kcu / ncu
+ * (reference include/cake.h:12-14, src/block_sizing.cpp:363-368) and of update_mr_nr
+ * (src/block_sizing.cpp:78-83): on a GPU the blocks a caller may pin are the tile, the walk and
+ * the cut along K.  The tuning cache (cakeb200_tune) applies them per shape.  cakeb200_get_option
+ * returns the override in force, -1 for an unknown name. */
+int cakeb200_set_option(const char* name, int value);
+int cakeb200_get_option(const char* name);
+
 /* Same, but only enqueues on `stream` (device pointers required, no host copies,
  * no synchronisation).  For callers that time or overlap the work themselves.
  * It can be recorded into a CUDA graph by stream capture once the same shape has

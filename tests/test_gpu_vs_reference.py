@@ -61,6 +61,22 @@ def test_full_product_against_the_reference(cake, oracle, reference, size):
         print("%d^3 kernel %d vs reference (%.2f s on %d host cores): normalised %.3e absolute %.3e"
               % (n, kernel, seconds, info["ncores"], err_n, err_a))
         assert err_n <= TOL
+        # The reference's own acceptance test (cake_sgemm_checker / mat_equals, absolute 1e-3 per element,
+        # reference src/util.cpp:139-169).  The exact-FP32 kernel meets it at every size; the tensor-core
+        # kernel folds its accumulation into an FP32 running sum every 512 of K up to K = 4096 and meets
+        # it at 3000^3 (the size the reference's own driver runs); above, with chunks of 1024, it stays
+        # within 3e-3 (one unbroken accumulation reaches 1e-2) and meets 1e-3 with chunks of 256.
+        assert err_a <= (1e-3 if kernel == cake.KERNEL_FFMA or n <= 4096 else 3e-3)
+    if n > 4096:
+        cake.set_option("chunk_kb", 8)
+        try:
+            C = torch.full((n, n), float("nan"), device="cuda")
+            cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+        finally:
+            cake.set_option("chunk_kb", 0)
+        err_n, err_a = _gate(C, C_ref, an, bn)
+        print("%d^3 tensor-core kernel, chunks of 256 of K: normalised %.3e absolute %.3e" % (n, err_n, err_a))
+        assert err_n <= TOL and err_a <= 1e-3
     # the host-pointer route (what a caller of the reference's API passes) gives the same bits as the device route
     Ch = np.empty((n, n), np.float32)
     cake.cake_sgemm(Ah, Bh, Ch, kernel=cake.KERNEL_TF32X3)
