@@ -104,6 +104,14 @@ _SIGNATURES["cakeb200_kshard_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _pf = ctypes.POINTER(ctypes.c_float)
 _SIGNATURES["cakeb200_tf32_peak"] = (_i, [ctypes.c_float, _pf, _pf, _vp])
+TUNE_COST = ctypes.CFUNCTYPE(ctypes.c_double, _i, _i, _i, _vp)
+_SIGNATURES["cakeb200_tune"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp])
+_SIGNATURES["cakeb200_tune_search"] = (_i, [_i, _i, _i, _i, _i, ctypes.c_ulonglong, TUNE_COST, _vp, _pi, _pi, _pi, _pf, _pi])
+_SIGNATURES["cakeb200_tune_put"] = (_i, [_i, _i, _i, _i, _i, _i, _i, ctypes.c_float])
+_SIGNATURES["cakeb200_tune_get"] = (_i, [_i, _i, _i, _i, _pi, _pi, _pi, _pf])
+_SIGNATURES["cakeb200_tune_clear"] = (_i, [])
+_SIGNATURES["cakeb200_tune_save"] = (_i, [ctypes.c_char_p])
+_SIGNATURES["cakeb200_tune_load"] = (_i, [ctypes.c_char_p])
 _SIGNATURES["cakeb200_set_option"] = (_i, [ctypes.c_char_p, _i])
 _SIGNATURES["cakeb200_get_option"] = (_i, [ctypes.c_char_p])
 _SIGNATURES["cakeb200_select_devices"] = (_i, [_pi, _i, _i, _i, _i, _i, _pi])
@@ -554,6 +562,59 @@ def tf32_peak(ms_target=0.0, stream=None):
     t, ms = ctypes.c_float(), ctypes.c_float()
     _check(lib().cakeb200_tf32_peak(ms_target, ctypes.byref(t), ctypes.byref(ms), ctypes.c_void_p(int(stream)) if stream else None))
     return t.value, ms.value
+
+
+def tune(A, B, C=None, sch=NA, trials=24, stream=None):
+    """Search the tile shape of the large-matrix kernel for this product's shape on the device and
+    remember the winner (cakeb200_tune).  Returns the winning entry as a dict."""
+    M, K = A.shape
+    K2, N = B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if C is None:
+        C = _empty_like_kind(A, (M, N))
+    _need_shape(C, (M, N), "C")
+    _check(lib().cakeb200_tune(_ptr(A), _ptr(B), _ptr(C), M, N, K, sch, trials, _stream_of(C, stream)))
+    st = last_stats()
+    return dict(tune_get(M, N, K, st["sched"]), evaluated=st["launches"])
+
+
+def tune_search(M, N, K, cost, sm_count=148, trials=24, seed=1):
+    """The search alone with a Python cost function cost(tile_n, band, k_pieces) -> ms (<= 0: invalid point)."""
+    cb = TUNE_COST(lambda w, b, p, _user: float(cost(w, b, p)))
+    w, b, p, n, ms = _i(), _i(), _i(), _i(), ctypes.c_float()
+    _check(lib().cakeb200_tune_search(M, N, K, sm_count, trials, seed, cb, None, ctypes.byref(w), ctypes.byref(b), ctypes.byref(p),
+                                      ctypes.byref(ms), ctypes.byref(n)))
+    return {"tile_n": w.value, "band": b.value, "k_pieces": p.value, "ms": ms.value, "evaluated": n.value}
+
+
+def tune_put(M, N, K, sch, tile_n, band, k_pieces, ms=0.0):
+    _check(lib().cakeb200_tune_put(M, N, K, sch, tile_n, band, k_pieces, ms))
+
+
+def tune_get(M, N, K, sch):
+    w, b, p, ms = _i(), _i(), _i(), ctypes.c_float()
+    if not lib().cakeb200_tune_get(M, N, K, sch, ctypes.byref(w), ctypes.byref(b), ctypes.byref(p), ctypes.byref(ms)):
+        return None
+    return {"tile_n": w.value, "band": b.value, "k_pieces": p.value, "ms": ms.value}
+
+
+def tune_clear():
+    _check(lib().cakeb200_tune_clear())
+
+
+def tune_save(path):
+    n = lib().cakeb200_tune_save(str(path).encode())
+    if n < 0:
+        _check(n)
+    return n
+
+
+def tune_load(path):
+    n = lib().cakeb200_tune_load(str(path).encode())
+    if n < 0:
+        _check(n)
+    return n
 
 
 def set_option(name, value):

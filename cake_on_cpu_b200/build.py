@@ -16,7 +16,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcake_b200.so")
 
-SOURCES = ["abi.cu", "sgemm_ffma.cu", "sgemm_tf32x3.cu", "sgemm_small_tf32x3.cu", "conv_tf32x3.cu", "gemv.cu", "kshard.cu", "peak_tf32.cu", "pack.cu", "sparse.cu", "conv.cu", "tiling.cpp", "host_api.cpp"]
+SOURCES = ["abi.cu", "sgemm_ffma.cu", "sgemm_tf32x3.cu", "sgemm_small_tf32x3.cu", "conv_tf32x3.cu", "gemv.cu", "kshard.cu", "peak_tf32.cu", "pack.cu", "sparse.cu", "conv.cu", "tiling.cpp", "tune.cpp", "host_api.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -68,6 +68,37 @@ def build(verbose=False, force=False):
     return LIB
 
 
+LINEAR_EXT = os.path.join(HERE, "linear_cpp.so")
+
+
+def build_linear_ext(force=False):
+    """Compile csrc/linear.cpp, the PyTorch extension `linear_cpp` of the reference's binding
+    (reference src/linear.cpp, python/setup.py), against include/cake.h and link it to
+    libcake_b200.so.  g++ only (the file holds no kernels); the module lands next to the library."""
+    src = os.path.join(CSRC, "linear.cpp")
+    if not force and os.path.exists(LINEAR_EXT) and os.path.getmtime(LINEAR_EXT) >= max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return LINEAR_EXT
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    cmd = [os.environ.get("CXX_FOR_EXT", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=linear_cpp",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", "-I", os.path.join(ROOT, "include"), "-I", cuda_inc,
+           "-I", sysconfig.get_paths()["include"]]
+    for inc in cpp_extension.include_paths():
+        cmd += ["-isystem", inc]
+    cmd += [src, "-o", LINEAR_EXT, "-L", libdir, "-lc10", "-lc10_cuda", "-ltorch", "-ltorch_cpu", "-ltorch_python",
+            "-L", HERE, "-l:libcake_b200.so", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + libdir]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("compiling linear.cpp failed")
+    return LINEAR_EXT
+
+
 if __name__ == "__main__":
     build(verbose="--verbose" in sys.argv, force=True)
     print(LIB)
+    if "--linear" in sys.argv:
+        print(build_linear_ext(force=True))

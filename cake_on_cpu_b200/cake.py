@@ -9,11 +9,25 @@ of the forward product and dY of the weight gradient; the reference makes
 contiguous transposed copies at src/linear.cpp:22 and :76-80) and the bias is
 added in the product's epilogue instead of a second pass (:44-46).
 """
+import os
+
 import torch
 from torch import nn
 from torch.nn import Parameter
 
 from . import api
+
+
+def linear_cpp():
+    """The compiled extension `linear_cpp` (csrc/linear.cpp, the counterpart of the reference's
+    src/linear.cpp built by python/setup.py); None when it has not been built
+    (`python -m cake_on_cpu_b200.build --linear`)."""
+    if not os.path.exists(os.path.join(os.path.dirname(os.path.abspath(__file__)), "linear_cpp.so")):
+        return None
+    api.lib()
+    from . import linear_cpp as ext
+    return ext
+
 
 
 def _rows(t):
@@ -39,15 +53,27 @@ def linear_backward(grad_output, input, weight, bias=None):
 
 
 class cake_linear_function(torch.autograd.Function):
+    """The autograd function of python/cake.py:18-31.  With the compiled extension present the three
+    products go through `linear_cpp.forward / backward` exactly as there; without it the ctypes
+    routines above compute the same products through the same C-ABI entry point."""
+
     @staticmethod
     def forward(ctx, data, weight, bias=None):
-        output = linear_forward(data, weight, bias)
+        ext = linear_cpp()
+        if ext is not None and data.dim() == 2:
+            output = ext.forward(data, weight, bias)
+        else:
+            output = linear_forward(data, weight, bias)
         ctx.save_for_backward(data, weight, bias)
         return output
 
     @staticmethod
     def backward(ctx, grad_output):
         data, weight, bias = ctx.saved_tensors
+        ext = linear_cpp()
+        if ext is not None and data.dim() == 2:
+            gi, gw, gb = ext.backward(grad_output.contiguous(), data, weight, bias)
+            return gi, gw, (gb if bias is not None else None)
         return linear_backward(grad_output, data, weight, bias)
 
 

@@ -584,6 +584,78 @@ int cakeb200_tf32_peak(float ms_target, float* tflops, float* ms, void* stream) 
     return CAKEB200_OK;
 }
 
+// ---- tile-shape search on the device (the cache and the search itself are host logic, tune.cpp)
+
+namespace {
+struct TuneRun {
+    DeviceState* st;
+    GemmProblem g;
+    cudaStream_t s;
+    int reps;
+    int rc;
+};
+
+// cost of one point of the grid: fastest of `reps` whole products (split pass + contraction) with the point forced
+double tune_cost(int tile_n, int band, int k_pieces, void* user) {
+    TuneRun* r = (TuneRun*) user;
+    if (cakeb200_set_option("tile_n", tile_n) || cakeb200_set_option("band", band) || cakeb200_set_option("k_pieces", k_pieces)) return -1;
+    double best = -1;
+    for (int i = 0; i < r->reps + 1; i++) {  // the first run uploads the tile plan of the point and is not timed
+        if (cudaEventRecord(r->st->ev[0], r->s) != cudaSuccess) return -1;
+        r->rc = launch_sgemm_tf32x3(r->g, r->st->scratch, r->st->scratch_bytes, r->st->status_word, r->st->sm_count, r->s, nullptr, nullptr);
+        if (r->rc) return -1;
+        if (cudaEventRecord(r->st->ev[1], r->s) != cudaSuccess || cudaEventSynchronize(r->st->ev[1]) != cudaSuccess) return -1;
+        const double ms = elapsed(r->st->ev[0], r->st->ev[1]);
+        if (i > 0 && (best < 0 || ms < best)) best = ms;
+    }
+    return best;
+}
+}  // namespace
+
+int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K, int sched, int trials, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!A || !B || !C || bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    if (!on_device(A) || !on_device(B) || !on_device(C)) {
+        set_error("cakeb200_tune needs device pointers");
+        return CAKEB200_ERR_ARG;
+    }
+    if (sched < 0 || sched > CAKEB200_SCHED_NA || trials < 1 || trials > 1000) {
+        set_error("cakeb200_tune: unknown schedule or trials outside 1..1000");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    TuneRun run = {};
+    run.st = st;
+    run.s = (cudaStream_t) stream;
+    run.reps = 3;
+    run.g.A = A; run.g.B = B; run.g.C = C;
+    run.g.M = M; run.g.N = N; run.g.K = K;
+    run.g.lda = K; run.g.ldb = N; run.g.ldc = N;
+    run.g.batch = 1;
+    run.g.order = resolve_schedule(st, M, N, K, sched);
+    int rc = ensure_scratch(st, tf32x3_scratch_bytes(M, N, K, st->sm_count));
+    if (rc) return rc;
+    const int keep[3] = {cakeb200_get_option("tile_n"), cakeb200_get_option("band"), cakeb200_get_option("k_pieces")};
+    int tile_n = 0, band = 0, k_pieces = 0, evaluated = 0;
+    float best_ms = 0.f;
+    rc = cakeb200_tune_search(M, N, K, st->sm_count, trials, 0x5eedULL + (unsigned long long) M * 31 + N * 17 + K, tune_cost, &run, &tile_n,
+                              &band, &k_pieces, &best_ms, &evaluated);
+    cakeb200_set_option("tile_n", keep[0]);
+    cakeb200_set_option("band", keep[1]);
+    cakeb200_set_option("k_pieces", keep[2]);
+    if (rc) return run.rc ? run.rc : rc;
+    if ((rc = check_status_word(st, run.s))) return rc;
+    if ((rc = cakeb200_tune_put(M, N, K, run.g.order, tile_n, band, k_pieces, best_ms))) return rc;
+    if (const char* path = getenv("CAKE_AUTOTUNE_CACHE")) cakeb200_tune_save(path);
+    g_stats.tile_m = 128; g_stats.tile_n = tile_n; g_stats.tile_k = 32;
+    g_stats.ms_gemm = best_ms;
+    g_stats.launches = evaluated;
+    g_stats.kernel = CAKEB200_KERNEL_TF32X3;
+    g_stats.sched = run.g.order;
+    return CAKEB200_OK;
+}
+
 int cakeb200_profile_begin(void) {
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;

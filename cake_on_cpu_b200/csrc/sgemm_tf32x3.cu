@@ -52,6 +52,8 @@
 #include "tcgen05.cuh"
 
 namespace cakeb200 {
+bool tune_lookup(int M, int N, int K, int sched, int* tile_n, int* band, int* k_pieces);  // tune.cpp
+
 namespace {
 
 using namespace ptx;
@@ -690,8 +692,21 @@ struct Tunables {
 };
 Tunables g_tune;
 
-inline int tile_width(int N) {
-    if (g_tune.bn == 128 || g_tune.bn == 256) return g_tune.bn;
+// What applies to one product: an explicit override wins, then the tuning cache's entry for the
+// shape, then the rule (a field left 0).
+Tunables resolve_tunables(int M, int N, int K, int order) {
+    Tunables t = g_tune;
+    int w = 0, b = 0, p = 0;
+    if (tune_lookup(M, N, K, order, &w, &b, &p)) {
+        if (!t.bn) t.bn = w;
+        if (!t.band) t.band = b;
+        if (!t.pieces) t.pieces = p;
+    }
+    return t;
+}
+
+inline int tile_width(int N, const Tunables& t) {
+    if ((t.bn == 128 || t.bn == 256) && !(t.bn == 256 && N <= 128)) return t.bn;
     return (N > 128) ? 256 : 128;
 }
 
@@ -699,9 +714,8 @@ inline int tile_width(int N) {
 // few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
 // the tall and the wide benchmark shapes alike (12 and 16 were equal on squares and up
 // to 20 % slower on the 65536 x 1024 x 1024 and 1024 x 1024 x 65536 products).
-int band_for(int order, int tiles_m, int tiles_n, int bn, int sm_count) {
-    (void) bn; (void) sm_count;
-    const int band = g_tune.band > 0 ? g_tune.band : 8;
+int band_for(int order, int tiles_m, int tiles_n, const Tunables& t) {
+    const int band = t.band > 0 ? t.band : 8;
     return std::max(1, std::min(band, order == CAKEB200_SCHED_NKM ? tiles_n : tiles_m));
 }
 
@@ -719,9 +733,9 @@ struct HostPlan {
     std::vector<TilePieces> pieces;
 };
 
-HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn) {
+HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, const Tunables& tn) {
     HostPlan p;
-    const int band = band_for(order, tiles_m, tiles_n, bn, sm_count);
+    const int band = band_for(order, tiles_m, tiles_n, tn);
     const long long T = (long long) tiles_m * tiles_n;
     const int G = (int) std::min<long long>(T, sm_count);
     p.grid = G;
@@ -747,8 +761,8 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
         const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
         if (cost < best * 0.97) { best = cost; best_s = s; }
     }
-    if (g_tune.pieces >= 1 && (long long) g_tune.pieces * R <= 4LL * sm_count + 8 && g_tune.pieces <= kblocks)
-        best_s = g_tune.pieces;  // the selector's choice for this shape
+    if (tn.pieces >= 1 && (long long) tn.pieces * R <= 4LL * sm_count + 8 && tn.pieces <= kblocks)
+        best_s = tn.pieces;  // the selector's choice for this shape
     if (best_s == 1) return p;
     const int s = best_s;
     p.dp_tiles = (int) T - R;
@@ -804,12 +818,13 @@ DevicePlan g_plans[PLAN_DEVICES][PLAN_SLOTS];
 unsigned long long g_plan_clock = 0;
 std::mutex g_plan_mutex;
 
-int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn, cudaStream_t stream, DevicePlan** out) {
+int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn, const Tunables& tn, cudaStream_t stream,
+             DevicePlan** out) {
     int dev = 0;
     CAKE_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= PLAN_DEVICES) dev = 0;
     std::lock_guard<std::mutex> lock(g_plan_mutex);
-    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn, g_tune.band, g_tune.pieces};
+    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn, tn.band, tn.pieces};
     DevicePlan* slots = g_plans[dev];
     DevicePlan* victim = nullptr;
     for (int i = 0; i < PLAN_SLOTS; i++) {
@@ -833,7 +848,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
             return CAKEB200_ERR_ARG;
         }
     }
-    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, bn);
+    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, tn);
     const size_t units_b = align_up(hp.units.size() * sizeof(int4) + 16, 256);
     const size_t begin_b = align_up(hp.cta_begin.size() * sizeof(int), 256);
     const size_t pieces_b = align_up(hp.pieces.size() * sizeof(TilePieces) + 16, 256);
@@ -874,7 +889,7 @@ size_t partial_slot_bytes(int sm_count) { return (size_t) (4 * sm_count + 8) * B
 // plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots)
 template <int BN>
 int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, DevicePlan* plan,
-           int* status_word, int sm_count, cudaStream_t stream, int* launches) {
+           int* status_word, int sm_count, cudaStream_t stream, int* launches, const Tunables& tn) {
     const int Kp = padded_k(g.K);
     alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
@@ -892,9 +907,9 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
-    a.chunk_kb = g_tune.chunk_kb > 0 ? g_tune.chunk_kb : (a.kblocks <= 128 ? CHUNK_KB : 2 * CHUNK_KB);
+    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (a.kblocks <= 128 ? CHUNK_KB : 2 * CHUNK_KB);
     a.order = g.order;
-    a.band = band_for(g.order, a.tiles_m, a.tiles_n, BN, sm_count);
+    a.band = band_for(g.order, a.tiles_m, a.tiles_n, tn);
     a.accumulate = g.accumulate;
     a.out_p = g.out_p;
     a.out_image_stride = g.out_image_stride;
@@ -1067,13 +1082,14 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     float* a_hi = p.a_hi + (size_t) r0 * p.Kp;
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
     DevicePlan* plan = nullptr;
+    const Tunables tn = resolve_tunables(rows, N, K, order);
+    const int bn = tile_width(N, tn);
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
-        const int bn = tile_width(N);
-        int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, stream, &plan);
+        int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, tn, stream, &plan);
         if (rc) return rc;
     }
-    return (tile_width(N) == 256) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr)
-                                  : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr);
+    return (bn == 256) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr, tn)
+                       : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr, tn);
 }
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + slots for the partial tiles of the last wave (worst case)
@@ -1085,10 +1101,11 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
 
 bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
     if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return false;
-    const int bn = tile_width(N), kblocks = (K + BK - 1) / BK;
+    const Tunables tn = resolve_tunables(M, N, K, order);
+    const int bn = tile_width(N, tn), kblocks = (K + BK - 1) / BK;
     const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     if (tiles >= sm_count) return false;
-    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, bn);
+    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, tn);
     return hp.dp_tiles == 0 && !hp.pieces.empty();
 }
 
@@ -1107,7 +1124,8 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* b_lo = (float*) (base + 2 * a_bytes + b_bytes);
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
-    const int bn = tile_width(g.N);
+    const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
+    const int bn = tile_width(g.N, tn);
     const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
@@ -1128,11 +1146,11 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
     DevicePlan* plan = nullptr;
-    if ((rc = get_plan((g.M + BM - 1) / BM, (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order, sm_count, bn, stream, &plan)))
+    if ((rc = get_plan((g.M + BM - 1) / BM, (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order, sm_count, bn, tn, stream, &plan)))
         return rc;
     int launches = 2;
-    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches)
-                     : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches);
+    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn)
+                     : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn);
     if (rc) return rc;
     if (stats) {
         stats->launches += launches;
@@ -1323,8 +1341,8 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
     // whole-K tiles only: cutting tiles along K would need slots for partial tiles, i.e. more scratch
-    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr)
-                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr);
+    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr, Tunables())
+                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr, Tunables());
     if (rc) return rc;
     int word[4] = {0, 0, 0, 0};
     CAKE_CUDA_OK(cudaMemcpyAsync(word, status_word, sizeof(word), cudaMemcpyDeviceToHost, s));

@@ -142,6 +142,40 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
 int cakeb200_set_option(const char* name, int value);
 int cakeb200_get_option(const char* name);
 
+/* ---- Tile-shape selection with a persistent cache.
+ *
+ * Replaces the reference's block-size autotuner (reference src/autotune_sa.cpp:13-82 and
+ * include/autotune.h:82-86: random-step search over (m_c, k_c, n_c) with a visited set; dead
+ * code there, not compiled by its Makefile).  On a GPU the blocks worth searching are the tile
+ * width, the band height of the tile walk and the cut of the last wave's tiles along K.
+ *
+ * cakeb200_tune times the large-matrix kernel on the caller's operands (device pointers; C is
+ * overwritten with the product every time) at up to `trials` points of that grid, walking it by
+ * random steps from the rule's own choice, and records the fastest point for (M, N, K, schedule);
+ * later products of that shape use it.  After the call cakeb200_get_stats reports the winning
+ * tile_n, its time (ms_gemm) and the points evaluated (launches).  Explicit options
+ * (cakeb200_set_option) still win over the cache.  The search changes the process-wide options
+ * while it runs: no other thread should multiply meanwhile.
+ *
+ * The cache lives in the process; _save / _load write and read it as JSON (they return the number
+ * of entries, or a negative status), and the file named by the environment variable
+ * CAKE_AUTOTUNE_CACHE is loaded on first use and rewritten after every cakeb200_tune.  _put / _get
+ * / _clear edit it directly (_get returns 1 when the shape has an entry, else 0); `sched` is a
+ * resolved schedule (KMN, MKN or NKM).
+ *
+ * cakeb200_tune_search is the search alone, host logic: `cost` returns the time of a point in
+ * milliseconds (<= 0: not a valid point) and may be anything, which is how the search is tested
+ * without a device. */
+typedef double (*cakeb200_tune_cost)(int tile_n, int band, int k_pieces, void* user);
+int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K, int sched, int trials, void* stream);
+int cakeb200_tune_search(int M, int N, int K, int sm_count, int trials, unsigned long long seed, cakeb200_tune_cost cost,
+                         void* user, int* tile_n, int* band, int* k_pieces, float* best_ms, int* evaluated);
+int cakeb200_tune_put(int M, int N, int K, int sched, int tile_n, int band, int k_pieces, float ms);
+int cakeb200_tune_get(int M, int N, int K, int sched, int* tile_n, int* band, int* k_pieces, float* ms);
+int cakeb200_tune_clear(void);
+int cakeb200_tune_save(const char* path);
+int cakeb200_tune_load(const char* path);
+
 /* Same, but only enqueues on `stream` (device pointers required, no host copies,
  * no synchronisation).  For callers that time or overlap the work themselves.
  * It can be recorded into a CUDA graph by stream capture once the same shape has
