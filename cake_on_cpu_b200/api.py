@@ -104,6 +104,9 @@ _SIGNATURES["cakeb200_kshard_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemv"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp])
 _pf = ctypes.POINTER(ctypes.c_float)
 _SIGNATURES["cakeb200_tf32_peak"] = (_i, [ctypes.c_float, _pf, _pf, _vp])
+_SIGNATURES["cakeb200_planes_create"] = (_i, [_vp, _i, _i, _i, ctypes.POINTER(_vp), _vp])
+_SIGNATURES["cakeb200_planes_destroy"] = (_i, [_vp])
+_SIGNATURES["cakeb200_sgemm_planes"] = (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp])
 TUNE_COST = ctypes.CFUNCTYPE(ctypes.c_double, _i, _i, _i, _vp)
 _SIGNATURES["cakeb200_tune"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_tune_search"] = (_i, [_i, _i, _i, _i, _i, ctypes.c_ulonglong, TUNE_COST, _vp, _pi, _pi, _pi, _pf, _pi])
@@ -562,6 +565,49 @@ def tf32_peak(ms_target=0.0, stream=None):
     t, ms = ctypes.c_float(), ctypes.c_float()
     _check(lib().cakeb200_tf32_peak(ms_target, ctypes.byref(t), ctypes.byref(ms), ctypes.c_void_p(int(stream)) if stream else None))
     return t.value, ms.value
+
+
+class Planes:
+    """An operand split once into its TF32 hi / lo planes and kept on the device (cakeb200_planes_create):
+    the counterpart of an operand packed once with pack_A / pack_B and passed with packedA / packedB = 1.
+    ``Planes(A)`` for the left operand (M x K), ``Planes(B, is_b=True)`` for the right one (K x N)."""
+
+    def __init__(self, mat, is_b=False, stream=None):
+        r, c = mat.shape
+        self.rows, self.K, self.is_b = (c, r, True) if is_b else (r, c, False)
+        self._h = _vp()
+        _check(lib().cakeb200_planes_create(_ptr(mat), self.rows, self.K, int(is_b), ctypes.byref(self._h), _stream_of(mat, stream)))
+
+    def close(self):
+        if self._h:
+            lib().cakeb200_planes_destroy(self._h)
+            self._h = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def cake_sgemm_planes(A, B, C=None, sch=NA, accumulate=False, stream=None):
+    """C (+)= A @ B where A and / or B is a ``Planes`` object (the other a matrix): cakeb200_sgemm_planes."""
+    pa, pb = isinstance(A, Planes), isinstance(B, Planes)
+    if not (pa or pb):
+        raise TypeError("at least one operand must be a Planes object")
+    M, K = (A.rows, A.K) if pa else A.shape
+    K2, N = (B.K, B.rows) if pb else B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if C is None:
+        if pa and pb:
+            raise ValueError("give C when both operands are planes")
+        C = _empty_like_kind(B if pa else A, (M, N))
+        accumulate = False
+    _need_shape(C, (M, N), "C")
+    _check(lib().cakeb200_sgemm_planes(A._h if pa else None, None if pa else _ptr(A), B._h if pb else None, None if pb else _ptr(B),
+                                       _ptr(C), M, N, K, int(bool(accumulate)), sch, _stream_of(C, stream)))
+    return C
 
 
 def tune(A, B, C=None, sch=NA, trials=24, stream=None):

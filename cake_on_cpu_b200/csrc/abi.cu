@@ -584,6 +584,112 @@ int cakeb200_tf32_peak(float ms_target, float* tflops, float* ms, void* stream) 
     return CAKEB200_OK;
 }
 
+// ---- an operand kept in the kernel's own form across products
+
+struct cakeb200_planes {
+    float *hi = nullptr, *lo = nullptr;
+    int rows = 0, K = 0, is_b = 0, device = -1;
+    size_t bytes = 0;  // of one plane
+};
+
+int cakeb200_planes_create(const float* mat, int rows, int K, int is_b, cakeb200_planes** out, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!mat || !out || rows <= 0 || K <= 0) {
+        set_error("cakeb200_planes_create: bad argument");
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    cudaStream_t s = (cudaStream_t) stream;
+    cakeb200_planes* p = new cakeb200_planes();
+    p->rows = rows; p->K = K; p->is_b = is_b ? 1 : 0; p->device = st->device;
+    p->bytes = tf32x3_one_plane_bytes(rows, K);
+    cudaError_t e = cudaMalloc((void**) &p->hi, 2 * p->bytes);
+    if (e != cudaSuccess) {
+        set_error("cakeb200_planes_create: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        delete p;
+        return CAKEB200_ERR_CUDA;
+    }
+    p->lo = (float*) ((char*) p->hi + p->bytes);
+    Operand om;
+    // A: rows x K row-major.  B: K x rows row-major, split into its transposed planes (rows x K).
+    int rc = stage_in(st, 0, om, mat, (size_t) rows * K * 4, true, s);
+    if (!rc) rc = tf32x3_make_planes((const float*) om.dev, rows, K, is_b ? rows : K, is_b != 0, p->hi, p->lo, st->sm_count, s);
+    if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = CAKEB200_ERR_CUDA;
+    if (rc) {
+        cudaFree(p->hi);
+        cudaGetLastError();
+        delete p;
+        return rc;
+    }
+    g_stats.launches = 1;
+    *out = p;
+    return CAKEB200_OK;
+}
+
+int cakeb200_planes_destroy(cakeb200_planes* p) {
+    if (!p) return CAKEB200_OK;
+    if (p->hi) {
+        cudaDeviceSynchronize();  // a product still reading the planes finishes first
+        cudaFree(p->hi);
+        cudaGetLastError();
+    }
+    delete p;
+    return CAKEB200_OK;
+}
+
+int cakeb200_sgemm_planes(const cakeb200_planes* A_planes, const float* A, const cakeb200_planes* B_planes, const float* B,
+                          float* C, int M, int N, int K, int accumulate, int sched, void* stream) {
+    g_stats = cakeb200_stats();
+    if (!C || (!A_planes && !A) || (!B_planes && !B)) {
+        set_error("cakeb200_sgemm_planes: every operand needs planes or a matrix");
+        return CAKEB200_ERR_ARG;
+    }
+    if (bad_dims(M, N, K)) return CAKEB200_ERR_ARG;
+    if (sched < 0 || sched > CAKEB200_SCHED_NA) {
+        set_error("unknown schedule %d", sched);
+        return CAKEB200_ERR_ARG;
+    }
+    DeviceState* st = device_state();
+    if (!st) return CAKEB200_ERR_NO_DEVICE;
+    if ((A_planes && (A_planes->is_b || A_planes->rows != M || A_planes->K != K || A_planes->device != st->device)) ||
+        (B_planes && (!B_planes->is_b || B_planes->rows != N || B_planes->K != K || B_planes->device != st->device))) {
+        set_error("cakeb200_sgemm_planes: the planes were made for another operand, shape or device");
+        return CAKEB200_ERR_ARG;
+    }
+    cudaStream_t s = (cudaStream_t) stream;
+    Operand oa, ob, oc;
+    int rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
+    if (!A_planes && (rc = stage_in(st, 0, oa, A, (size_t) M * K * 4, true, s))) return rc;
+    if (!B_planes && (rc = stage_in(st, 1, ob, B, (size_t) K * N * 4, true, s))) return rc;
+    if ((rc = stage_in(st, 2, oc, C, (size_t) M * N * 4, accumulate != 0, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[1], s));
+    GemmProblem g = {};
+    g.A = (const float*) oa.dev; g.B = (const float*) ob.dev; g.C = (float*) oc.dev;
+    g.M = M; g.N = N; g.K = K;
+    g.lda = K; g.ldb = N; g.ldc = N;
+    g.batch = 1;
+    g.accumulate = accumulate ? 1 : 0;
+    g.order = resolve_schedule(st, M, N, K, sched);
+    if (A_planes) { g.a_hi = A_planes->hi; g.a_lo = A_planes->lo; }
+    if (B_planes) { g.b_hi = B_planes->hi; g.b_lo = B_planes->lo; }
+    g_stats.sched = g.order;
+    g_stats.kernel = CAKEB200_KERNEL_TF32X3;
+    if ((rc = ensure_scratch(st, tf32x3_scratch_bytes(M, N, K, st->sm_count)))) return rc;
+    if ((rc = launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats, &st->ev[4]))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[2], s));
+    if ((rc = stage_out(oc, s))) return rc;
+    CAKE_CUDA_OK(cudaEventRecord(st->ev[3], s));
+    if ((rc = check_status_word(st, s))) return rc;
+    g_stats.ms_h2d = elapsed(st->ev[0], st->ev[1]);
+    g_stats.ms_prepass = elapsed(st->ev[4], st->ev[5]);
+    g_stats.ms_gemm = elapsed(st->ev[1], st->ev[2]) - g_stats.ms_prepass;
+    g_stats.ms_d2h = elapsed(st->ev[2], st->ev[3]);
+    return CAKEB200_OK;
+}
+
 // ---- tile-shape search on the device (the cache and the search itself are host logic, tune.cpp)
 
 namespace {
@@ -786,7 +892,8 @@ struct cakeb200_kshard {
     char* peer[MAX_RANKS] = {};    // peer[rank] is this rank's own buffer
     bool ipc_opened[MAX_RANKS] = {};
     bool connected = false;
-    int epoch = 0;
+    int epoch = 0;      // products started (partial)
+    int finished = 0;   // products completed (finish); partial is refused while epoch != finished
 };
 
 namespace {
@@ -905,6 +1012,12 @@ int cakeb200_kshard_partial(cakeb200_kshard* x, const float* A, int lda, const f
         set_error("kshard_partial: the ranks are not connected yet");
         return CAKEB200_ERR_ARG;
     }
+    if (x->epoch != x->finished) {
+        // the two slot sets alternate by product number: a second product may only start once this rank's
+        // rows of the first have been summed, or an owner still reading set (epoch & 1) would be overwritten
+        set_error("kshard_partial: the previous product has not been finished (call cakeb200_kshard_finish first)");
+        return CAKEB200_ERR_ARG;
+    }
     if (bad_dims(x->M, x->N, K_local)) return CAKEB200_ERR_ARG;
     if (lda < K_local || ldb < x->N || !on_device(A) || !on_device(B)) {
         set_error("kshard_partial: needs device operands with lda >= K and ldb >= N");
@@ -923,11 +1036,11 @@ int cakeb200_kshard_partial(cakeb200_kshard* x, const float* A, int lda, const f
     cudaStream_t s = (cudaStream_t) stream;
     int rc;
     if ((rc = ensure_scratch(st, tf32x3_scratch_bytes(x->M, x->N, K_local, st->sm_count)))) return rc;
-    x->epoch++;
-    const int set = x->epoch & 1;
+    const int epoch = x->epoch + 1;  // counted only once the launch below has succeeded
+    const int set = epoch & 1;
     OwnerSlots os = {};
     os.world = x->world;
-    os.epoch = x->epoch;
+    os.epoch = epoch;
     os.done = (unsigned*) (x->peer[x->rank] + KSHARD_DONE_AT);
     for (int o = 0; o < x->world; o++) {
         os.base[o] = (float*) (x->peer[o] + KSHARD_HEADER) + ((long long) set * x->world + x->rank) * x->slot_floats;
@@ -944,11 +1057,13 @@ int cakeb200_kshard_partial(cakeb200_kshard* x, const float* A, int lda, const f
     g.owners = &os;
     g_stats.kernel = CAKEB200_KERNEL_TF32X3;
     g_stats.sched = g.order;
-    return launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats, nullptr);
+    rc = launch_sgemm_tf32x3(g, st->scratch, st->scratch_bytes, st->status_word, st->sm_count, s, &g_stats, nullptr);
+    if (rc == CAKEB200_OK) x->epoch = epoch;  // a failed launch publishes nothing: the peers' count is unchanged
+    return rc;
 }
 
 int cakeb200_kshard_finish(cakeb200_kshard* x, float* C_block, int wait_limit_us, void* stream) {
-    if (!x || x->epoch == 0) {
+    if (!x || x->epoch == x->finished) {
         set_error("kshard_finish: no product in flight");
         return CAKEB200_ERR_ARG;
     }
@@ -971,7 +1086,9 @@ int cakeb200_kshard_finish(cakeb200_kshard* x, float* C_block, int wait_limit_us
                                     (const int*) x->peer[x->rank], x->epoch, limit_ns, st->status_word, st->sm_count, s);
     if (rc) return rc;
     g_stats.launches += 1;
-    return check_status_word(st, s);
+    rc = check_status_word(st, s);
+    if (rc == CAKEB200_OK) x->finished = x->epoch;  // after a timeout the product stays open: finish may be called again
+    return rc;
 }
 
 int cakeb200_kshard_destroy(cakeb200_kshard* x) {

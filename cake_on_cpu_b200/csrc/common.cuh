@@ -43,6 +43,10 @@ struct GemmProblem {
     // trans_b -> B points at an N x K row-major matrix (ldb >= K); the product is op(A) * op(B)
     int trans_a, trans_b;
     const float* bias;  // length N, added to every row of the result (nullptr: none)
+    // 3xTF32 path only: operands already split into TF32 hi / lo planes by an earlier call (both K-major with
+    // leading dimension ceil4(K): a_* is M x Kp, b_* is N x Kp, i.e. B transposed).  Where set, the operand's
+    // split pass is skipped and A (B) itself is not read.
+    const float *a_hi, *a_lo, *b_hi, *b_lo;
     // 3xTF32 path only, K-sharded product over several GPUs: when set, the rows of the result are not
     // stored at C but sent to the ranks that own them (see OwnerSlots)
     const struct OwnerSlots* owners;
@@ -129,6 +133,11 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
                          long long out_image_stride = 0);
 int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_bytes, int* status_word,
                         int sm_count, cudaStream_t stream, cakeb200_stats* stats, cudaEvent_t* prepass_events);
+// hi / lo planes of one operand, for callers that keep an operand split across many products (weights):
+// bytes of one plane and the split itself (transpose: `mat` is K x rows row-major, as B is; else rows x K)
+size_t tf32x3_one_plane_bytes(int rows, int K);
+int tf32x3_make_planes(const float* mat, int rows, int K, int ld, bool transpose, float* hi, float* lo, int sm_count,
+                       cudaStream_t stream);
 // true when the tile plan of this shape cuts every tile into K pieces, so that the kernel that sums the
 // pieces is the only one that stores rows of the result (the condition for GemmProblem::owners)
 bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count);

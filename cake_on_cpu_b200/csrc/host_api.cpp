@@ -370,6 +370,74 @@ int grid_dims_2d(int M, int N, int K, int p, int ncores) {
 }
 
 // ------------------------------------------------------------------ packing
+//
+// pack_A / pack_B write the reference's packed layout byte for byte (callers size and inspect those
+// buffers).  The tensor-core kernel's own preferred form of an operand is something else, its two
+// TF32 planes, so a pack call also splits the operand once and keeps the planes on the device,
+// remembered under the address of the packed buffer.  cake_sgemm(..., packedA / packedB = 1) looks the
+// buffer up and multiplies straight from the planes: no unpacking, no second split.  A buffer the
+// registry does not know (copied elsewhere, or its few sampled words differ: the memory was reused)
+// is unpacked instead, which is slower and always right.  At most 8 plane sets are kept (the least
+// recently used goes first); each costs two copies of its operand in device memory.
+
+namespace {
+
+struct KeptPlanes {
+    const void* packed = nullptr;
+    int rows = 0, K = 0, is_b = 0;
+    size_t floats = 0;
+    float sample[8] = {};
+    bool sampled = false;
+    cakeb200_planes* planes = nullptr;
+    unsigned long long stamp = 0;
+};
+KeptPlanes g_kept[8];
+unsigned long long g_kept_clock = 0;
+std::mutex g_kept_mutex;
+
+bool sample_packed(const float* packed, size_t floats, float* out) {
+    if (is_device_ptr(packed) || floats == 0) return false;
+    for (int i = 0; i < 8; i++) out[i] = packed[(floats - 1) * i / 7];
+    return true;
+}
+
+void keep_planes(const float* mat, const float* packed, size_t packed_floats, int rows, int K, int is_b) {
+    if (rows < 128 || K < 32) return;  // products this small do not run on the tensor cores
+    cakeb200_planes* planes = nullptr;
+    if (cakeb200_planes_create(mat, rows, K, is_b, &planes, nullptr) != CAKEB200_OK) return;  // the packed buffer alone still works
+    std::lock_guard<std::mutex> lock(g_kept_mutex);
+    KeptPlanes* slot = nullptr;
+    for (auto& k : g_kept)
+        if (k.packed == packed) slot = &k;
+    if (!slot)
+        for (auto& k : g_kept)
+            if (!slot || k.stamp < slot->stamp) slot = &k;
+    if (slot->planes) cakeb200_planes_destroy(slot->planes);
+    slot->packed = packed;
+    slot->rows = rows; slot->K = K; slot->is_b = is_b;
+    slot->floats = packed_floats;
+    slot->sampled = sample_packed(packed, packed_floats, slot->sample);
+    slot->planes = planes;
+    slot->stamp = ++g_kept_clock;
+}
+
+// planes recorded for this packed buffer by pack_A / pack_B, or nullptr
+const cakeb200_planes* kept_planes(const float* packed, int rows, int K, int is_b) {
+    std::lock_guard<std::mutex> lock(g_kept_mutex);
+    for (auto& k : g_kept) {
+        if (k.packed != packed || !k.planes || k.rows != rows || k.K != K || k.is_b != is_b) continue;
+        if (k.sampled) {
+            float now[8];
+            if (!sample_packed(packed, k.floats, now) || memcmp(now, k.sample, sizeof(now)) != 0) return nullptr;
+        }
+        k.stamp = ++g_kept_clock;
+        return k.planes;
+    }
+    return nullptr;
+}
+
+}  // namespace
+
 
 size_t cake_sgemm_packed_A_size(int M, int K, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
     cakeb200_cntx c = to_abi(cake_cntx);
@@ -390,13 +458,18 @@ double pack_A(float* A, float* A_p, int M, int K, int p, blk_dims_t* x, cake_cnt
     cakeb200_blk_dims d = *as_abi(x);
     d.sch = sch;
     if (cakeb200_pack_A(A, A_p, M, K, p, &d, &c, nullptr)) return fail("pack_A");
+    keep_planes(A, A_p, cakeb200_packed_A_size(M, K, p, &d, &c, sch) / sizeof(float), M, K, 0);
     return now_s() - t0;
 }
 void pack_B(float* B, float* B_p, int K, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
     cakeb200_cntx c = to_abi(cake_cntx);
     cakeb200_blk_dims d = *as_abi(x);
     d.sch = sch;
-    if (cakeb200_pack_B(B, B_p, K, N, p, &d, &c, nullptr)) fail("pack_B");
+    if (cakeb200_pack_B(B, B_p, K, N, p, &d, &c, nullptr)) {
+        fail("pack_B");
+        return;
+    }
+    keep_planes(B, B_p, cakeb200_packed_B_size(K, N, p, &d, &c) / sizeof(float), N, K, 1);
 }
 void pack_C(float* C, float* C_p, int M, int N, int p, blk_dims_t* x, cake_cntx_t* cake_cntx, enum sched sch) {
     cakeb200_cntx c = to_abi(cake_cntx);
@@ -451,6 +524,16 @@ double sgemm_driver(float* A, float* B, float* C, int M, int N, int K, int p, ca
 
     float *A_plain = A, *B_plain = B;
     int rc = CAKEB200_OK;
+    // packed operands: multiply from the planes pack_A / pack_B kept, when they did and the tensor cores are to run
+    const bool tensor_ok = preferred_kernel() != CAKEB200_KERNEL_FFMA && M >= 128 && N >= 128 && K >= 32;
+    const cakeb200_planes* pa = (packedA && tensor_ok) ? kept_planes(A, M, K, 0) : nullptr;
+    const cakeb200_planes* pb = (packedB && tensor_ok) ? kept_planes(B, N, K, 1) : nullptr;
+    if ((pa || !packedA) && (pb || !packedB) && (pa || pb)) {
+        rc = cakeb200_sgemm_planes(pa, pa ? nullptr : A, pb, pb ? nullptr : B, C, M, N, K, accumulate, sch, nullptr);
+        if (own) free(own);
+        if (rc) return fail("cake_sgemm");
+        return now_s() - t0;
+    }
     if (packedA && !(A_plain = unpacked_copy(true, A, M, K, M, N, K, p, &x, cake_cntx))) rc = CAKEB200_ERR_CUDA;
     if (!rc && packedB && !(B_plain = unpacked_copy(false, B, K, N, M, N, K, p, &x, cake_cntx))) rc = CAKEB200_ERR_CUDA;
     if (!rc) {

@@ -1099,6 +1099,14 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
 }
 
+size_t tf32x3_one_plane_bytes(int rows, int K) { return align_up((size_t) rows * padded_k(K) * 4, 1024); }
+
+int tf32x3_make_planes(const float* mat, int rows, int K, int ld, bool transpose, float* hi, float* lo, int sm_count,
+                       cudaStream_t stream) {
+    const int Kp = padded_k(K);
+    return transpose ? run_split_transpose(mat, hi, lo, K, rows, ld, Kp, stream) : run_split_rows(mat, hi, lo, rows, K, ld, Kp, sm_count, stream);
+}
+
 bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
     if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return false;
     const Tunables tn = resolve_tunables(M, N, K, order);
@@ -1118,10 +1126,11 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     const int Kp = padded_k(g.K);
     const size_t a_bytes = align_up((size_t) g.M * Kp * 4, 1024), b_bytes = align_up((size_t) g.N * Kp * 4, 1024);
     char* base = (char*) align_up((size_t) scratch, 1024);
-    float* a_hi = (float*) base;
-    float* a_lo = (float*) (base + a_bytes);
-    float* b_hi = (float*) (base + 2 * a_bytes);
-    float* b_lo = (float*) (base + 2 * a_bytes + b_bytes);
+    // planes the caller kept from an earlier split are used where they lie; the others go to the scratch arena
+    float* a_hi = g.a_hi ? const_cast<float*>(g.a_hi) : (float*) base;
+    float* a_lo = g.a_hi ? const_cast<float*>(g.a_lo) : (float*) (base + a_bytes);
+    float* b_hi = g.b_hi ? const_cast<float*>(g.b_hi) : (float*) (base + 2 * a_bytes);
+    float* b_lo = g.b_hi ? const_cast<float*>(g.b_lo) : (float*) (base + 2 * a_bytes + b_bytes);
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
     const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
@@ -1131,24 +1140,35 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
         return CAKEB200_ERR_ARG;
     }
+    if ((g.a_hi && !g.a_lo) || (g.b_hi && !g.b_lo) || (((uintptr_t) a_hi | (uintptr_t) a_lo | (uintptr_t) b_hi | (uintptr_t) b_lo) % 16)) {
+        set_error("sgemm_tf32x3: operand planes come in hi / lo pairs, 16-byte aligned");
+        return CAKEB200_ERR_ARG;
+    }
 
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[0], stream));
-    int rc;
+    int rc = CAKEB200_OK;
+    int split_launches = 0;
     // both operand planes are K-major; an operand already stored that way (A as given, B
     // transposed, e.g. the N x K weight of a linear layer) is split in place, the other
     // kind is transposed through shared memory on the way
-    if (g.trans_a) rc = run_split_transpose(g.A, a_hi, a_lo, g.K, g.M, g.lda, Kp, stream);
-    else rc = run_split_rows(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp, sm_count, stream);
-    if (rc) return rc;
-    if (g.trans_b) rc = run_split_rows(g.B, b_hi, b_lo, g.N, g.K, g.ldb, Kp, sm_count, stream);
-    else rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream);
-    if (rc) return rc;
+    if (!g.a_hi) {
+        if (g.trans_a) rc = run_split_transpose(g.A, a_hi, a_lo, g.K, g.M, g.lda, Kp, stream);
+        else rc = run_split_rows(g.A, a_hi, a_lo, g.M, g.K, g.lda, Kp, sm_count, stream);
+        if (rc) return rc;
+        split_launches++;
+    }
+    if (!g.b_hi) {
+        if (g.trans_b) rc = run_split_rows(g.B, b_hi, b_lo, g.N, g.K, g.ldb, Kp, sm_count, stream);
+        else rc = run_split_transpose(g.B, b_hi, b_lo, g.K, g.N, g.ldb, Kp, stream);
+        if (rc) return rc;
+        split_launches++;
+    }
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
     DevicePlan* plan = nullptr;
     if ((rc = get_plan((g.M + BM - 1) / BM, (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order, sm_count, bn, tn, stream, &plan)))
         return rc;
-    int launches = 2;
+    int launches = split_launches;
     rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn)
                      : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn);
     if (rc) return rc;
@@ -1268,13 +1288,15 @@ int noalloc_scratch(unsigned char** out) {
     return CAKEB200_OK;
 }
 
-bool noalloc_on_device(const void* p) {
+// device memory of the device `dev` (the kernels run there; memory of another GPU may not even be mapped)
+bool noalloc_on_device(const void* p, int dev) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+    if (a.type == cudaMemoryTypeManaged) return true;
+    return a.type == cudaMemoryTypeDevice && a.device == dev;
 }
 
 }  // namespace
@@ -1291,8 +1313,11 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
         set_error("cakeb200_sgemm_noalloc: null pointer or non-positive dimension");
         return CAKEB200_ERR_ARG;
     }
-    if (!noalloc_on_device(A) || !noalloc_on_device(B) || !noalloc_on_device(C)) {
-        set_error("cakeb200_sgemm_noalloc: A, B and C must be device pointers (staging a host operand would allocate)");
+    int cur_dev = -1;
+    CAKE_CUDA_OK(cudaGetDevice(&cur_dev));
+    if (!noalloc_on_device(A, cur_dev) || !noalloc_on_device(B, cur_dev) || !noalloc_on_device(C, cur_dev)) {
+        set_error("cakeb200_sgemm_noalloc: A, B and C must be device pointers of the current device %d (staging a host "
+                  "operand would allocate; another GPU's memory is not reachable from the kernels)", cur_dev);
         return CAKEB200_ERR_ARG;
     }
     const size_t need = noalloc_scratch_need(M, N, K);

@@ -142,6 +142,26 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
 int cakeb200_set_option(const char* name, int value);
 int cakeb200_get_option(const char* name);
 
+/* ---- An operand kept in the kernel's preferred form across products.
+ *
+ * The reference lets a caller pack an operand once and pass packedA / packedB = 1 to every later
+ * cake_sgemm (reference src/cake_sgemm.cpp:40-85 skips pack_A / pack_B then; used with stationary
+ * weights in examples/cake_conv.cpp:1032-1055).  The tensor-core kernel's preferred form is not a
+ * blocked copy but the operand's two TF32 planes (hi = tf32(v), lo = tf32(v - hi), K-major), so that
+ * is what is kept: cakeb200_planes_create splits a matrix once into device memory owned by the object
+ * (is_b == 0: `mat` is A, rows x K row-major; is_b != 0: `mat` is B, K x rows row-major, and its
+ * transposed planes are stored), and cakeb200_sgemm_planes multiplies with planes standing in for A,
+ * for B or for both (pass NULL for the planes of an operand that is given as a matrix, and the matrix
+ * pointer may be NULL where planes are given).  The operand's split pass, a third of the time of a
+ * product with little reuse, is then not repeated.  Host or device pointers for the matrices and C;
+ * the call blocks like cakeb200_sgemm.  The C++ API's pack_A / pack_B record such planes next to the
+ * layout-exact packed buffer, which is how cake_sgemm(..., packedA = 1) finds them. */
+typedef struct cakeb200_planes cakeb200_planes;
+int cakeb200_planes_create(const float* mat, int rows, int K, int is_b, cakeb200_planes** out, void* stream);
+int cakeb200_planes_destroy(cakeb200_planes* p);
+int cakeb200_sgemm_planes(const cakeb200_planes* A_planes, const float* A, const cakeb200_planes* B_planes, const float* B,
+                          float* C, int M, int N, int K, int accumulate, int sched, void* stream);
+
 /* ---- Tile-shape selection with a persistent cache.
  *
  * Replaces the reference's block-size autotuner (reference src/autotune_sa.cpp:13-82 and
@@ -244,6 +264,12 @@ int cakeb200_selftest_bounded_wait(int limit_us, void* stream);
  * Call order on every rank: create -> exchange the 64-byte handles between the
  * processes by any means -> connect_ipc -> any number of (partial, finish) pairs, the
  * same number on every rank, all on one stream -> a barrier of the caller's -> destroy.
+ * partial and finish must alternate: a second partial before the finish of the first is
+ * refused (CAKEB200_ERR_ARG), because the slots alternate between two sets by product
+ * number and an owner may still be reading the set a third product would write.  A finish
+ * that gave up waiting leaves the product open: call finish again (the late rank may still
+ * arrive) or destroy the object; a new partial is refused until a finish has succeeded.  A
+ * partial whose launch failed publishes nothing and does not count.
  * cakeb200_kshard_finish blocks until this rank's rows are complete; it waits at most
  * `wait_limit_us` (0: 2 s) for the other ranks and otherwise returns
  * CAKEB200_ERR_DEVICE_TIMEOUT with "where 910" and the missing rank in the error text,
@@ -361,19 +387,25 @@ int cakeb200_unpack_B(float* B, const float* B_p, int K, int N, int p, const cak
  * cudaMalloc, cudaFree or other allocating call.
  *   - A, B, C must be DEVICE pointers (copying a host operand would need a buffer).
  *   - Limit: 1024 + 2*roundup1024(4*M*ceil4(K)) + 2*roundup1024(4*N*ceil4(K)) bytes
- *     must fit in CAKEB200_NOALLOC_SCRATCH_BYTES (17 MiB: 1024 x 1024 x 1024 fits;
- *     so does 2048 x 512 x 1024).  Larger shapes return CAKEB200_ERR_TOO_LARGE and
- *     compute nothing.
+ *     must fit in CAKEB200_NOALLOC_SCRATCH_BYTES (17 MiB).  With the arguments in this
+ *     function's order: M = N = K = 1024 fits (16 MiB of planes); so does M = 2048,
+ *     N = 1024, K = 512 (12 MiB); M = 2048, N = 512, K = 1024 (20 MiB) does not.  Larger
+ *     shapes return CAKEB200_ERR_TOO_LARGE and compute nothing.
+ *   - A, B and C must belong to the current device (CAKEB200_ERR_ARG otherwise).
  *   - The array occupies that much memory on every GPU that loads the library,
  *     until the process exits.
- *   - The first call on a device looks up the array's device address; make that
- *     first call before starting any stream capture.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress).  With CUDA's default lazy module loading that first call, or
+ *     the first kernel launch of this library, is also when the driver loads the library's
+ *     module and reserves the array, which is an allocation in effect and synchronises.
+ *     Make one call (any small product) at start-up, outside any stream capture, before
+ *     the region that must not allocate; or start the process with CUDA_MODULE_LOADING=EAGER.
  *   - All calls on a device share the one array: two calls whose work overlaps on
  *     the GPU (different streams, or different threads) race on it.  Issue them
  *     one after the other.  Each call clears the state it needs at its start, so
  *     what an earlier call left behind does not matter.
- *   - `stream` is a cudaStream_t (NULL = the default stream).  The call returns
- *     after the work has finished and the device-side status has been read. */
+ *   - `stream` is a cudaStream_t (NULL = the default stream).  Every call synchronises
+ *     `stream` before it returns (it reads the device-side status word back). */
 #define CAKEB200_NOALLOC_SCRATCH_BYTES (17u << 20)
 int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, int M, int N, int K, void* stream);
 

@@ -55,6 +55,23 @@ int main(int argc, char* argv[]) {
         std::fill(C.begin(), C.end(), -7.f);
         schedule_KMN(A_p.data(), B_p.data(), C.data(), NULL, M, N, K, p, cntx, &x);
         expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "schedule_KMN result");
+        // a packed buffer moved to another address is not one the library kept planes for: it is unpacked instead
+        std::vector<float> A_moved(A_p), B_moved(B_p);
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm(A_moved.data(), B_moved.data(), C.data(), M, N, K, p, cntx, NULL, 1, 1, 1, 0, KMN) > 0, "packed cake_sgemm, moved buffers");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "moved packed operands result");
+        // the same address refilled with another operand's packed image (without pack_A): the kept planes must not be used
+        std::vector<float> A2((size_t) M * K), A2_p(A_p.size());
+        rand_init(A2.data(), M, K);
+        pack_A(A2.data(), A2_p.data(), M, K, p, &x, cntx, KMN);
+        memcpy(A_p.data(), A2_p.data(), A_p.size() * sizeof(float));
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm(A_p.data(), B_p.data(), C.data(), M, N, K, p, cntx, NULL, 1, 1, 1, 0, KMN) > 0, "packed cake_sgemm, refilled buffer");
+        expect(cake_sgemm_checker(A2.data(), B.data(), C.data(), N, M, K) == 0, "refilled packed operand result");
+        // one operand packed, the other plain
+        std::fill(C.begin(), C.end(), -7.f);
+        expect(cake_sgemm(A.data(), B_p.data(), C.data(), M, N, K, p, cntx, NULL, 0, 1, 1, 0, KMN) > 0, "cake_sgemm, packed B only");
+        expect(cake_sgemm_checker(A.data(), B.data(), C.data(), N, M, K) == 0, "packed B only result");
     }
     // M-first on packed operands accumulates into packed C; unpack_C brings it back
     {

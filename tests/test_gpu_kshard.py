@@ -117,3 +117,45 @@ def test_shapes_the_exchange_does_not_take(cake):
             x.partial(A, B)
     finally:
         x.close()
+
+
+def test_partial_and_finish_must_alternate(cake):
+    """Misuse is refused on the host, before any launch: a second partial before the finish of the first (its
+    slot set may still be read by an owner), a finish with nothing in flight, and a new partial after a finish
+    that gave up waiting."""
+    import torch
+    from cake_on_cpu_b200 import api, partition
+    world, M, K, N = 2, 256, 8192, 256
+    A, B = _operands(M, K, N, 24)
+    ranks = [api.KShard(world, r, M, N) for r in range(world)]
+    try:
+        api.KShard.connect_local(ranks)
+        with pytest.raises(api.CakeError) as e:
+            ranks[0].finish()
+        assert e.value.code == -1
+        k0, k1 = partition.k_block(K, world, 0)
+        ranks[0].partial(A[:, k0:k1], B[k0:k1])
+        with pytest.raises(api.CakeError) as e:
+            ranks[0].partial(A[:, k0:k1], B[k0:k1])
+        assert e.value.code == -1 and "finish" in str(e.value)
+        with pytest.raises(api.CakeError) as e:  # rank 1 has not stored: the wait gives up after 2 ms
+            ranks[0].finish(wait_limit_us=2000)
+        assert e.value.code == -4
+        with pytest.raises(api.CakeError) as e:  # still open: no new product
+            ranks[0].partial(A[:, k0:k1], B[k0:k1])
+        assert e.value.code == -1
+        k0, k1 = partition.k_block(K, world, 1)
+        ranks[1].partial(A[:, k0:k1], B[k0:k1])
+        for x in ranks:
+            lo, hi = x.rows
+            assert _norm_err(x.finish(), A, B, lo, hi) <= TOL
+        # and the next product runs as usual
+        for r, x in enumerate(ranks):
+            k0, k1 = partition.k_block(K, world, r)
+            x.partial(A[:, k0:k1], B[k0:k1])
+        for x in ranks:
+            lo, hi = x.rows
+            assert _norm_err(x.finish(), A, B, lo, hi) <= TOL
+    finally:
+        for x in ranks:
+            x.close()

@@ -533,3 +533,28 @@ def test_errors_are_status_codes(cake):
     # the library is still usable afterwards
     C = cake.cake_sgemm(np.eye(4, dtype=np.float32), np.eye(4, dtype=np.float32))
     assert np.array_equal(C, np.eye(4, dtype=np.float32))
+
+
+def test_operand_planes_kept_across_products(cake):
+    """An operand split once (cakeb200_planes_create, what pack_A / pack_B keep behind packedA / packedB = 1) gives
+    the same bits as the product that splits it on every call, with the operand's split kernel gone from the call."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for (M, K, N) in [(1000, 515, 777), (2048, 1024, 512), (130, 36, 140)]:
+        A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
+        B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
+        want = cake.cake_sgemm(A, B, kernel=cake.KERNEL_TF32X3)
+        base = cake.last_stats()["launches"]
+        pa, pb = cake.Planes(A), cake.Planes(B, is_b=True)
+        try:
+            assert torch.equal(cake.cake_sgemm_planes(pa, B), want) and cake.last_stats()["launches"] == base - 1
+            assert torch.equal(cake.cake_sgemm_planes(A, pb), want) and cake.last_stats()["launches"] == base - 1
+            C = torch.full((M, N), float("nan"), device="cuda")
+            assert torch.equal(cake.cake_sgemm_planes(pa, pb, C), want) and cake.last_stats()["launches"] == base - 2
+            # host matrices work too, and planes of the wrong operand or shape are refused
+            assert np.array_equal(cake.cake_sgemm_planes(A.cpu().numpy(), pb), want.cpu().numpy())
+            with pytest.raises(cake.CakeError):
+                cake.cake_sgemm_planes(pb, B)
+        finally:
+            pa.close()
+            pb.close()

@@ -60,3 +60,53 @@ def test_no_alloc_entry_point_rejects_what_it_cannot_hold(cake):
     # still usable afterwards
     I = torch.eye(64, device="cuda")
     assert torch.equal(cake.cake_sgemm_noalloc(I, I, torch.empty((64, 64), device="cuda")), I)
+
+
+def test_size_limit_follows_the_documented_formula(cake):
+    """The header's examples, in the function's own (M, N, K) order: 2048 x 1024 x 512 fits the 17 MiB array,
+    2048 x 512 x 1024 does not (A's planes alone take 16 MiB)."""
+    import torch
+    torch.cuda.set_device(0)
+    M, N, K = 2048, 1024, 512
+    A = torch.rand((M, K), device="cuda") * 2 - 1
+    B = torch.rand((K, N), device="cuda") * 2 - 1
+    C = cake.cake_sgemm_noalloc(A, B, torch.empty((M, N), device="cuda"))
+    assert _norm_err(C, A.double() @ B.double(), A, B) <= TOL
+    M, N, K = 2048, 512, 1024
+    with pytest.raises(cake.CakeError) as e:
+        cake.cake_sgemm_noalloc(torch.zeros((M, K), device="cuda"), torch.zeros((K, N), device="cuda"), torch.empty((M, N), device="cuda"))
+    assert e.value.code == -5
+
+
+def test_first_library_call_of_a_process_may_be_the_no_alloc_one(cake):
+    """A fresh process whose very first call into the library is the no-allocation entry point: that first call
+    is where the driver loads the library's module (and with it the built-in array) under CUDA's lazy loading,
+    so it is the warm-up the header asks for; the second call must then leave the device's free memory alone
+    and give the same bits."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = """
+import torch, cake_on_cpu_b200 as cake
+torch.cuda.set_device(0)
+g = torch.Generator(device='cuda').manual_seed(11)
+A = torch.rand((512, 384), device='cuda', generator=g) * 2 - 1
+B = torch.rand((384, 640), device='cuda', generator=g) * 2 - 1
+C1 = torch.empty((512, 640), device='cuda'); C2 = torch.empty((512, 640), device='cuda')
+torch.cuda.synchronize()
+cake.cake_sgemm_noalloc(A, B, C1)            # first call into the library in this process
+free_before = torch.cuda.mem_get_info()[0]
+cake.cake_sgemm_noalloc(A, B, C2)
+free_after = torch.cuda.mem_get_info()[0]
+exact = A.double() @ B.double()
+den = A.double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
+err = ((C2.double() - exact).abs() / den).max().item()
+print('RESULT', int(torch.equal(C1, C2)), int(free_after >= free_before), err)
+"""
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, PYTHONPATH=root))
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT")]
+    assert line, r.stderr[-2000:]
+    same, no_new_memory, err = line[0].split()[1:]
+    assert same == "1" and no_new_memory == "1" and float(err) <= TOL
