@@ -31,16 +31,18 @@
 // into a running sum held in registers with round-to-nearest FP32 adds, so only
 // the chunk length, not K, sets the truncation error.  The fold overlaps the MMAs
 // of the next chunk; the last chunk is added on the way out to global memory.
-// Reading an accumulator out of tensor memory occupies the tensor pipe for about 2300
-// cycles (tcgen05.ld delivers ~57 bytes per clock per SM and the MMAs wait meanwhile;
-// loads of 32 or 64 columns, one or two in flight, all cost the same), so every fold
-// costs the time of 17 MMAs and the chunk length trades accuracy for speed.  Measured
-// at 8192^3, uniform(-1, 1), largest absolute error over 64 rows / kernel time: chunks
-// of 128 / 256 / 512 / 1024 of K and one unbroken accumulation give 1.4e-4 / 2.7e-4 /
-// 5.3e-4 / 1.1e-3 / 1.0e-2 and 5.43 / 4.81 / 4.44 / 4.26 / 4.19 ms.  Rule: 512 up to
-// K = 4096 (3000^3 then stays below 1e-3 everywhere), 1024 above (1 to 2 % of the
-// kernel time, error a fifth of the unbroken accumulation's); the "chunk_kb" option
-// sets it (8: below 1e-3 at 8192^3 as well, for 15 % of the kernel time).
+// Reading an accumulator out of tensor memory is not free: each fold costs the MMAs about
+// 2300 cycles (the time of 17 of them), whether the loads are 32 or 64 columns wide, one or
+// two in flight, bunched or spread over the chunk, so the chunk length trades accuracy for
+// speed.  Largest absolute error over the whole matrix against float64, uniform(-1, 1), and
+// kernel time, for chunks of 512 / 768 / 1024 / 1536 of K / one unbroken accumulation:
+//   3000^3: 3.3e-4 / 5.2e-4 / 7.3e-4 / 1.1e-3 / 2.5e-3,  0.282 / 0.271 / 0.270 / 0.265 / 0.263 ms
+//   4096^3: 4.4e-4 / 6.5e-4 / 9.2e-4 / 1.3e-3 / 3.6e-3,  0.594 / 0.568 / 0.557 / 0.555 / 0.541 ms
+//   8192^3 (64 rows sampled): 5.3e-4 / - / 1.1e-3 / - / 1.0e-2,  4.44 / - / 4.26 / - / 4.19 ms
+// (the exact-FP32 FFMA kernel: 2.3e-4, 3.7e-4 and, against the reference's own result,
+// 9.5e-4 at 8192^3).  Rule: 1024 of K, which keeps every product up to 4096^3 below the
+// reference's 1e-3 for 2 to 3 % of the kernel time; the "chunk_kb" option sets it (8, i.e.
+// 256 of K, brings 8192^3 to 9.0e-4 against the reference, for 15 % of the kernel time).
 #include <cuda.h>
 
 #include <stdlib.h>
@@ -63,7 +65,7 @@ constexpr int BK = 32;           // K per pipeline stage: 32 floats = one 128-by
 constexpr int UMMA_K = 8;        // K of one tcgen05.mma kind::tf32
 constexpr int NUM_THREADS = 384;   // warp group 0: TMA warp, MMA warp, two idle warps; groups 1 and 2: drain warps
 constexpr int EPI_WARPS = 8;      // two per quarter of the tensor-memory lanes, each taking half of the columns
-constexpr int CHUNK_KB = 16;      // default chunk: 16 slices of 32 = 512 of K (twice that for K above 4096)
+constexpr int CHUNK_KB = 32;      // default chunk: 32 slices of 32 = 1024 of K
 
 template <int BN>
 struct Cfg {
@@ -294,9 +296,8 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN + half * COLS);
                 float v[32];
                 if (ci + 1 < chunks) {
-                    // fold: sum (+)= chunk, round to nearest.  A tensor-memory load queues behind the MMAs
-                    // already issued (microseconds), so two loads are in flight per wait: four waits in a
-                    // row took longer than a chunk of 256 of K and stalled the MMAs.
+                    // fold: sum (+)= chunk, round to nearest; 64 columns per load and wait (a tensor-memory
+                    // load queues behind the MMAs already issued, so fewer, wider loads shorten the fold)
                     float v2[64];
 #pragma unroll
                     for (int c = 0; c < LOADS; c += 2) {
@@ -907,7 +908,7 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
-    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (a.kblocks <= 128 ? CHUNK_KB : 2 * CHUNK_KB);
+    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : CHUNK_KB;
     a.order = g.order;
     a.band = band_for(g.order, a.tiles_m, a.tiles_n, tn);
     a.accumulate = g.accumulate;

@@ -132,7 +132,7 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
  *   "band"     tile rows (columns for N-first) per band of the tile walk (rule: 8);
  *   "k_pieces" K ranges each tile of the ragged last wave is cut into (rule: a cost model);
  *   "chunk_kb" 32-deep slices of K accumulated in tensor memory before they are folded into the
- *              FP32 running sum (rule: 16, i.e. 512 of K, up to K = 4096 and 32 above; a value >= K / 32 means one unbroken
+ *              FP32 running sum (rule: 32, i.e. 1024 of K; a value >= K / 32 means one unbroken
  *              accumulation, whose truncation error grows with K).
  * They take the place of the block sizes a caller of the reference forces with mcu / kcu / ncu
  * (reference include/cake.h:12-14, src/block_sizing.cpp:363-368) and of update_mr_nr
