@@ -747,6 +747,29 @@ int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K,
     float best_ms = 0.f;
     rc = cakeb200_tune_search(M, N, K, st->sm_count, trials, 0x5eedULL + (unsigned long long) M * 31 + N * 17 + K, tune_cost, &run, &tile_n,
                               &band, &k_pieces, &best_ms, &evaluated);
+    // The clocks drift while dozens of candidates run, so times taken minutes apart do not compare.  The winner
+    // is therefore run again in turns with the rule's own choice, and it replaces the rule only when it is
+    // at least 3 % faster on the median of those turns.
+    if (!rc) {
+        double win[5], rule[5];
+        bool ok = true;
+        run.reps = 2;
+        for (int i = 0; i < 5 && ok; i++) {
+            rule[i] = tune_cost(0, 0, 0, &run);
+            win[i] = tune_cost(tile_n, band, k_pieces, &run);
+            ok = rule[i] > 0 && win[i] > 0;
+        }
+        if (ok) {
+            std::sort(win, win + 5);
+            std::sort(rule, rule + 5);
+            if (win[2] > 0.97 * rule[2]) {  // not clearly better: record the rule itself
+                tile_n = 0; band = 8; k_pieces = 0;
+                best_ms = (float) rule[2];
+            } else {
+                best_ms = (float) win[2];
+            }
+        }
+    }
     cakeb200_set_option("tile_n", keep[0]);
     cakeb200_set_option("band", keep[1]);
     cakeb200_set_option("k_pieces", keep[2]);

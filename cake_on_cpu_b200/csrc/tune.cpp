@@ -67,7 +67,7 @@ int load_locked(const char* path) {
         float ms;
         if (sscanf(text.c_str() + at, "{\"M\": %d, \"N\": %d, \"K\": %d, \"sched\": %d, \"tile_n\": %d, \"band\": %d, \"k_pieces\": %d, \"ms\": %f}",
                    &M, &N, &K, &s, &t, &b, &p, &ms) == 8 &&
-            M > 0 && N > 0 && K > 0 && s >= 0 && s <= 2 && (t == 128 || t == 256) && b >= 1 && p >= 0) {
+            M > 0 && N > 0 && K > 0 && s >= 0 && s <= 2 && (t == 0 || t == 128 || t == 256) && b >= 1 && p >= 0) {
             g_cache[ShapeKey(M, N, K, s)] = {t, b, p, ms};
             loaded++;
         }
@@ -119,7 +119,7 @@ using namespace cakeb200;
 extern "C" {
 
 int cakeb200_tune_put(int M, int N, int K, int sched, int tile_n, int band, int k_pieces, float ms) {
-    if (M <= 0 || N <= 0 || K <= 0 || sched < 0 || sched > 2 || (tile_n != 128 && tile_n != 256) || band < 1 || k_pieces < 0) {
+    if (M <= 0 || N <= 0 || K <= 0 || sched < 0 || sched > 2 || (tile_n != 0 && tile_n != 128 && tile_n != 256) || band < 1 || k_pieces < 0) {
         set_error("cakeb200_tune_put: bad entry");
         return CAKEB200_ERR_ARG;
     }

@@ -171,8 +171,9 @@ int cakeb200_sgemm_planes(const cakeb200_planes* A_planes, const float* A, const
  *
  * cakeb200_tune times the large-matrix kernel on the caller's operands (device pointers; C is
  * overwritten with the product every time) at up to `trials` points of that grid, walking it by
- * random steps from the rule's own choice, and records the fastest point for (M, N, K, schedule);
- * later products of that shape use it.  After the call cakeb200_get_stats reports the winning
+ * random steps from the rule's own choice; the fastest point is then run in turns with the rule's
+ * choice and recorded for (M, N, K, schedule) when it is at least 3 % faster, else the rule itself
+ * is recorded (tile_n = 0); later products of that shape use the entry.  After the call cakeb200_get_stats reports the winning
  * tile_n, its time (ms_gemm) and the points evaluated (launches).  Explicit options
  * (cakeb200_set_option) still win over the cache.  The search changes the process-wide options
  * while it runs: no other thread should multiply meanwhile.

