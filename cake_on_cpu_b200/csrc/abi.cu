@@ -2,6 +2,7 @@
 // handling, kernel selection and timing.  No arithmetic happens here and there
 // is no CPU fallback: every product is computed by a kernel of this library.
 #include <algorithm>
+#include <atomic>
 #include <climits>
 #include <cstdarg>
 #include <cstdlib>
@@ -31,6 +32,12 @@ std::mutex g_state_mutex;
 constexpr int MAX_DEVICES = 64;
 DeviceState* g_states[MAX_DEVICES] = {};
 }  // namespace
+
+namespace {
+std::atomic<int> g_options[OPT_COUNT];
+const char* const g_option_names[OPT_COUNT] = {"tile_n", "band", "k_pieces", "chunk_kb", "conv_route", "small_operands", "pack_scalar"};
+}  // namespace
+int option_get(int id) { return (id >= 0 && id < OPT_COUNT) ? g_options[id].load() : 0; }
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -548,6 +555,32 @@ int cakeb200_query_cntx(cakeb200_cntx* out) {
     if (!st) return CAKEB200_ERR_NO_DEVICE;
     b200_cntx(st, out);
     return CAKEB200_OK;
+}
+
+int cakeb200_set_option(const char* name, int value) {
+    if (!name || value < 0) {
+        set_error("cakeb200_set_option: null name or negative value");
+        return CAKEB200_ERR_ARG;
+    }
+    for (int i = 0; i < OPT_COUNT; i++) {
+        if (strcmp(name, g_option_names[i])) continue;
+        if ((i == OPT_TILE_N && value != 0 && value != 128 && value != 256) || (i == OPT_CONV_ROUTE && value > 3) ||
+            (i == OPT_SMALL_OPERANDS && value > 2) || (i == OPT_PACK_SCALAR && value > 1)) {
+            set_error("cakeb200_set_option: %d is not a value of '%s'", value, name);
+            return CAKEB200_ERR_ARG;
+        }
+        g_options[i] = value;
+        return CAKEB200_OK;
+    }
+    set_error("cakeb200_set_option: unknown option '%s'", name);
+    return CAKEB200_ERR_ARG;
+}
+
+int cakeb200_get_option(const char* name) {
+    if (!name) return -1;
+    for (int i = 0; i < OPT_COUNT; i++)
+        if (!strcmp(name, g_option_names[i])) return g_options[i];
+    return -1;
 }
 
 int cakeb200_tf32_peak(float ms_target, float* tflops, float* ms, void* stream) {
@@ -1282,7 +1315,7 @@ int cakeb200_conv2d(const float* in, const float* filters, float* out, int batch
         set_error("unknown kernel id %d", kernel);
         return CAKEB200_ERR_ARG;
     }
-    if (tensor && getenv("CAKEB200_CONV_PLANES") == nullptr &&
+    if (tensor && option_get(OPT_CONV_ROUTE) != 1 &&
         conv_tf32x3_fits((const float*) oi.dev, batch, cin, H, W, cout, hf, wf, stride, pad)) {
         // Implicit product: input rows come on chip by TMA, the patch operand is built in shared memory
         if ((rc = ensure_scratch(st, conv_tf32x3_scratch_bytes(cin, cout, hf, wf)))) return rc;

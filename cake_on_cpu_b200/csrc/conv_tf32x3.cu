@@ -518,10 +518,10 @@ bool plan(ConvArgs& a, const float* in, int batch, int cin, int H, int W, int co
     const long long flat_tiles = (a.positions + BM - 1) / BM * a.ntiles;
     ConvArgs f = a;
     f.flat = 1;
-    const bool flat_ok = segs > 0 && getenv("CAKEB200_CONV_ROWS") == nullptr && layout(f, segs, span);
+    const bool flat_ok = segs > 0 && option_get(OPT_CONV_ROUTE) != 2 && layout(f, segs, span);
     // flat tiles when they save a round of tiles on the machine (or when row tiles do not fit at all)
     const long long sms = std::max(sm_count, 1);
-    const bool take_flat = flat_ok && (!rows_ok || getenv("CAKEB200_CONV_FLAT") != nullptr ||
+    const bool take_flat = flat_ok && (!rows_ok || option_get(OPT_CONV_ROUTE) == 3 ||
                                        (flat_tiles + sms - 1) / sms < (row_tiles + sms - 1) / sms);
     if (take_flat) {
         a = f;

@@ -375,7 +375,7 @@ int run_move(std::vector<ObDesc>& descs, float* mat, float* packed, int ld, int 
         return true;
     };
     int vec = allows(4) ? 4 : (KIND == OB_A && allows(2)) ? 2 : 1;
-    if (getenv("CAKEB200_PACK_SCALAR")) vec = 1;  // for tests: the one-element-per-thread path
+    if (option_get(OPT_PACK_SCALAR)) vec = 1;  // for tests: the one-element-per-thread path
     g_last_width = vec;
     // enough CTAs per block to cover it with ~8 elements (2 quads) per thread, capped
     int chunks = (int) std::min<long long>(std::max<long long>((biggest + 2047) / 2048, 1), 1024);

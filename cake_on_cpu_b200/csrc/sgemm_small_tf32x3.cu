@@ -620,7 +620,7 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
     a.raw_bytes = (a.raw_a_bytes + a.raw_b_bytes + 127) / 128 * 128;
     a.raw_tx = (g.M + a.npad) * 128;
     const bool tma_ok = (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (g.stride_a % 4 == 0) && (g.stride_b % 4 == 0) &&
-                        (((uintptr_t) g.A | (uintptr_t) g.B) % 16 == 0) && getenv("CAKEB200_SMALL_DIRECT") == nullptr;
+                        (((uintptr_t) g.A | (uintptr_t) g.B) % 16 == 0) && option_get(OPT_SMALL_OPERANDS) != 2;
     // two split stages (one being multiplied, one being filled); the rest of shared memory goes to the
     // ring of raw boxes, whose depth is what keeps enough bytes in flight (measured at 96^3: ring of
     // 2 / 3 / 4 boxes -> 0.145 / 0.126 / 0.124 ms for 4096 products; a third split stage instead: 0.139 ms)
@@ -628,7 +628,7 @@ int launch_sgemm_small_tf32x3(const GemmProblem& g, int* status_word, int sm_cou
     a.ring = tma_ok ? std::min(MAX_RING, (MAX_SMEM - fixed - a.stages * a.stage_bytes) / a.raw_bytes) : 0;
     // With room in tensor memory next to the two accumulators (N up to 192) the split A operand goes there:
     // shared memory then holds only B's planes and raw boxes (A's box 128-byte swizzled, in 1 KiB units).
-    if (tma_ok && a.acc_stride <= 192 && getenv("CAKEB200_SMALL_A_SMEM") == nullptr) {
+    if (tma_ok && a.acc_stride <= 192 && option_get(OPT_SMALL_OPERANDS) != 1) {
         SmallArgs t = a;
         t.a_tmem = 1;
         t.a_col0 = 2 * t.acc_stride;

@@ -685,18 +685,18 @@ int make_map(CUtensorMap* map, const float* base, int rows, int K, int Kp, int b
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be a multiple of 16 bytes
 
-// Choices the selector may override per shape (0 = the rule below): tile width, band height of the
-// tile walk, K pieces per tile of the ragged last wave, chunk length of the accumulation.  Set through
-// cakeb200_set_option / the tuning cache; the rules are what an untuned shape gets.
+// Choices that can be overridden per shape (0 = the rule below): tile width, band height of the tile
+// walk, K pieces per tile of the ragged last wave, chunk length of the accumulation.  They come from
+// cakeb200_set_option and the tuning cache (resolve_tunables); the rules are what an untuned shape gets.
 struct Tunables {
     int bn = 0, band = 0, pieces = 0, chunk_kb = 0;
 };
-Tunables g_tune;
 
 // What applies to one product: an explicit override wins, then the tuning cache's entry for the
 // shape, then the rule (a field left 0).
 Tunables resolve_tunables(int M, int N, int K, int order) {
-    Tunables t = g_tune;
+    Tunables t;
+    t.bn = option_get(OPT_TILE_N); t.band = option_get(OPT_BAND); t.pieces = option_get(OPT_K_PIECES); t.chunk_kb = option_get(OPT_CHUNK_KB);
     int w = 0, b = 0, p = 0;
     if (tune_lookup(M, N, K, order, &w, &b, &p)) {
         if (!t.bn) t.bn = w;
@@ -1187,43 +1187,6 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 }
 
 }  // namespace cakeb200
-
-// ------------------------------------------------- options of the large-matrix kernel
-extern "C" int cakeb200_set_option(const char* name, int value) {
-    using namespace cakeb200;
-    if (!name || value < 0) {
-        set_error("cakeb200_set_option: null name or negative value");
-        return CAKEB200_ERR_ARG;
-    }
-    std::lock_guard<std::mutex> lock(g_plan_mutex);
-    if (!strcmp(name, "tile_n")) {
-        if (value != 0 && value != 128 && value != 256) {
-            set_error("cakeb200_set_option: tile_n is 0, 128 or 256");
-            return CAKEB200_ERR_ARG;
-        }
-        g_tune.bn = value;
-    } else if (!strcmp(name, "band")) {
-        g_tune.band = value;
-    } else if (!strcmp(name, "k_pieces")) {
-        g_tune.pieces = value;
-    } else if (!strcmp(name, "chunk_kb")) {
-        g_tune.chunk_kb = value;
-    } else {
-        set_error("cakeb200_set_option: unknown option '%s' (tile_n, band, k_pieces, chunk_kb)", name);
-        return CAKEB200_ERR_ARG;
-    }
-    return CAKEB200_OK;
-}
-
-extern "C" int cakeb200_get_option(const char* name) {
-    using namespace cakeb200;
-    if (!name) return -1;
-    if (!strcmp(name, "tile_n")) return g_tune.bn;
-    if (!strcmp(name, "band")) return g_tune.band;
-    if (!strcmp(name, "k_pieces")) return g_tune.pieces;
-    if (!strcmp(name, "chunk_kb")) return g_tune.chunk_kb;
-    return -1;
-}
 
 // ------------------------------------------------- self-test of the bounded wait
 //

@@ -133,7 +133,13 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
  *   "k_pieces" K ranges each tile of the ragged last wave is cut into (rule: a cost model);
  *   "chunk_kb" 32-deep slices of K accumulated in tensor memory before they are folded into the
  *              FP32 running sum (rule: 32, i.e. 1024 of K; a value >= K / 32 means one unbroken
- *              accumulation, whose truncation error grows with K).
+ *              accumulation, whose truncation error grows with K);
+ * and, so that tests can reach every code path of the other kernels:
+ *   "conv_route" 1 = im2col planes + the large-matrix kernel, 2 / 3 = the implicit kernel tiled by
+ *              whole rows of one image / by runs of 128 positions across images (rule: by geometry);
+ *   "small_operands" of the batched tensor-core kernel: 1 = A's split planes in shared memory
+ *              instead of tensor memory, 2 = operands read from global memory instead of by TMA;
+ *   "pack_scalar" 1 = pack / unpack move one element per thread instead of 16 bytes.
  * They take the place of the block sizes a caller of the reference forces with mcu / kcu / ncu
  * (reference include/cake.h:12-14, src/block_sizing.cpp:363-368) and of update_mr_nr
  * (src/block_sizing.cpp:78-83): on a GPU the blocks a caller may pin are the tile, the walk and

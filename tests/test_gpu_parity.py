@@ -277,14 +277,14 @@ def test_pack_sixteen_byte_path_bit_exact(cake, oracle):
             got = {}
             for mode in ("vector", "scalar"):
                 if mode == "scalar":
-                    os.environ["CAKEB200_PACK_SCALAR"] = "1"
+                    cake.set_option("pack_scalar", 1)
                 try:
                     Ap = cake.pack_A(A, M, K, p, x, cx); wa = cake.last_stats()["tile_k"]
                     Bp = cake.pack_B(B, K, N, p, x, cx); wb = cake.last_stats()["tile_k"]
                     Cp = cake.pack_C(C, M, N, p, x, cx); wc = cake.last_stats()["tile_k"]
                     back = (cake.unpack_A(Ap, M, K, p, x, cx), cake.unpack_B(Bp, K, N, p, x, cx), cake.unpack_C(Cp, M, N, p, x, cx))
                 finally:
-                    os.environ.pop("CAKEB200_PACK_SCALAR", None)
+                    cake.set_option("pack_scalar", 0)
                 got[mode] = (Ap, Bp, Cp)
                 if mode == "vector":
                     wide += (wa > 1) + (wb > 1) + (wc > 1)
@@ -387,12 +387,12 @@ def test_implicit_convolution_geometries(cake, oracle):
         assert st["kernel"] == cake.KERNEL_TF32X3
         assert (st["launches"] == 2) == implicit, (b, cin, H, W, cout, hf, wf, pad, st)
         # both tilings of the implicit kernel (whole rows of one image; runs of 128 positions across images)
-        for force in ("CAKEB200_CONV_ROWS", "CAKEB200_CONV_FLAT"):
-            os.environ[force] = "1"
+        for force in (2, 3):  # "conv_route": 2 = whole rows of one image, 3 = runs of 128 positions
+            cake.set_option("conv_route", force)
             try:
                 other = cake.cake_conv2d(x, w, 1, pad, kernel=cake.KERNEL_TF32X3)
             finally:
-                os.environ.pop(force, None)
+                cake.set_option("conv_route", 0)
             assert np.abs(other - out).max() <= 1e-4 * max(1.0, np.abs(out).max()), (force, b, cin, H, W, cout)
         ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(w).double(), padding=pad).numpy()
         assert out.shape == ref.shape
@@ -407,12 +407,12 @@ def test_implicit_convolution_geometries(cake, oracle):
     # the older route (im2col planes) must agree with the implicit one to the same tolerance
     x, w = oracle.normal((2, 40, 12, 12), 4, 0.1), oracle.normal((130, 40, 3, 3), 5, 0.1)
     a = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
-    os.environ["CAKEB200_CONV_PLANES"] = "1"
+    cake.set_option("conv_route", 1)
     try:
         b2 = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
         assert cake.last_stats()["launches"] == 3
     finally:
-        os.environ.pop("CAKEB200_CONV_PLANES", None)
+        cake.set_option("conv_route", 0)
     col = oracle.im2col(x, 3, 3, 1, 1)
     assert rel_err(a.transpose(1, 0, 2, 3).reshape(130, -1), b2.transpose(1, 0, 2, 3).reshape(130, -1), w.reshape(130, -1), col) <= TOL
 
@@ -434,10 +434,10 @@ def test_batched_small_on_tensor_cores(cake, oracle):
     for case, (batch, M, K, N) in enumerate(shapes):
         # the last case repeats the first with the producers reading global memory themselves instead of the TMA ring
         if case == len(shapes) - 1:
-            os.environ["CAKEB200_SMALL_DIRECT"] = "1"
+            cake.set_option("small_operands", 2)
         # ... and the one before it with the split A operand in shared memory instead of tensor memory
         if case == len(shapes) - 2:
-            os.environ["CAKEB200_SMALL_A_SMEM"] = "1"
+            cake.set_option("small_operands", 1)
         A, B = oracle.uniform((batch, M, K), 1), oracle.uniform((batch, K, N), 2)
         C = np.full((batch, M, N), np.nan, np.float32)
         cake.cake_sgemm_batched(A, B, C, kernel=cake.KERNEL_TF32X3)
@@ -450,8 +450,7 @@ def test_batched_small_on_tensor_cores(cake, oracle):
         ref64 = np.einsum("bmk,bkn->bmn", A.astype(np.float64), B.astype(np.float64))
         den = np.linalg.norm(A, axis=2)[:, :, None] * np.linalg.norm(B, axis=1)[:, None, :]
         assert (np.abs(C - ref64) / np.maximum(den, 1e-30)).max() <= TOL
-    os.environ.pop("CAKEB200_SMALL_DIRECT", None)
-    os.environ.pop("CAKEB200_SMALL_A_SMEM", None)
+    cake.set_option("small_operands", 0)
     # AUTO takes the tensor-core kernel for a large batch of well-filled tiles, FFMA for a handful of tiny ones
     A, B = oracle.uniform((300, 96, 96), 1), oracle.uniform((300, 96, 96), 2)
     cake.cake_sgemm_batched(A, B)
