@@ -706,15 +706,17 @@ Tunables resolve_tunables(int M, int N, int K, int order) {
     return t;
 }
 
-// Columns of C per tile.  256 halves the reads of A per flop and is what large products want; a product
-// with fewer 128 x 256 tiles than SMs leaves most of the machine to the K cut alone, and 128-wide tiles
-// then give twice the tiles to spread (measured: 2048^3 0.145 -> 0.117 ms, 1024^3 0.053 -> 0.048 ms;
-// 3000^3 and larger are faster with 256).
-inline int tile_width(int M, int N, int sm_count, const Tunables& t) {
+// Columns of C per tile.  256 halves the reads of A per flop and its MMAs run about 30 % better per
+// flop than 128-wide ones, so it is what large products want.  A shallow product with fewer 128 x 256
+// tiles than SMs leaves most of the machine to the K cut alone, which has little K to cut, and 128-wide
+// tiles then give twice the tiles to spread (measured: 2048^3 0.145 -> 0.117 ms, 1024^3 0.053 -> 0.048 ms;
+// 3000^3 and larger are faster with 256, and so is a deep product with few tiles, 1024 x 262144 x 1024:
+// 2.6 ms against 3.4 ms, because its K cut fills the machine by itself).
+inline int tile_width(int M, int N, int K, int sm_count, const Tunables& t) {
     if ((t.bn == 128 || t.bn == 256) && !(t.bn == 256 && N <= 128)) return t.bn;
     if (N <= 128) return 128;
     const long long wide_tiles = (long long) ((M + BM - 1) / BM) * ((N + 255) / 256);
-    return wide_tiles <= sm_count ? 128 : 256;
+    return (wide_tiles <= sm_count && K <= 4096) ? 128 : 256;
 }
 
 // Band height of the tile walk.  Tiles that run together should cover a patch of C with
@@ -1090,7 +1092,7 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
     DevicePlan* plan = nullptr;
     const Tunables tn = resolve_tunables(rows, N, K, order);
-    const int bn = tile_width(p.M, N, sm_count, tn);  // of the whole product, so that every band of rows uses one width
+    const int bn = tile_width(p.M, N, K, sm_count, tn);  // of the whole product, so that every band of rows uses one width
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
         int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, tn, stream, &plan);
         if (rc) return rc;
@@ -1117,7 +1119,7 @@ int tf32x3_make_planes(const float* mat, int rows, int K, int ld, bool transpose
 bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
     if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return false;
     const Tunables tn = resolve_tunables(M, N, K, order);
-    const int bn = tile_width(M, N, sm_count, tn), kblocks = (K + BK - 1) / BK;
+    const int bn = tile_width(M, N, K, sm_count, tn), kblocks = (K + BK - 1) / BK;
     const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     if (tiles >= sm_count) return false;
     const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, tn);
@@ -1141,7 +1143,7 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
     const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
-    const int bn = tile_width(g.M, g.N, sm_count, tn);
+    const int bn = tile_width(g.M, g.N, g.K, sm_count, tn);
     const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
