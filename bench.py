@@ -326,6 +326,14 @@ def gpu_arm(args):
             roofline["tf32_issue_rate"] = {"tflops": tf32_rate, "ms": tf32_ms, "third": tf32_rate / 3,
                                            "frac_of_third": achieved / (tf32_rate / 3),
                                            "how": "tcgen05.mma kind::tf32 128x256x8 issue-rate microbenchmark, measured"}
+            # The microbenchmark lasts 5 ms and runs at the maximum SM clock (its 1113-1116 TFLOP/s are 99 % of
+            # 148 SMs x 8192 flop/clock x 1.965 GHz, and ncu shows its tensor pipe 99.5 % active); the timed loop
+            # runs for seconds under the power cap at the sampled clock.  Scaled to that clock the pipe could
+            # have issued third x (sampled MHz / max MHz).
+            if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+                scale = clocks["sm_mhz"] / clocks["sm_max_mhz"]
+                roofline["tf32_issue_rate"]["third_at_sampled_clock"] = tf32_rate / 3 * scale
+                roofline["tf32_issue_rate"]["frac_at_sampled_clock"] = achieved / (tf32_rate / 3 * scale)
         line = {
             "metric": METRIC, "value": flops * args.steps / (ms_total * 1e-3) / 1e12, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
