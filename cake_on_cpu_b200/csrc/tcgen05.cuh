@@ -48,8 +48,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
 // barrier did not flip within WAIT_LIMIT_NS or another role already gave up.
+// `backoff_ns` > 0: once the quick polls have failed the thread sleeps that long between polls (for waits
+// that are expected to take many microseconds: a polling warp takes issue slots and power from the warps
+// that feed the tensor cores).
 __device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
-                                              int where, long long limit_ns) {
+                                              int where, long long limit_ns, unsigned backoff_ns = 0) {
     // short waits are the common case: poll a while before touching the (slow) global timer
 #pragma unroll 1
     for (int i = 0; i < 64; i++)
@@ -57,7 +60,8 @@ __device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, vol
     const unsigned long long t0 = global_ns();
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 1023) == 0) {
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if ((++spins & (backoff_ns ? 63 : 1023)) == 0) {
             if (*abort_flag) return false;
             if ((long long) (global_ns() - t0) > limit_ns) {
                 *abort_flag = 1;
