@@ -18,8 +18,9 @@
 //                    the persistent CTAs take tiles;
 //   * microkernel -> tcgen05.mma kind::tf32, 128 x BN x 8 per instruction.
 //
-// One CTA per SM, three warp groups: in the first, warp 0 issues TMA loads and warp 1 issues
-// the MMAs and owns the tensor-memory allocation; the eight warps of the other two drain accumulators
+// Two kernels share this file.  Both: one CTA per SM, warp 0 issues TMA loads, warp 1 issues the MMAs
+// and owns the tensor-memory allocation.  The plain kernel has four more warps that drain finished
+// accumulators; the chunked kernel has three warp groups, the eight warps of the last two drain accumulators
 // (tcgen05.ld) while the MMAs already fill the other accumulator buffer.
 //
 // Accumulation in chunks of K.  The tensor core adds into tensor memory with
@@ -38,11 +39,14 @@
 // kernel time, for chunks of 512 / 768 / 1024 / 1536 of K / one unbroken accumulation:
 //   3000^3: 3.3e-4 / 5.2e-4 / 7.3e-4 / 1.1e-3 / 2.5e-3,  0.282 / 0.271 / 0.270 / 0.265 / 0.263 ms
 //   4096^3: 4.4e-4 / 6.5e-4 / 9.2e-4 / 1.3e-3 / 3.6e-3,  0.594 / 0.568 / 0.557 / 0.555 / 0.541 ms
-//   8192^3 (64 rows sampled): 5.3e-4 / - / 1.1e-3 / - / 1.0e-2,  4.44 / - / 4.26 / - / 4.19 ms
+//   8192^3 (64 rows sampled): 5.3e-4 / - / 1.1e-3 / - / 1.0e-2,  4.44 / - / 4.26 / - / 4.19 ms alone,
+//   and in a loop of 60 products under the power cap 5.2 ms with chunks of 1024 against 4.6 ms plain
 // (the exact-FP32 FFMA kernel: 2.3e-4, 3.7e-4 and, against the reference's own result,
-// 9.5e-4 at 8192^3).  Rule: 1024 of K, which keeps every product up to 4096^3 below the
-// reference's 1e-3 for 2 to 3 % of the kernel time; the "chunk_kb" option sets it (8, i.e.
-// 256 of K, brings 8192^3 to 9.0e-4 against the reference, for 15 % of the kernel time).
+// 9.5e-4 at 8192^3).  Rule: chunks of 1024 of K up to K = 4096, which keeps those products below
+// the reference's 1e-3 for 2 to 3 % of the kernel time, and the plain kernel (one unbroken
+// accumulation) above, where no affordable chunk length reaches 1e-3 anyway; the "chunk_kb"
+// option forces a chunk length at any K (8, i.e. 256 of K, brings 8192^3 to 9.0e-4 against the
+// reference).
 #include <cuda.h>
 
 #include <stdlib.h>
@@ -63,7 +67,8 @@ using namespace ptx;
 constexpr int BM = 128;          // rows of C per tile = TMEM lanes
 constexpr int BK = 32;           // K per pipeline stage: 32 floats = one 128-byte swizzle row
 constexpr int UMMA_K = 8;        // K of one tcgen05.mma kind::tf32
-constexpr int NUM_THREADS = 384;   // warp group 0: TMA warp, MMA warp, two idle warps; groups 1 and 2: drain warps
+constexpr int NUM_THREADS = 192;           // plain kernel: TMA warp, MMA warp, four drain warps
+constexpr int CHUNKED_THREADS = 384;   // chunked kernel: warp group 0 = TMA warp, MMA warp, two idle warps; groups 1 and 2 = drain warps
 constexpr int EPI_WARPS = 8;      // two per quarter of the tensor-memory lanes, each taking half of the columns
 constexpr int CHUNK_KB = 32;      // default chunk: 32 slices of 32 = 1024 of K
 
@@ -74,8 +79,9 @@ struct Cfg {
     static constexpr int B_BYTES = BN * BK * 4;   // one plane of B per stage
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
-    static constexpr int EPI_BYTES = EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 patch per drain warp
+    static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;          // plain kernel: one 32 x 32 patch per drain warp
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
+    static constexpr int SMEM_BYTES_CHUNKED = SMEM_BYTES + (EPI_WARPS - 4) * 32 * 32 * 4;  // eight patches
 };
 
 // Work of one CTA: first whole tiles taken round-robin (tile = blockIdx.x + i * gridDim.x
@@ -131,9 +137,257 @@ __device__ __forceinline__ int piece_chunks(const WorkPiece& w, int chunk_kb) {
 
 // ------------------------------------------------------------------ the kernel
 
+// The plain kernel: every tile's (or piece's) K range is one unbroken accumulation in tensor memory.
+// Four drain warps, no running sums, 192 threads.  It is what runs when no K range is longer than a
+// chunk, and for deep products (K above 4096) under the default rule, where it is 5 to 12 % faster than
+// the chunked kernel below in a long loop under the power cap (8192^3, 60 products back to back on one
+// box: 4.58-4.65 ms per product against 4.77 ms for the chunked kernel with folding switched off and
+// 5.17-5.23 ms with chunks of 1024 of K).
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                    const Tf32x3Args args) {
+    using C_ = Cfg<BN>;
+    constexpr int STAGES = C_::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte alignment
+    uint8_t* tiles = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    uint64_t* bars = (uint64_t*) (tiles + STAGES * C_::STAGE_BYTES);
+    // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
+    uint32_t* tmem_slot = (uint32_t*) (bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor-memory allocation belongs to the MMA warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    WorkPiece w;
+
+    if (warp == 0) {
+        // ------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int it = 0; ok && work_piece(args, it, w); it++) {
+                int tm, tn;
+                tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
+                    if (!ok) break;
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
+                    tma_load_2d(base, &map_a_hi, kb * BK, tm * BM, full_bar(stage));
+                    tma_load_2d(base + C_::A_BYTES, &map_a_lo, kb * BK, tm * BM, full_bar(stage));
+                    tma_load_2d(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, tn * BN, full_bar(stage));
+                    tma_load_2d(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, tn * BN, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Gave up: let the loads already issued land before the CTA goes away.
+                // A stage's loads have landed once its full barrier completed the phase
+                // the producer last armed; poll each briefly (bounded).
+                const unsigned long long t0 = global_ns();
+                for (int s = 0; s < STAGES; s++) {
+                    const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+                    while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (; ok && work_piece(args, local, w); local++) {
+                const int kb0 = w.kb0, kb1 = w.kb1;
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
+                    const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
+                    const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
+                    const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
+                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                        accumulate = 1;
+                    }
+                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar(buf));  // accumulator complete
+            }
+        }
+    } else {
+        // ----------------------------------------------------------- epilogue
+        // tcgen05.ld hands each thread one row of the accumulator (32 columns per load), so
+        // storing from those registers would touch 32 different rows per instruction.  Every
+        // 32 x 32 chunk therefore goes through a swizzled shared-memory patch of the warp and
+        // comes back with eight lanes per row: a store instruction then covers 4 rows x 128
+        // contiguous bytes.
+        const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) quarter * 4096u;
+        const int sub_r = lane >> 3, sub_c = lane & 7;
+        const bool c_vec = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
+        const bool p_vec = (args.out_p % 4 == 0) && (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
+        int local = 0;
+        bool ok = true;
+        for (; ok && work_piece(args, local, w); local++) {
+            int tm, tn;
+            tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+            if (!ok) break;
+            tcgen05_fence_after();
+            const bool empty_range = w.kb0 >= w.kb1;  // a piece with no K range contributes zeros
+            const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
+            const int row0 = tm * BM + quarter * 32;
+            // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
+            // beyond the matrix are zeros computed from zero-filled operand tiles)
+            float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN : nullptr;
+            float v[32];
+            if (!empty_range) {
+                tmem_ld32(t_addr, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] = 0.0f;
+            }
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                if (!empty_range) tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                                 v[4 * j + 2], v[4 * j + 3]);
+                __syncwarp();
+                if (!empty_range) {
+                    if (c + 1 < BN / 32) {
+                        tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);  // lands while this chunk is stored
+                    } else {
+                        // the accumulator has been read out: hand the buffer back before the stores
+                        tcgen05_fence_before();
+                        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                    }
+                }
+                const int col = tn * BN + c * 32 + sub_c * 4;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = i * 4 + sub_r;
+                    float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
+                    const int row = row0 + r;
+                    if (args.bias != nullptr && slot == nullptr) {
+                        if (col < args.N) o.x += __ldg(args.bias + col);
+                        if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
+                        if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
+                        if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
+                    }
+                    if (slot != nullptr) {
+                        *reinterpret_cast<float4*>(slot + (long long) r * BN + c * 32 + sub_c * 4) = o;
+                    } else if (row < args.M && col < args.N) {
+                        if (args.out_p > 0) {
+                            // convolution output: columns are (image, position); rows are output channels
+                            const int img = col / args.out_p, pos = col - img * args.out_p;
+                            float* dst = args.C + (long long) img * args.out_image_stride + (long long) row * args.out_p + pos;
+                            if (p_vec && pos + 4 <= args.out_p && col + 4 <= args.N) {
+                                *reinterpret_cast<float4*>(dst) = o;
+                            } else {
+                                const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    const int cj = col + j;
+                                    if (cj < args.N) {
+                                        const int im = cj / args.out_p, ps = cj - im * args.out_p;
+                                        args.C[(long long) im * args.out_image_stride + (long long) row * args.out_p + ps] = e[j];
+                                    }
+                                }
+                            }
+                        } else {
+                            float* dst = args.C + (long long) row * args.ldc + col;
+                            if (c_vec && col + 4 <= args.N) {
+                                if (args.accumulate) {
+                                    const float4 old = *reinterpret_cast<const float4*>(dst);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *reinterpret_cast<float4*>(dst) = o;
+                            } else {
+                                const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
+                            }
+                        }
+                    }
+                }
+                __syncwarp();  // the patch is rewritten by the next chunk
+            }
+            if (empty_range) {
+                tcgen05_fence_before();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// The chunked kernel.
+template <int BN>
+__global__ void __launch_bounds__(CHUNKED_THREADS, 1)
+sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                     const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                     const Tf32x3Args args) {
     using C_ = Cfg<BN>;
@@ -737,7 +991,7 @@ int band_for(int order, int tiles_m, int tiles_n, const Tunables& t) {
 // cut get their pieces summed by reduce_pieces_kernel.  This is how the K-first schedule
 // keeps all cores busy on shapes with few output blocks (src/cake_sgemm_k_first.cpp:75-98).
 struct HostPlan {
-    int grid = 0, dp_tiles = 0, slots = 0;
+    int grid = 0, dp_tiles = 0, slots = 0, longest_kb = 0;  // longest_kb: slices of the longest K piece
     std::vector<int4> units;
     std::vector<int> cta_begin;
     std::vector<TilePieces> pieces;
@@ -779,6 +1033,7 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     p.grid = (int) std::min<long long>((long long) sm_count, std::max<long long>(G, (long long) R * s));
     p.slots = R * s;
     const int per = (kblocks + s - 1) / s;
+    p.longest_kb = per;
     std::vector<std::vector<int4>> per_cta(p.grid);
     for (int q = 0; q < s; q++)
         for (int r = 0; r < R; r++) {
@@ -813,7 +1068,7 @@ struct PlanKey {
 struct DevicePlan {
     PlanKey key = {};
     bool valid = false;
-    int grid = 0, dp_tiles = 0, slots = 0, num_pieces = 0;
+    int grid = 0, dp_tiles = 0, slots = 0, num_pieces = 0, longest_kb = 0;
     char* dev = nullptr;
     size_t dev_bytes = 0;
     const int4* units = nullptr;
@@ -882,7 +1137,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
                                      cudaMemcpyHostToDevice, stream));
     CAKE_CUDA_OK(cudaStreamSynchronize(stream));  // the host vectors die with this scope
     victim->key = key;
-    victim->grid = hp.grid; victim->dp_tiles = hp.dp_tiles; victim->slots = hp.slots;
+    victim->grid = hp.grid; victim->dp_tiles = hp.dp_tiles; victim->slots = hp.slots; victim->longest_kb = hp.longest_kb;
     victim->num_pieces = (int) hp.pieces.size();
     victim->units = hp.units.empty() ? nullptr : (const int4*) victim->dev;
     victim->cta_begin = (const int*) (victim->dev + units_b);
@@ -917,7 +1172,9 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
-    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : CHUNK_KB;
+    // Chunk length of the accumulation.  Rule: 1024 of K for products up to K = 4096 (the sizes the reference's
+    // own tests and driver run, which then stay below its 1e-3), one unbroken accumulation above.
+    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (g.K <= 4096 ? CHUNK_KB : 0x7fffffff);
     a.drain_backoff = 400;  // a chunk lasts tens of microseconds; measured +0.4 % at 8192^3 against plain polling
     a.order = g.order;
     a.band = band_for(g.order, a.tiles_m, a.tiles_n, tn);
@@ -939,7 +1196,20 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
         a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
         grid = (int) std::min<long long>(tiles, sm_count);
     }
-    CAKE_CUDA_OK(cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+    static const cudaError_t attr_plain =
+        cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+    static const cudaError_t attr_chunked = cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                                 Cfg<BN>::SMEM_BYTES_CHUNKED);
+    CAKE_CUDA_OK(attr_plain);
+    CAKE_CUDA_OK(attr_chunked);
+    // the chunked kernel only where some K range is longer than a chunk (whole tiles; pieces are shorter)
+    auto run = [&](const Tf32x3Args& args) {
+        const int longest = (plan && a.units && plan->dp_tiles == 0 && plan->longest_kb > 0) ? plan->longest_kb : args.kblocks;
+        if (args.chunk_kb < longest)
+            sgemm_tf32x3_chunked_kernel<BN><<<grid, CHUNKED_THREADS, Cfg<BN>::SMEM_BYTES_CHUNKED, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
+        else
+            sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
+    };
     // A very deep product with many tiles is run as several launches over ranges of K, each adding to C.
     // Within one launch the CTAs of a wave share their A and B panels through L2 only while they work on
     // nearby slices of K; over thousands of slices they drift apart and the panels come from DRAM once per
@@ -958,13 +1228,13 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
             a.kblocks = std::min(range_kb, total_kb - first);
             a.accumulate = (first > 0) ? 1 : g.accumulate;
             a.bias = (first > 0) ? nullptr : g.bias;
-            sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
+            run(a);
             CAKE_CUDA_OK(cudaGetLastError());
             if (launches) (*launches)++;
         }
         return CAKEB200_OK;
     }
-    sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
+    run(a);
     CAKE_CUDA_OK(cudaGetLastError());
     if (launches) (*launches)++;
     if (g.owners) {
