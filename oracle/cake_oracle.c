@@ -576,9 +576,11 @@ void oracle_sgemm_batched(const float* A, const float* B, float* C, int M, int N
                           M, N, K, p, c, ORACLE_NA, 0.0f, 0, 0, 0);
 }
 
-/* cake_sp_sgemm_haswell_6x16, src/kernels/haswell/sparse.cpp:7-131: for each
+/* cake_sp_sgemm_haswell_6x16, src/kernels/haswell/sparse.cpp:7-126: for each
  * stored column k of A (ascending), every nonzero a[m,k] issues
- * C[m,:] = fma(a, B[k,:], C[m,:]); zeros issue nothing. */
+ * C[m,:] = fma(a, B[k,:], C[m,:]); zeros issue nothing.  Pinned: bit-identical to that
+ * microkernel driven tile by tile over whole matrices (oracle/ref_sparse_driver.cpp,
+ * tests/test_oracle_vs_reference.py) and to its stored outputs (tests/golden/). */
 void oracle_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K) {
 #pragma omp parallel for schedule(static)
     for (int m = 0; m < M; m++) {
@@ -598,9 +600,10 @@ void oracle_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int
  * ascending order, and its microkernel cake_sgemv_haswell_8x8_col (:87-140) loads C,
  * issues c = fma(A[k*M + m], B[k], c) for k ascending and stores C.  Per output
  * element that is one chain of fused multiply-adds over k = 0 .. K-1 on top of the
- * value C held on entry; A is column-major (A[k*M + m]).  parity unpinned: the
- * example is a stand-alone program with its own main and is not part of the
- * reference library, so this restatement is checked against float64 only. */
+ * value C held on entry; A is column-major (A[k*M + m]).  Pinned: bit-identical to that
+ * microkernel driven eight rows at a time (oracle/ref_gemv_driver.cpp; the example is a
+ * stand-alone program, so only the microkernel is compiled, not its main), and to its
+ * stored outputs (tests/golden/). */
 void oracle_sgemv(const float* A, const float* B, float* C, int M, int K) {
 #pragma omp parallel for schedule(static)
     for (int m = 0; m < M; m++) {

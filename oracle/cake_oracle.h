@@ -91,7 +91,7 @@ void oracle_sgemm_batched(const float* A, const float* B, float* C, int M, int N
 void oracle_sp_sgemm(const float* A, const float* B, float* C, int M, int N, int K);
 
 /* C[m] += sum_k A[k*M + m] * B[k], one fused multiply-add chain per element over ascending k
- * (reference examples/cake_gemv.cpp:87-140, 424-489).  parity unpinned (see the .c file). */
+ * (reference examples/cake_gemv.cpp:87-140, 424-489); pinned against that microkernel. */
 void oracle_sgemv(const float* A, const float* B, float* C, int M, int K);
 
 /* seeded generators shared by tests and benches (counter based, stateless) */

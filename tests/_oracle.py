@@ -256,6 +256,41 @@ class Reference:
         N = B.shape[1]
         return self.L.ref_checker(_f(A), _f(B), _f(C), N, M, K)
 
+    GEMV_PATH = os.path.join(ORACLE_DIR, "_ref", "libcake_ref_gemv.so")
+
+    @classmethod
+    def gemv_available(cls):
+        return os.path.exists(cls.GEMV_PATH)
+
+    def sgemv(self, A_colmajor, x, y0=None):
+        """y0 + A x through the reference's microkernel cake_sgemv_haswell_8x8_col (examples/cake_gemv.cpp:87-140),
+        eight rows at a time (oracle/ref_gemv_driver.cpp); A is the (K, M) array with A[k, m]."""
+        if not hasattr(self, "_gemv"):
+            self._gemv = ctypes.CDLL(self.GEMV_PATH)
+            self._gemv.ref_sgemv.argtypes = [_fp, _fp, _fp, _c_int, _c_int]
+        K, M = A_colmajor.shape
+        y = np.zeros(M, np.float32) if y0 is None else np.array(y0, np.float32)
+        assert self._gemv.ref_sgemv(_f(A_colmajor), _f(x), _f(y), M, K) == 0
+        return y
+
+    SPARSE_PATH = os.path.join(ORACLE_DIR, "_ref", "libcake_ref_sparse.so")
+
+    @classmethod
+    def sparse_available(cls):
+        return os.path.exists(cls.SPARSE_PATH)
+
+    def sp_sgemm(self, A, B):
+        """C = A @ B through the reference's sparse microkernel cake_sp_sgemm_haswell_6x16
+        (src/kernels/haswell/sparse.cpp:7-126), one 6 x 16 tile at a time (oracle/ref_sparse_driver.cpp)."""
+        if not hasattr(self, "_sparse"):
+            self._sparse = ctypes.CDLL(self.SPARSE_PATH)
+            self._sparse.ref_sp_sgemm.argtypes = [_fp, _fp, _fp, _c_int, _c_int, _c_int]
+        M, K = A.shape
+        N = B.shape[1]
+        C = np.full((M, N), np.nan, np.float32)
+        assert self._sparse.ref_sp_sgemm(_f(A), _f(B), _f(C), M, N, K) == 0
+        return C
+
 
 def rel_err(C, C_ref, A, B):
     """max |C - C_ref| / (||A[m,:]||_2 * ||B[:,n]||_2), the parity gate of the SGEMM path."""

@@ -18,6 +18,9 @@ from _oracle import KMN, MKN, NKM, NA, Oracle, Reference  # noqa: E402
 SGEMM_CASES = [(1, 1, 1, 2), (10, 10, 10, 3), (96, 96, 96, 4), (111, 96, 77, 4), (96, 111, 10, 8),
                (10, 2111, 96, 5), (2111, 10, 7, 8), (111, 960, 33, 2), (37, 300, 211, 8)]
 PACK_CASES = [(111, 96, 77, 4), (10, 960, 20, 5), (960, 10, 7, 8)]
+# (M, K, N, nonzeros per thousand) for the sparse microkernel
+GEMV_CASES = [(37, 53), (1000, 700), (96, 2111), (13, 9)]
+SPARSE_CASES = [(37, 53, 29, 100), (100, 257, 130, 20), (111, 300, 211, 300), (96, 1030, 64, 10), (64, 96, 48, 0)]
 # block-dimension cases: edge sizes plus every shape of the benchmark configurations
 BLOCK_CASES = [(m, k, n, p) for m in (1, 10, 96, 111, 960, 2111) for k in (1, 96, 2111) for n in (10, 111, 960)
                for p in (2, 8)]
@@ -53,6 +56,13 @@ def main():
     sets = [[s, M, N, K, R.set_schedule(s, M, N, K)] for s in (KMN, NA) for M in (1, 100, 1000) for N in (1, 100, 1000)
             for K in (1, 100, 1000)]
     out["set_schedule"] = np.array(sets, dtype=np.int64)
+    # the reference's sparse microkernel, tile by tile (oracle/ref_sparse_driver.cpp): A = sparse stream (1, mask 3)
+    for (M, K, N, d) in SPARSE_CASES:
+        A, B = O.sparse((M, K), 1, 3, d / 1000.0), O.uniform((K, N), 2)
+        out["sparse_%d_%d_%d_%d" % (M, K, N, d)] = R.sp_sgemm(A, B)
+    # the matrix-vector microkernel of examples/cake_gemv.cpp (oracle/ref_gemv_driver.cpp): A (K, M) = stream 1
+    for (M, K) in GEMV_CASES:
+        out["gemv_%d_%d" % (M, K)] = R.sgemv(O.uniform((K, M), 1), O.uniform((K,), 2), O.uniform((M,), 3))
     # rand_init(srand(1)) head, examples/cake_conv.cpp:924 seeds this way
     out["rand_init_seed1"] = R.rand_init(1, 4, 8)
     path = os.path.join(HERE, "reference_golden.npz")

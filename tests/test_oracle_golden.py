@@ -63,6 +63,22 @@ def test_benchmark_shapes_derive_expected_schedules(oracle):
         assert oracle.block_dims(M, N, K, 8, NA)["sch"] == sch, (M, K, N)
 
 
+@pytest.mark.parametrize("key", _cases("sparse"))
+def test_sparse_bit_exact(oracle, key):
+    """The row-skipping restatement against stored outputs of the reference's sparse microkernel."""
+    M, K, N, d = (int(v) for v in key.split("_")[1:])
+    A, B = oracle.sparse((M, K), 1, 3, d / 1000.0), oracle.uniform((K, N), 2)
+    assert np.array_equal(oracle.sp_sgemm(A, B), GOLDEN[key])
+
+
+@pytest.mark.parametrize("key", _cases("gemv"))
+def test_matrix_vector_bit_exact(oracle, key):
+    """The matrix-vector restatement against stored outputs of the reference example's microkernel."""
+    M, K = (int(v) for v in key.split("_")[1:])
+    got = oracle.sgemv(oracle.uniform((K, M), 1), oracle.uniform((K,), 2), oracle.uniform((M,), 3))
+    assert np.array_equal(got, GOLDEN[key])
+
+
 def test_sparse_restatement_equals_dense_chain(oracle):
     # zeros contribute no operation: skipping them leaves the FMA chain of the others unchanged
     A = oracle.sparse((37, 53), 1, 3, 0.1)

@@ -84,3 +84,29 @@ def test_rectangular_benchmark_shapes_scaled_down(oracle, reference):
         Co, so = oracle.sgemm(A, B, 8, NA)
         Cr, _ = reference.sgemm(A, B, 8, NA)
         assert np.array_equal(Co, Cr)
+
+
+def test_sparse_restatement_equals_the_reference_microkernel(oracle, reference):
+    """oracle_sp_sgemm against the reference's own sparse microkernel (cake_sp_sgemm_haswell_6x16, the one sparse
+    routine the reference ships), driven tile by tile over whole matrices: bit for bit, at densities from empty to
+    dense, with ragged M (not a multiple of 6), N (not a multiple of 16) and K (not a multiple of 4)."""
+    if not reference.sparse_available():
+        pytest.skip("oracle/_ref/libcake_ref_sparse.so not built")
+    for (M, K, N, d) in [(6, 4, 16, 0.5), (37, 53, 29, 0.1), (100, 257, 130, 0.02), (13, 7, 5, 1.0), (64, 96, 48, 0.0),
+                         (111, 300, 211, 0.3), (7, 1, 17, 0.9), (96, 1030, 64, 0.01)]:
+        A = oracle.sparse((M, K), 1, 3, d) if d < 1.0 else oracle.uniform((M, K), 1)
+        B = oracle.uniform((K, N), 2)
+        assert np.array_equal(oracle.sp_sgemm(A, B), reference.sp_sgemm(A, B)), (M, K, N, d)
+
+
+def test_matrix_vector_restatement_equals_the_reference_microkernel(oracle, reference):
+    """oracle_sgemv against the microkernel of the reference's matrix-vector example (cake_sgemv_haswell_8x8_col),
+    bit for bit: ragged M (not a multiple of 8), K not a multiple of the kernel's unrolling, y added to."""
+    if not reference.gemv_available():
+        pytest.skip("oracle/_ref/libcake_ref_gemv.so not built")
+    for (M, K) in [(8, 8), (1, 1), (37, 53), (1000, 700), (96, 2111), (13, 9), (300, 4)]:
+        A = oracle.uniform((K, M), 1)
+        x = oracle.uniform((K,), 2)
+        y0 = oracle.uniform((M,), 3)
+        assert np.array_equal(oracle.sgemv(A, x, y0), reference.sgemv(A, x, y0)), (M, K)
+        assert np.array_equal(oracle.sgemv(A, x), reference.sgemv(A, x)), (M, K)
