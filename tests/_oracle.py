@@ -256,6 +256,23 @@ class Reference:
         N = B.shape[1]
         return self.L.ref_checker(_f(A), _f(B), _f(C), N, M, K)
 
+    IM2COL_PATH = os.path.join(ORACLE_DIR, "_ref", "libcake_ref_im2col.so")
+
+    @classmethod
+    def im2col_available(cls):
+        return os.path.exists(cls.IM2COL_PATH)
+
+    def im2col(self, x, hf, wf):
+        """im_2_col of the reference's convolution example (examples/cake_conv.cpp:1178-1213): one image
+        (cin, H, W), no padding, stride 1."""
+        if not hasattr(self, "_im2col"):
+            self._im2col = ctypes.CDLL(self.IM2COL_PATH)
+            self._im2col.ref_im_2_col.argtypes = [_fp, _fp] + [_c_int] * 5
+        cin, H, W = x.shape
+        col = np.full((cin * hf * wf, (H - hf + 1) * (W - wf + 1)), np.nan, np.float32)
+        assert self._im2col.ref_im_2_col(_f(x), _f(col), cin, H, W, hf, wf) == 0
+        return col
+
     GEMV_PATH = os.path.join(ORACLE_DIR, "_ref", "libcake_ref_gemv.so")
 
     @classmethod

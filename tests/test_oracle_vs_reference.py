@@ -110,3 +110,14 @@ def test_matrix_vector_restatement_equals_the_reference_microkernel(oracle, refe
         y0 = oracle.uniform((M,), 3)
         assert np.array_equal(oracle.sgemv(A, x, y0), reference.sgemv(A, x, y0)), (M, K)
         assert np.array_equal(oracle.sgemv(A, x), reference.sgemv(A, x)), (M, K)
+
+
+def test_im2col_restatement_equals_the_reference(oracle, reference):
+    """oracle_im2col against im_2_col of the reference's convolution example, for what the reference covers
+    (one image, no padding, stride 1); batch and padding are this build's extensions and are checked against
+    float64 convolutions elsewhere."""
+    if not reference.im2col_available():
+        pytest.skip("oracle/_ref/libcake_ref_im2col.so not built")
+    for (cin, H, W, hf, wf) in [(3, 7, 6, 3, 3), (8, 33, 33, 3, 3), (5, 9, 12, 1, 1), (2, 10, 8, 5, 3), (16, 14, 14, 3, 3)]:
+        x = oracle.normal((1, cin, H, W), 4, 0.1)
+        assert np.array_equal(oracle.im2col(x, hf, wf, 1, 0), reference.im2col(x[0], hf, wf)), (cin, H, W, hf, wf)
