@@ -1219,11 +1219,11 @@ int cakeb200_sp_sgemm(const float* A, const float* B, float* C, int M, int N, in
         if ((rc = ensure_scratch(st, sparse_scratch_bytes(M, K)))) return rc;
         if ((rc = sp_compact((const float*) oa.dev, M, K, st->scratch, st->status_word, s, &nnz, &g_stats.launches)))
             return rc;
-        // Skipping zeros pays only when almost everything is zero: the tensor cores multiply
-        // the whole matrix faster than the CUDA cores multiply 3 % of it (measured at 8192^3:
-        // dense 4.3 ms at any density; zero skipping 0.6 ms + 1.2 ms per percent of nonzeros).
+        // Skipping zeros pays only when almost everything is zero: the tensor cores multiply the whole
+        // matrix faster than the CUDA cores gather rows of B for 3.5 % of it (measured at 8192^3: dense
+        // 4.6 ms at any density; zero skipping 0.25 ms + 1.1 ms per percent of nonzeros).
         if (kernel == CAKEB200_KERNEL_AUTO && M >= 256 && N >= 256 && K >= 64 &&
-            (double) M * N * K >= (double) (1LL << 27) && (double) nnz > 0.025 * (double) M * (double) K)
+            (double) M * N * K >= (double) (1LL << 27) && (double) nnz > 0.035 * (double) M * (double) K)
             dense = true;
     }
     if (dense) {

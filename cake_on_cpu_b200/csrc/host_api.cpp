@@ -807,9 +807,9 @@ double cake_sp_sgemm(float* A, float* B, float* C, int M, int N, int K, int p, c
     (void) p; (void) cake_cntx;
     const double t0 = now_s();
     // without a hint the library counts the nonzeros and decides; a hint saves that decision
-    // (above ~2.5 % nonzeros the dense tensor-core product is faster than skipping zeros)
+    // (above ~3.5 % nonzeros the dense tensor-core product is faster than skipping zeros)
     const int kernel = density_hint <= 0 ? CAKEB200_KERNEL_AUTO
-                       : (density_hint > 0.025f && M >= 256 && N >= 256 && K >= 64) ? CAKEB200_KERNEL_TF32X3
+                       : (density_hint > 0.035f && M >= 256 && N >= 256 && K >= 64) ? CAKEB200_KERNEL_TF32X3
                                                                                      : CAKEB200_KERNEL_FFMA;
     if (cakeb200_sp_sgemm(A, B, C, M, N, K, kernel, nullptr)) return fail("cake_sp_sgemm");
     return now_s() - t0;

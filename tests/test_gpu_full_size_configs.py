@@ -79,7 +79,7 @@ def test_sparse_8192(cake, density):
     rows = np.random.default_rng(1).integers(0, n, 32)
     auto = cake.cake_sp_sgemm(A, B, kernel=cake.KERNEL_AUTO)
     picked = cake.last_stats()["kernel"]
-    assert picked == (cake.KERNEL_TF32X3 if density > 0.025 else cake.KERNEL_FFMA)
+    assert picked == (cake.KERNEL_TF32X3 if density > 0.035 else cake.KERNEL_FFMA)
     assert _sample_err(A, B, auto, rows) <= TOL
     dense = torch.empty((n, n), device="cuda")
     cake.cake_sgemm(A, B, dense)  # the dense path on the densified operand
