@@ -35,7 +35,7 @@ DeviceState* g_states[MAX_DEVICES] = {};
 
 namespace {
 std::atomic<int> g_options[OPT_COUNT];
-const char* const g_option_names[OPT_COUNT] = {"tile_n", "band", "k_pieces", "chunk_kb", "conv_route", "small_operands", "pack_scalar"};
+const char* const g_option_names[OPT_COUNT] = {"tile_n", "band", "k_pieces", "chunk_kb", "conv_route", "small_operands", "pack_scalar", "pair"};
 }  // namespace
 int option_get(int id) { return (id >= 0 && id < OPT_COUNT) ? g_options[id].load() : 0; }
 
@@ -565,7 +565,7 @@ int cakeb200_set_option(const char* name, int value) {
     for (int i = 0; i < OPT_COUNT; i++) {
         if (strcmp(name, g_option_names[i])) continue;
         if ((i == OPT_TILE_N && value != 0 && value != 128 && value != 256) || (i == OPT_CONV_ROUTE && value > 3) ||
-            (i == OPT_SMALL_OPERANDS && value > 2) || (i == OPT_PACK_SCALAR && value > 1)) {
+            (i == OPT_SMALL_OPERANDS && value > 2) || (i == OPT_PACK_SCALAR && value > 1) || (i == OPT_PAIR && value > 2)) {
             set_error("cakeb200_set_option: %d is not a value of '%s'", value, name);
             return CAKEB200_ERR_ARG;
         }

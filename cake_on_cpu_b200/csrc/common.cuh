@@ -97,7 +97,7 @@ int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int 
 // one CTA runs a bounded wait that must give up (sgemm_tf32x3.cu)
 int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream);
 // Process-wide overrides set through cakeb200_set_option (abi.cu); 0 = the library's own rule.
-enum Option { OPT_TILE_N, OPT_BAND, OPT_K_PIECES, OPT_CHUNK_KB, OPT_CONV_ROUTE, OPT_SMALL_OPERANDS, OPT_PACK_SCALAR, OPT_COUNT };
+enum Option { OPT_TILE_N, OPT_BAND, OPT_K_PIECES, OPT_CHUNK_KB, OPT_CONV_ROUTE, OPT_SMALL_OPERANDS, OPT_PACK_SCALAR, OPT_PAIR, OPT_COUNT };
 int option_get(int id);
 // issue rate of dense TF32 MMAs on every SM (peak_tf32.cu)
 int measure_tf32_peak(int* status_word, int sm_count, float ms_target, cudaStream_t stream, float* tflops, float* ms_out);

@@ -670,6 +670,226 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
     }
 }
 
+// ------------------------------------------------------------- the pair kernel
+//
+// Two CTAs of a cluster (the two SMs of one processor pair) work on one 256 x 256 tile of C with
+// tcgen05.mma.cta_group::2: each CTA stages its 128 rows of A and its 128 of the tile's 256 rows of B^T,
+// the MMAs issued by the even CTA read both halves of B (the odd CTA's half comes over the link between
+// the two SMs) and write 128 accumulator rows into each CTA's tensor memory.  Per MMA an SM then reads
+// 4 KB of A and 4 KB of B from its shared memory instead of 4 + 8, and a pipeline stage is 64 KB instead
+// of 96, which takes the 3xTF32 loop (three MMAs per 8 of K, all reading shared memory) off the
+// shared-memory bandwidth limit of the single-CTA kernel.  Whole tiles only, one unbroken accumulation,
+// plain row-major C: what the large products need.
+//
+// Hand-overs between the two CTAs:
+//   full[s]   (leader's)  : the leader's producer arms it for the bytes of BOTH CTAs; each CTA's loads
+//                           count their bytes on it;
+//   empty[s]  (each CTA's): the MMA commit arrives on both copies, each producer waits on its own;
+//   acc_full  (each CTA's): the commit after a tile's last MMA arrives on both copies;
+//   acc_empty (leader's)  : the four drain warps of each CTA arrive on it (eight arrivals).
+struct PairCfg {
+    static constexpr int BN = 256;                 // columns of C per tile (both CTAs see all of them)
+    static constexpr int HALF_N = BN / 2;          // rows of B^T staged by each CTA
+    static constexpr int STAGES = 3;
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = HALF_N * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // per CTA
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                         const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                         const Tf32x3Args args) {
+    using C_ = PairCfg;
+    constexpr int STAGES = C_::STAGES, BN = C_::BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    uint64_t* bars = (uint64_t*) (tiles + STAGES * C_::STAGE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*) (bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();       // 0 = leader
+    const int pair = (int) blockIdx.x >> 1, pairs = (int) gridDim.x >> 1;
+    const int tiles_total = args.tiles_m * args.tiles_n;   // tiles_m counts 256-row tiles here
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 8);  // four drain warps in each of the two CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both CTAs allocates (and later frees) the pair's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < tiles_total; t += pairs) {
+                int tm, tn;
+                tile_coords(t, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+                const int a_row = tm * 2 * BM + (int) rank * BM, b_row = tn * BN + (int) rank * C_::HALF_N;
+                for (int kb = args.kb_first; kb < args.kb_first + args.kblocks; kb++) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
+                    if (!ok) break;
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C_::STAGE_BYTES);
+                    tma_load_2d_pair(base, &map_a_hi, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_pair(base + C_::A_BYTES, &map_a_lo, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_pair(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, b_row, full_bar(stage));
+                    tma_load_2d_pair(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, b_row, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Gave up: loads already issued must land before either CTA goes away (they write this CTA's
+                // shared memory and count on the leader's barriers).  They take microseconds; the drain warps
+                // reach the final cluster barrier only after their own waits, this adds a fixed margin.
+                const unsigned long long t0 = global_ns();
+                while ((long long) (global_ns() - t0) < 200000LL) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(2 * BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = pair; ok && t < tiles_total; t += pairs, local++) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
+                uint32_t accumulate = 0;
+                for (int kb = 0; kb < args.kblocks; kb++) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
+                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
+                    const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
+                    const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
+                    const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
+                        umma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                        umma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                        umma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                        accumulate = 1;
+                    }
+                    umma_commit_pair(empty_bar(stage));  // both CTAs' stage is reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(acc_full_bar(buf));  // both CTAs' halves of the accumulator are complete
+            }
+        }
+    } else {
+        // ----------------------------------------------------------- drain warps (both CTAs, own 128 rows)
+        const int quarter = warp & 3;
+        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) quarter * 4096u;
+        const int sub_r = lane >> 3, sub_c = lane & 7;
+        const bool c_vec = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
+        int local = 0;
+        bool ok = true;
+        for (int t = pair; ok && t < tiles_total; t += pairs, local++) {
+            int tm, tn;
+            tile_coords(t, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
+            const int row0 = tm * 2 * BM + (int) rank * BM + quarter * 32;
+            float v[32];
+            tmem_ld32(t_addr, v);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                                 v[4 * j + 2], v[4 * j + 3]);
+                __syncwarp();
+                if (c + 1 < BN / 32) {
+                    tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);
+                } else {
+                    tcgen05_fence_before();
+                    if (lane == 0) mbar_arrive_leader(acc_empty_bar(buf));
+                }
+                const int col = tn * BN + c * 32 + sub_c * 4;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = i * 4 + sub_r;
+                    float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
+                    const int row = row0 + r;
+                    if (row >= args.M || col >= args.N) continue;
+                    if (args.bias != nullptr) {
+                        o.x += __ldg(args.bias + col);
+                        if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
+                        if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
+                        if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
+                    }
+                    float* dst = args.C + (long long) row * args.ldc + col;
+                    if (c_vec && col + 4 <= args.N) {
+                        if (args.accumulate) {
+                            const float4 old = *reinterpret_cast<const float4*>(dst);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = o;
+                    } else {
+                        const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    cluster_sync_all();  // neither CTA frees tensor memory or leaves while the other may still touch it
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
+                     : "memory");
+    }
+}
+
 // ------------------------------------------------------------- operand split
 
 
@@ -1151,10 +1371,90 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
 // bytes of partial-tile slots a product may need (an upper bound that does not depend on the plan)
 size_t partial_slot_bytes(int sm_count) { return (size_t) (4 * sm_count + 8) * BM * 256 * sizeof(float); }
 
+// Clusters of two CTAs of the pair kernel that the device runs at once (0: it cannot run them), per device.
+int pair_clusters() {
+    static std::mutex m;
+    static int cached[PLAN_DEVICES];  // 0 = not asked yet, -1 = unavailable
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PLAN_DEVICES) { cudaGetLastError(); return 0; }
+    std::lock_guard<std::mutex> lock(m);
+    if (cached[dev] == 0) {
+        cached[dev] = -1;
+        int sms = 0, n = 0;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms >= 2 &&
+            cudaFuncSetAttribute(sgemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) == cudaSuccess) {
+            cfg.gridDim = dim3((unsigned) (sms / 2 * 2));
+            if (cudaOccupancyMaxActiveClusters(&n, sgemm_tf32x3_pair_kernel, &cfg) == cudaSuccess && n > 0) cached[dev] = n;
+        }
+        cudaGetLastError();
+    }
+    return cached[dev] > 0 ? cached[dev] : 0;
+}
+
+// The product on pairs of SMs, 256 x 256 tiles, whole K per tile (ranges of K for very deep products).
+// Returns PAIR_NOT_APPLICABLE when the caller should go on with the single-CTA kernels.
+constexpr int PAIR_NOT_APPLICABLE = 1;
+int launch_pair(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, int* status_word, int sm_count,
+                cudaStream_t stream, int* launches, const Tunables& tn) {
+    const int mode = option_get(OPT_PAIR);  // 0 = rule, 1 = wherever it applies, 2 = never
+    if (mode == 2 || g.out_p != 0 || g.owners || g.M < 2 * BM || g.N < PairCfg::BN) return PAIR_NOT_APPLICABLE;
+    const int kblocks = (g.K + BK - 1) / BK;
+    const int chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (g.K <= 4096 ? CHUNK_KB : 0x7fffffff);
+    const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + PairCfg::BN - 1) / PairCfg::BN;
+    const long long tiles = (long long) tiles_m * tiles_n;
+    const int range_kb = (kblocks > 512 && tiles >= 2LL * sm_count) ? 256 : kblocks;
+    if (chunk_kb < range_kb) return PAIR_NOT_APPLICABLE;  // this product accumulates in chunks: the chunked kernel's job
+    const int clusters = pair_clusters();
+    if (clusters <= 0 || tiles > 0x7fffffffLL) return PAIR_NOT_APPLICABLE;
+    // Rule: the pair kernel takes whole tiles in waves of `clusters`, so it is used where the last wave is
+    // nearly full (the single-CTA kernels cut their ragged last wave along K instead); it gains 15 to 20 %.
+    const long long waves = (tiles + clusters - 1) / clusters;
+    if (mode == 0 && tiles * 100 < waves * clusters * 88) return PAIR_NOT_APPLICABLE;
+    const int Kp = padded_k(g.K);
+    alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    int rc;
+    if ((rc = make_map(&ma_hi, a_hi, g.M, g.K, Kp, BM))) return rc;
+    if ((rc = make_map(&ma_lo, a_lo, g.M, g.K, Kp, BM))) return rc;
+    if ((rc = make_map(&mb_hi, b_hi, g.N, g.K, Kp, PairCfg::HALF_N))) return rc;
+    if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, PairCfg::HALF_N))) return rc;
+    Tf32x3Args a = {};
+    a.C = g.C;
+    a.M = g.M; a.N = g.N; a.K = g.K;
+    a.ldc = g.ldc;
+    a.tiles_m = tiles_m; a.tiles_n = tiles_n;
+    a.dp_tiles = (int) tiles;
+    a.chunk_kb = 0x7fffffff;
+    a.order = g.order;
+    a.band = band_for(g.order, tiles_m, tiles_n, tn);
+    a.status_word = status_word;
+    const int grid = 2 * (int) std::min<long long>(tiles, clusters);
+    for (int first = 0; first < kblocks; first += range_kb) {
+        a.kb_first = first;
+        a.kblocks = std::min(range_kb, kblocks - first);
+        a.accumulate = (first > 0) ? 1 : g.accumulate;
+        a.bias = (first > 0) ? nullptr : g.bias;
+        sgemm_tf32x3_pair_kernel<<<grid, NUM_THREADS, PairCfg::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
+        CAKE_CUDA_OK(cudaGetLastError());
+        if (launches) (*launches)++;
+    }
+    return CAKEB200_OK;
+}
+
 // plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots)
 template <int BN>
 int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, DevicePlan* plan,
            int* status_word, int sm_count, cudaStream_t stream, int* launches, const Tunables& tn) {
+    if (BN == 256) {
+        const int prc = launch_pair(g, a_hi, a_lo, b_hi, b_lo, status_word, sm_count, stream, launches, tn);
+        if (prc != PAIR_NOT_APPLICABLE) return prc;
+    }
     const int Kp = padded_k(g.K);
     alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
