@@ -284,8 +284,10 @@ int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float*
         if ((rc = tf32x3_planes(M, N, K, st->scratch, st->scratch_bytes, &planes))) return rc;
     }
 
-    // bands of whole 128-row tiles; enough of them that the first and last are short
-    const int tiles = (M + 127) / 128;
+    // bands of whole tiles (128 rows, or 256 where the tensor-core kernel runs on pairs of SMs); enough of
+    // them that the first and last are short
+    const int tile_rows = (kernel == CAKEB200_KERNEL_TF32X3) ? tf32x3_tile_rows(M) : 128;
+    const int tiles = (M + tile_rows - 1) / tile_rows;
     const int bands = std::max(1, std::min(std::min(DeviceState::MAX_BANDS, 16), tiles / 2));
     CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
     CAKE_CUDA_OK(cudaEventRecord(st->fence[0], s));
@@ -302,11 +304,11 @@ int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float*
     if (kernel == CAKEB200_KERNEL_TF32X3) {
         if ((rc = tf32x3_split_B(dB, N, K, N, planes, s))) return rc;
         g_stats.launches++;
-        g_stats.tile_m = 128; g_stats.tile_n = N > 128 ? 256 : 128; g_stats.tile_k = 32;
+        g_stats.tile_m = tile_rows; g_stats.tile_n = N > 128 ? 256 : 128; g_stats.tile_k = 32;
     }
     for (int b = 0; b < bands; b++) {
-        const int r0 = (int) ((long long) tiles * b / bands) * 128;
-        const int r1 = (b == bands - 1) ? M : (int) ((long long) tiles * (b + 1) / bands) * 128;
+        const int r0 = (int) ((long long) tiles * b / bands) * tile_rows;
+        const int r1 = (b == bands - 1) ? M : (int) ((long long) tiles * (b + 1) / bands) * tile_rows;
         const int rows = r1 - r0;
         if (rows <= 0) continue;
         CAKE_CUDA_OK(cudaMemcpyAsync(dA + (size_t) r0 * K, A + (size_t) r0 * K, (size_t) rows * K * 4,

@@ -72,12 +72,24 @@ constexpr int CHUNKED_THREADS = 384;   // chunked kernel: warp group 0 = TMA war
 constexpr int EPI_WARPS = 8;      // two per quarter of the tensor-memory lanes, each taking half of the columns
 constexpr int CHUNK_KB = 32;      // default chunk: 32 slices of 32 = 1024 of K
 
-template <int BN>
+// PAIR: two CTAs of a cluster (the two SMs of one processor pair) work on one 256 x BN tile of C with
+// tcgen05.mma.cta_group::2.  Each CTA stages its 128 rows of A and its half of the tile's BN rows of B^T; the
+// MMAs, issued by the even CTA, read both halves of B (the other CTA's half comes over the link between
+// the two SMs) and write 128 accumulator rows into each CTA's tensor memory.  Per MMA an SM then reads
+// half as much of B from its shared memory and a pipeline stage shrinks from 96 KB to 64 KB (BN = 256),
+// which takes the 3xTF32 loop (three MMAs per 8 of K, all reading shared memory) off the shared-memory
+// bandwidth limit of the single-CTA form: 8192^3 kernel 4.12 -> 3.64 ms.
+// Hand-overs in a pair: the stage-full barriers are the leader's (armed for the bytes of both CTAs, both
+// CTAs' loads count on them); stage-empty and accumulator-full live in each CTA and the MMA commit arrives
+// on both copies; accumulator-empty is the leader's and the drain warps of both CTAs arrive on it.
+template <int BN, bool PAIR>
 struct Cfg {
-    static constexpr int STAGES = (BN == 256) ? 2 : 3;
-    static constexpr int A_BYTES = BM * BK * 4;   // one plane of A per stage
-    static constexpr int B_BYTES = BN * BK * 4;   // one plane of B per stage
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of B^T staged by one CTA
+    static constexpr int A_BYTES = BM * BK * 4;       // one plane of A per stage
+    static constexpr int B_BYTES = B_ROWS * BK * 4;   // one plane of B per stage
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int STAGES = STAGE_BYTES > 64 * 1024 ? 2 : (STAGE_BYTES > 48 * 1024 ? 3 : 4);
+    static constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of C per tile
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
     static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;          // plain kernel: one 32 x 32 patch per drain warp
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_BYTES;
@@ -90,7 +102,8 @@ struct Cfg {
 // kernel adds the slots of each tile up in a fixed order.
 struct Tf32x3Args {
     float* C;
-    float* partials;         // [slot][BM x BN]
+    float* partials;         // [slot][BM x BN]; in a pair the odd CTA's halves follow at slot + slot_count
+    int slot_count;
     const int4* units;       // {tile, first k-block, end k-block, slot or -1 = whole K, store to C}
     const int* cta_begin;    // units of CTA b are [cta_begin[b], cta_begin[b + 1])
     int dp_tiles;
@@ -114,8 +127,7 @@ struct WorkPiece {
 };
 
 // The it-th piece of this CTA; every role of the CTA walks the same sequence.
-__device__ __forceinline__ bool work_piece(const Tf32x3Args& a, int it, WorkPiece& w) {
-    const int g = (int) gridDim.x, b = (int) blockIdx.x;
+__device__ __forceinline__ bool work_piece(const Tf32x3Args& a, int it, WorkPiece& w, int b, int g) {
     const int whole = (b < a.dp_tiles) ? (a.dp_tiles - b + g - 1) / g : 0;
     if (it < whole) {
         w.tile = b + it * g; w.kb0 = a.kb_first; w.kb1 = a.kb_first + a.kblocks; w.slot = -1;
@@ -143,12 +155,12 @@ __device__ __forceinline__ int piece_chunks(const WorkPiece& w, int chunk_kb) {
 // the chunked kernel below in a long loop under the power cap (8192^3, 60 products back to back on one
 // box: 4.58-4.65 ms per product against 4.77 ms for the chunked kernel with folding switched off and
 // 5.17-5.23 ms with chunks of 1024 of K).
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                     const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                     const Tf32x3Args args) {
-    using C_ = Cfg<BN>;
+    using C_ = Cfg<BN, PAIR>;
     constexpr int STAGES = C_::STAGES;
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
@@ -159,6 +171,9 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
     volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // within the pair; rank 0 ("leader") issues the MMAs
+    // position among the units that take tiles: CTAs, or pairs of CTAs
+    const int cta = PAIR ? (int) blockIdx.x >> 1 : (int) blockIdx.x, ctas = PAIR ? (int) gridDim.x >> 1 : (int) gridDim.x;
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -172,19 +187,14 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full_bar(b), 1);
-            mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+            mbar_init(acc_empty_bar(b), PAIR ? 8 : 4);  // one arrival per drain warp (of both CTAs of a pair)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor-memory allocation belongs to the MMA warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 1) tmem_alloc<PAIR>(smem_u32(tmem_slot), (uint32_t) C_::TMEM_COLS);  // belongs to the MMA warp (of both CTAs of a pair)
     tcgen05_fence_before();
-    __syncthreads();
+    sync_all_t<PAIR>();  // in a pair: both CTAs' barriers exist before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -196,18 +206,19 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int it = 0; ok && work_piece(args, it, w); it++) {
+            for (int it = 0; ok && work_piece(args, it, w, cta, ctas); it++) {
                 int tm, tn;
                 tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+                const int a_row = tm * C_::TILE_M + (int) rank * BM, b_row = tn * BN + (int) rank * C_::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; kb++) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
                     if (!ok) break;
                     const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
-                    mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
-                    tma_load_2d(base, &map_a_hi, kb * BK, tm * BM, full_bar(stage));
-                    tma_load_2d(base + C_::A_BYTES, &map_a_lo, kb * BK, tm * BM, full_bar(stage));
-                    tma_load_2d(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, tn * BN, full_bar(stage));
-                    tma_load_2d(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, tn * BN, full_bar(stage));
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), (PAIR ? 2 : 1) * C_::STAGE_BYTES);
+                    tma_load_2d_t<PAIR>(base, &map_a_hi, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + C_::A_BYTES, &map_a_lo, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, b_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, b_row, full_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -216,21 +227,26 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 // A stage's loads have landed once its full barrier completed the phase
                 // the producer last armed; poll each briefly (bounded).
                 const unsigned long long t0 = global_ns();
-                for (int s = 0; s < STAGES; s++) {
-                    const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
-                    while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                if (rank == 0) {
+                    for (int s = 0; s < STAGES; s++) {
+                        const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+                        while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                    }
+                } else {
+                    // the odd CTA of a pair has no barrier of its own to poll: a fixed margin (loads take microseconds)
+                    while ((long long) (global_ns() - t0) < 200000LL) __nanosleep(1000);
                 }
             }
         }
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(C_::TILE_M, BN);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (; ok && work_piece(args, local, w); local++) {
+            for (; ok && work_piece(args, local, w, cta, ctas); local++) {
                 const int kb0 = w.kb0, kb1 = w.kb1;
                 const int buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
@@ -252,16 +268,16 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
                         const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
-                        umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
-                        umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
-                        umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                        umma_tf32_t<PAIR>(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                        umma_tf32_t<PAIR>(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                        umma_tf32_t<PAIR>(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
                         accumulate = 1;
                     }
-                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                    umma_commit_t<PAIR>(empty_bar(stage));  // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit(acc_full_bar(buf));  // accumulator complete
+                umma_commit_t<PAIR>(acc_full_bar(buf));  // accumulator complete
             }
         }
     } else {
@@ -278,7 +294,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         const bool p_vec = (args.out_p % 4 == 0) && (args.out_image_stride % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
         int local = 0;
         bool ok = true;
-        for (; ok && work_piece(args, local, w); local++) {
+        for (; ok && work_piece(args, local, w, cta, ctas); local++) {
             int tm, tn;
             tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
             const int buf = local & 1;
@@ -289,10 +305,10 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             tcgen05_fence_after();
             const bool empty_range = w.kb0 >= w.kb1;  // a piece with no K range contributes zeros
             const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
-            const int row0 = tm * BM + quarter * 32;
+            const int row0 = tm * C_::TILE_M + (int) rank * BM + quarter * 32;
             // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
             // beyond the matrix are zeros computed from zero-filled operand tiles)
-            float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN : nullptr;
+            float* slot = (w.slot >= 0) ? args.partials + ((long long) (w.slot + (int) rank * args.slot_count) * BM + quarter * 32) * BN : nullptr;
             float v[32];
             if (!empty_range) {
                 tmem_ld32(t_addr, v);
@@ -314,7 +330,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                     } else {
                         // the accumulator has been read out: hand the buffer back before the stores
                         tcgen05_fence_before();
-                        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                        if (lane == 0) mbar_arrive_t<PAIR>(acc_empty_bar(buf));
                     }
                 }
                 const int col = tn * BN + c * 32 + sub_c * 4;
@@ -370,27 +386,26 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             }
             if (empty_range) {
                 tcgen05_fence_before();
-                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                if (lane == 0) mbar_arrive_t<PAIR>(acc_empty_bar(buf));
             }
         }
     }
 
     tcgen05_fence_before();
-    __syncthreads();
+    sync_all_t<PAIR>();  // in a pair: neither CTA frees tensor memory or leaves while the other may still touch it
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
+        tmem_free<PAIR>(tmem_base, (uint32_t) C_::TMEM_COLS);
     }
 }
 
 // The chunked kernel.
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(CHUNKED_THREADS, 1)
 sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                     const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                     const Tf32x3Args args) {
-    using C_ = Cfg<BN>;
+    using C_ = Cfg<BN, PAIR>;
     constexpr int STAGES = C_::STAGES;
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
@@ -401,6 +416,9 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
     volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // within the pair; rank 0 ("leader") issues the MMAs
+    // position among the units that take tiles: CTAs, or pairs of CTAs
+    const int cta = PAIR ? (int) blockIdx.x >> 1 : (int) blockIdx.x, ctas = PAIR ? (int) gridDim.x >> 1 : (int) gridDim.x;
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -414,19 +432,14 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full_bar(b), 1);
-            mbar_init(acc_empty_bar(b), EPI_WARPS);  // one arrival per drain warp
+            mbar_init(acc_empty_bar(b), (PAIR ? 2 : 1) * EPI_WARPS);  // one arrival per drain warp (of both CTAs of a pair)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor-memory allocation belongs to the MMA warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 1) tmem_alloc<PAIR>(smem_u32(tmem_slot), (uint32_t) C_::TMEM_COLS);  // belongs to the MMA warp (of both CTAs of a pair)
     tcgen05_fence_before();
-    __syncthreads();
+    sync_all_t<PAIR>();  // in a pair: both CTAs' barriers exist before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -443,18 +456,19 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int it = 0; ok && work_piece(args, it, w); it++) {
+            for (int it = 0; ok && work_piece(args, it, w, cta, ctas); it++) {
                 int tm, tn;
                 tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
+                const int a_row = tm * C_::TILE_M + (int) rank * BM, b_row = tn * BN + (int) rank * C_::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; kb++) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
                     if (!ok) break;
                     const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
-                    mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
-                    tma_load_2d(base, &map_a_hi, kb * BK, tm * BM, full_bar(stage));
-                    tma_load_2d(base + C_::A_BYTES, &map_a_lo, kb * BK, tm * BM, full_bar(stage));
-                    tma_load_2d(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, tn * BN, full_bar(stage));
-                    tma_load_2d(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, tn * BN, full_bar(stage));
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), (PAIR ? 2 : 1) * C_::STAGE_BYTES);
+                    tma_load_2d_t<PAIR>(base, &map_a_hi, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + C_::A_BYTES, &map_a_lo, kb * BK, a_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, b_row, full_bar(stage));
+                    tma_load_2d_t<PAIR>(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, b_row, full_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -463,21 +477,26 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                 // A stage's loads have landed once its full barrier completed the phase
                 // the producer last armed; poll each briefly (bounded).
                 const unsigned long long t0 = global_ns();
-                for (int s = 0; s < STAGES; s++) {
-                    const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
-                    while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                if (rank == 0) {
+                    for (int s = 0; s < STAGES; s++) {
+                        const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+                        while (!mbar_try_wait(full_bar(s), armed) && (long long) (global_ns() - t0) < 20000000LL) {}
+                    }
+                } else {
+                    // the odd CTA of a pair has no barrier of its own to poll: a fixed margin (loads take microseconds)
+                    while ((long long) (global_ns() - t0) < 200000LL) __nanosleep(1000);
                 }
             }
         }
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(BM, BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(C_::TILE_M, BN);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0, handover = 0;
             bool ok = true;
-            for (; ok && work_piece(args, local, w); local++) {
+            for (; ok && work_piece(args, local, w, cta, ctas); local++) {
                 const int chunks = piece_chunks(w, args.chunk_kb);
                 for (int ci = 0; ok && ci < chunks; ci++, handover++) {
                     const int kb0 = w.kb0 + ci * args.chunk_kb, kb1 = min(w.kb1, kb0 + args.chunk_kb);
@@ -501,16 +520,16 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                         for (int k = 0; k < BK / UMMA_K; k++) {
                             // advance 8 floats = 32 bytes inside the 128-byte swizzle row (16-byte units)
                             const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
-                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
-                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
-                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+                            umma_tf32_t<PAIR>(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
+                            umma_tf32_t<PAIR>(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+                            umma_tf32_t<PAIR>(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
                             accumulate = 1;
                         }
-                        umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                        umma_commit_t<PAIR>(empty_bar(stage));  // stage reusable once these MMAs have read it
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                     if (!ok) break;
-                    umma_commit(acc_full_bar(buf));  // chunk complete
+                    umma_commit_t<PAIR>(acc_full_bar(buf));  // chunk complete
                 }
             }
         }
@@ -536,7 +555,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         float sum[COLS];
         int local = 0, handover = 0;
         bool ok = true;
-        for (; ok && work_piece(args, local, w); local++) {
+        for (; ok && work_piece(args, local, w, cta, ctas); local++) {
             int tm, tn;
             tile_coords(w.tile, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
             const int chunks = piece_chunks(w, args.chunk_kb);
@@ -567,14 +586,14 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                         }
                     }
                     tcgen05_fence_before();
-                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                    if (lane == 0) mbar_arrive_t<PAIR>(acc_empty_bar(buf));
                     continue;
                 }
                 // last chunk of the piece: out it goes
-                const int row0 = tm * BM + quarter * 32;
+                const int row0 = tm * C_::TILE_M + (int) rank * BM + quarter * 32;
                 // a piece of K: the whole accumulator goes to its slot, unclipped (rows and columns
                 // beyond the matrix are zeros computed from zero-filled operand tiles)
-                float* slot = (w.slot >= 0) ? args.partials + ((long long) w.slot * BM + quarter * 32) * BN + half * COLS : nullptr;
+                float* slot = (w.slot >= 0) ? args.partials + ((long long) (w.slot + (int) rank * args.slot_count) * BM + quarter * 32) * BN + half * COLS : nullptr;
                 if (!empty_range) {
                     tmem_ld32(t_addr, v);
                 } else {
@@ -599,7 +618,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                         } else {
                             // the accumulator has been read out: hand the buffer back before the stores
                             tcgen05_fence_before();
-                            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                            if (lane == 0) mbar_arrive_t<PAIR>(acc_empty_bar(buf));
                         }
                     }
                     const int col = tn * BN + half * COLS + c * 32 + sub_c * 4;
@@ -655,238 +674,17 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                 }
                 if (empty_range) {
                     tcgen05_fence_before();
-                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                    if (lane == 0) mbar_arrive_t<PAIR>(acc_empty_bar(buf));
                 }
             }
         }
     }
 
     tcgen05_fence_before();
-    __syncthreads();
+    sync_all_t<PAIR>();  // in a pair: neither CTA frees tensor memory or leaves while the other may still touch it
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
-    }
-}
-
-// ------------------------------------------------------------- the pair kernel
-//
-// Two CTAs of a cluster (the two SMs of one processor pair) work on one 256 x 256 tile of C with
-// tcgen05.mma.cta_group::2: each CTA stages its 128 rows of A and its 128 of the tile's 256 rows of B^T,
-// the MMAs issued by the even CTA read both halves of B (the odd CTA's half comes over the link between
-// the two SMs) and write 128 accumulator rows into each CTA's tensor memory.  Per MMA an SM then reads
-// 4 KB of A and 4 KB of B from its shared memory instead of 4 + 8, and a pipeline stage is 64 KB instead
-// of 96, which takes the 3xTF32 loop (three MMAs per 8 of K, all reading shared memory) off the
-// shared-memory bandwidth limit of the single-CTA kernel.  Whole tiles only, one unbroken accumulation,
-// plain row-major C: what the large products need.
-//
-// Hand-overs between the two CTAs:
-//   full[s]   (leader's)  : the leader's producer arms it for the bytes of BOTH CTAs; each CTA's loads
-//                           count their bytes on it;
-//   empty[s]  (each CTA's): the MMA commit arrives on both copies, each producer waits on its own;
-//   acc_full  (each CTA's): the commit after a tile's last MMA arrives on both copies;
-//   acc_empty (leader's)  : the four drain warps of each CTA arrive on it (eight arrivals).
-struct PairCfg {
-    static constexpr int BN = 256;                 // columns of C per tile (both CTAs see all of them)
-    static constexpr int HALF_N = BN / 2;          // rows of B^T staged by each CTA
-    static constexpr int STAGES = 3;
-    static constexpr int A_BYTES = BM * BK * 4;
-    static constexpr int B_BYTES = HALF_N * BK * 4;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // per CTA
-    static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int EPI_BYTES = 4 * 32 * 32 * 4;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
-};
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-sgemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                         const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                         const Tf32x3Args args) {
-    using C_ = PairCfg;
-    constexpr int STAGES = C_::STAGES, BN = C_::BN;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* tiles = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
-    uint64_t* bars = (uint64_t*) (tiles + STAGES * C_::STAGE_BYTES);
-    uint32_t* tmem_slot = (uint32_t*) (bars + 2 * STAGES + 4);
-    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();       // 0 = leader
-    const int pair = (int) blockIdx.x >> 1, pairs = (int) gridDim.x >> 1;
-    const int tiles_total = args.tiles_m * args.tiles_n;   // tiles_m counts 256-row tiles here
-    const uint32_t bar0 = smem_u32(bars);
-    auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
-        }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(acc_full_bar(b), 1);
-            mbar_init(acc_empty_bar(b), 8);  // four drain warps in each of the two CTAs
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {  // the same warp of both CTAs allocates (and later frees) the pair's tensor memory
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tcgen05_fence_before();
-    cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them
-    tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ------------------------------------------------------- TMA producer (both CTAs)
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = pair; ok && t < tiles_total; t += pairs) {
-                int tm, tn;
-                tile_coords(t, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
-                const int a_row = tm * 2 * BM + (int) rank * BM, b_row = tn * BN + (int) rank * C_::HALF_N;
-                for (int kb = args.kb_first; kb < args.kb_first + args.kblocks; kb++) {
-                    ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status_word, 100 + stage);
-                    if (!ok) break;
-                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C_::STAGE_BYTES);
-                    tma_load_2d_pair(base, &map_a_hi, kb * BK, a_row, full_bar(stage));
-                    tma_load_2d_pair(base + C_::A_BYTES, &map_a_lo, kb * BK, a_row, full_bar(stage));
-                    tma_load_2d_pair(base + 2 * C_::A_BYTES, &map_b_hi, kb * BK, b_row, full_bar(stage));
-                    tma_load_2d_pair(base + 2 * C_::A_BYTES + C_::B_BYTES, &map_b_lo, kb * BK, b_row, full_bar(stage));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                }
-            }
-            if (!ok) {
-                // Gave up: loads already issued must land before either CTA goes away (they write this CTA's
-                // shared memory and count on the leader's barriers).  They take microseconds; the drain warps
-                // reach the final cluster barrier only after their own waits, this adds a fixed margin.
-                const unsigned long long t0 = global_ns();
-                while ((long long) (global_ns() - t0) < 200000LL) __nanosleep(1000);
-            }
-        }
-    } else if (warp == 1) {
-        // --------------------------------------------------------- MMA issuer (leader only)
-        if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(2 * BM, BN);
-            int stage = 0;
-            uint32_t phase = 0;
-            int local = 0;
-            bool ok = true;
-            for (int t = pair; ok && t < tiles_total; t += pairs, local++) {
-                const int buf = local & 1;
-                const uint32_t acc_phase = (local >> 1) & 1;
-                ok = mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, abort_flag, args.status_word, 200 + buf);
-                if (!ok) break;
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t) (buf * BN);
-                uint32_t accumulate = 0;
-                for (int kb = 0; kb < args.kblocks; kb++) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
-                    const uint64_t a_hi = make_kmajor_sw128_desc(base);
-                    const uint64_t a_lo = make_kmajor_sw128_desc(base + C_::A_BYTES);
-                    const uint64_t b_hi = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES);
-                    const uint64_t b_lo = make_kmajor_sw128_desc(base + 2 * C_::A_BYTES + C_::B_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        const uint64_t adv = (uint64_t) (k * UMMA_K * 4 >> 4);
-                        umma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, accumulate);
-                        umma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
-                        umma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
-                        accumulate = 1;
-                    }
-                    umma_commit_pair(empty_bar(stage));  // both CTAs' stage is reusable once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                }
-                if (!ok) break;
-                umma_commit_pair(acc_full_bar(buf));  // both CTAs' halves of the accumulator are complete
-            }
-        }
-    } else {
-        // ----------------------------------------------------------- drain warps (both CTAs, own 128 rows)
-        const int quarter = warp & 3;
-        const uint32_t patch = smem_u32(tiles + STAGES * C_::STAGE_BYTES + 256) + (uint32_t) quarter * 4096u;
-        const int sub_r = lane >> 3, sub_c = lane & 7;
-        const bool c_vec = (args.ldc % 4 == 0) && (((uintptr_t) args.C) % 16 == 0);
-        int local = 0;
-        bool ok = true;
-        for (int t = pair; ok && t < tiles_total; t += pairs, local++) {
-            int tm, tn;
-            tile_coords(t, args.tiles_m, args.tiles_n, args.order, args.band, tm, tn);
-            const int buf = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
-            ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tcgen05_fence_after();
-            const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
-            const int row0 = tm * 2 * BM + (int) rank * BM + quarter * 32;
-            float v[32];
-            tmem_ld32(t_addr, v);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    st_shared_v4(patch + (uint32_t) lane * 128u + (uint32_t) ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
-                                 v[4 * j + 2], v[4 * j + 3]);
-                __syncwarp();
-                if (c + 1 < BN / 32) {
-                    tmem_ld32(t_addr + (uint32_t) ((c + 1) * 32), v);
-                } else {
-                    tcgen05_fence_before();
-                    if (lane == 0) mbar_arrive_leader(acc_empty_bar(buf));
-                }
-                const int col = tn * BN + c * 32 + sub_c * 4;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int r = i * 4 + sub_r;
-                    float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
-                    const int row = row0 + r;
-                    if (row >= args.M || col >= args.N) continue;
-                    if (args.bias != nullptr) {
-                        o.x += __ldg(args.bias + col);
-                        if (col + 1 < args.N) o.y += __ldg(args.bias + col + 1);
-                        if (col + 2 < args.N) o.z += __ldg(args.bias + col + 2);
-                        if (col + 3 < args.N) o.w += __ldg(args.bias + col + 3);
-                    }
-                    float* dst = args.C + (long long) row * args.ldc + col;
-                    if (c_vec && col + 4 <= args.N) {
-                        if (args.accumulate) {
-                            const float4 old = *reinterpret_cast<const float4*>(dst);
-                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                        }
-                        *reinterpret_cast<float4*>(dst) = o;
-                    } else {
-                        const float e[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                        for (int j = 0; j < 4; j++)
-                            if (col + j < args.N) dst[j] = args.accumulate ? dst[j] + e[j] : e[j];
-                    }
-                }
-                __syncwarp();
-            }
-        }
-    }
-
-    tcgen05_fence_before();
-    cluster_sync_all();  // neither CTA frees tensor memory or leaves while the other may still touch it
-    if (warp == 1) {
-        tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t) C_::TMEM_COLS)
-                     : "memory");
+        tmem_free<PAIR>(tmem_base, (uint32_t) C_::TMEM_COLS);
     }
 }
 
@@ -1217,7 +1015,9 @@ struct HostPlan {
     std::vector<TilePieces> pieces;
 };
 
-HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, const Tunables& tn) {
+// `sm_count` is the number of units that take tiles: SMs, or pairs of SMs (`pair`, whose tiles are 256 rows
+// high and whose partial tiles are two 128-row halves, the odd CTA's `slots` further on).
+HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, const Tunables& tn, bool pair) {
     HostPlan p;
     const int band = band_for(order, tiles_m, tiles_n, tn);
     const long long T = (long long) tiles_m * tiles_n;
@@ -1235,7 +1035,7 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     const int R = (int) (T % sm_count);
     if (R == 0 || kblocks < 16) return p;
     const int s_max = std::min(std::min(32, kblocks / 8), std::max(1, (4 * sm_count) / R));
-    const double tile_us = 1.17 * kblocks, slot_us = 0.09, fixed_us = 8.0;
+    const double tile_us = 1.17 * kblocks, slot_us = pair ? 0.18 : 0.09, fixed_us = 8.0;
     int best_s = 1;
     double best = tile_us;
     // (Pieces of very different lengths were timed on 1024 x 262144 x 1024, 32 tiles: 4, 9 and 18 pieces per
@@ -1245,7 +1045,7 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
         const double cost = tile_us * rounds / s + slot_us * R * s + fixed_us;
         if (cost < best * 0.97) { best = cost; best_s = s; }
     }
-    if (tn.pieces >= 1 && (long long) tn.pieces * R <= 4LL * sm_count + 8 && tn.pieces <= kblocks)
+    if (tn.pieces >= 1 && (long long) tn.pieces * R <= 4LL * sm_count + 4 && tn.pieces <= kblocks)
         best_s = tn.pieces;  // the selector's choice for this shape
     if (best_s == 1) return p;
     const int s = best_s;
@@ -1270,7 +1070,12 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
     for (int r = 0; r < R; r++) {
         int tm, tn;
         tile_coords(p.dp_tiles + r, tiles_m, tiles_n, order, band, tm, tn);
-        p.pieces.push_back({tm, tn, r * s, s});
+        if (pair) {
+            p.pieces.push_back({2 * tm, tn, r * s, s});
+            p.pieces.push_back({2 * tm + 1, tn, p.slots + r * s, s});
+        } else {
+            p.pieces.push_back({tm, tn, r * s, s});
+        }
     }
     return p;
 }
@@ -1279,10 +1084,10 @@ HostPlan build_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_cou
 // the last kernel that read it has finished (event), so asynchronous callers may queue
 // many products ahead.
 struct PlanKey {
-    int tiles_m, tiles_n, kblocks, order, sm_count, bn, band, pieces;  // band, pieces: the overrides in force (0 = rule)
+    int tiles_m, tiles_n, kblocks, order, sm_count, bn, band, pieces, pair;  // band, pieces: the overrides in force (0 = rule)
     bool operator==(const PlanKey& o) const {
         return tiles_m == o.tiles_m && tiles_n == o.tiles_n && kblocks == o.kblocks && order == o.order &&
-               sm_count == o.sm_count && bn == o.bn && band == o.band && pieces == o.pieces;
+               sm_count == o.sm_count && bn == o.bn && band == o.band && pieces == o.pieces && pair == o.pair;
     }
 };
 struct DevicePlan {
@@ -1303,13 +1108,13 @@ DevicePlan g_plans[PLAN_DEVICES][PLAN_SLOTS];
 unsigned long long g_plan_clock = 0;
 std::mutex g_plan_mutex;
 
-int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn, const Tunables& tn, cudaStream_t stream,
-             DevicePlan** out) {
+int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int bn, const Tunables& tn, bool pair,
+             cudaStream_t stream, DevicePlan** out) {
     int dev = 0;
     CAKE_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= PLAN_DEVICES) dev = 0;
     std::lock_guard<std::mutex> lock(g_plan_mutex);
-    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn, tn.band, tn.pieces};
+    const PlanKey key = {tiles_m, tiles_n, kblocks, order, sm_count, bn, tn.band, tn.pieces, pair ? 1 : 0};
     DevicePlan* slots = g_plans[dev];
     DevicePlan* victim = nullptr;
     for (int i = 0; i < PLAN_SLOTS; i++) {
@@ -1333,7 +1138,7 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
             return CAKEB200_ERR_ARG;
         }
     }
-    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, tn);
+    const HostPlan hp = build_plan(tiles_m, tiles_n, kblocks, order, sm_count, tn, pair);
     const size_t units_b = align_up(hp.units.size() * sizeof(int4) + 16, 256);
     const size_t begin_b = align_up(hp.cta_begin.size() * sizeof(int), 256);
     const size_t pieces_b = align_up(hp.pieces.size() * sizeof(TilePieces) + 16, 256);
@@ -1369,9 +1174,9 @@ int get_plan(int tiles_m, int tiles_n, int kblocks, int order, int sm_count, int
 }
 
 // bytes of partial-tile slots a product may need (an upper bound that does not depend on the plan)
-size_t partial_slot_bytes(int sm_count) { return (size_t) (4 * sm_count + 8) * BM * 256 * sizeof(float); }
+size_t partial_slot_bytes(int sm_count) { return (size_t) (4 * sm_count + 16) * BM * 256 * sizeof(float); }
 
-// Clusters of two CTAs of the pair kernel that the device runs at once (0: it cannot run them), per device.
+// Pairs of CTAs (clusters of two) of the largest pair kernel that the device runs at once; 0: it cannot. Per device.
 int pair_clusters() {
     static std::mutex m;
     static int cached[PLAN_DEVICES];  // 0 = not asked yet, -1 = unavailable
@@ -1385,90 +1190,87 @@ int pair_clusters() {
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cudaLaunchConfig_t cfg = {};
-        cfg.blockDim = dim3(NUM_THREADS);
-        cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+        cfg.blockDim = dim3(CHUNKED_THREADS);
+        cfg.dynamicSmemBytes = Cfg<256, true>::SMEM_BYTES_CHUNKED;
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms >= 2 &&
-            cudaFuncSetAttribute(sgemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) == cudaSuccess) {
+            cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<256, true>::SMEM_BYTES_CHUNKED) == cudaSuccess) {
             cfg.gridDim = dim3((unsigned) (sms / 2 * 2));
-            if (cudaOccupancyMaxActiveClusters(&n, sgemm_tf32x3_pair_kernel, &cfg) == cudaSuccess && n > 0) cached[dev] = n;
+            if (cudaOccupancyMaxActiveClusters(&n, sgemm_tf32x3_chunked_kernel<256, true>, &cfg) == cudaSuccess && n > 0) cached[dev] = n;
         }
         cudaGetLastError();
     }
     return cached[dev] > 0 ? cached[dev] : 0;
 }
 
-// The product on pairs of SMs, 256 x 256 tiles, whole K per tile (ranges of K for very deep products).
-// Returns PAIR_NOT_APPLICABLE when the caller should go on with the single-CTA kernels.
-constexpr int PAIR_NOT_APPLICABLE = 1;
-int launch_pair(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, int* status_word, int sm_count,
-                cudaStream_t stream, int* launches, const Tunables& tn) {
-    const int mode = option_get(OPT_PAIR);  // 0 = rule, 1 = wherever it applies, 2 = never
-    if (mode == 2 || g.out_p != 0 || g.owners || g.M < 2 * BM || g.N < PairCfg::BN) return PAIR_NOT_APPLICABLE;
-    const int kblocks = (g.K + BK - 1) / BK;
-    const int chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (g.K <= 4096 ? CHUNK_KB : 0x7fffffff);
-    const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + PairCfg::BN - 1) / PairCfg::BN;
-    const long long tiles = (long long) tiles_m * tiles_n;
-    const int range_kb = (kblocks > 512 && tiles >= 2LL * sm_count) ? 256 : kblocks;
-    if (chunk_kb < range_kb) return PAIR_NOT_APPLICABLE;  // this product accumulates in chunks: the chunked kernel's job
-    const int clusters = pair_clusters();
-    if (clusters <= 0 || tiles > 0x7fffffffLL) return PAIR_NOT_APPLICABLE;
-    // Rule: the pair kernel takes whole tiles in waves of `clusters`, so it is used where the last wave is
-    // nearly full (the single-CTA kernels cut their ragged last wave along K instead); it gains 15 to 20 %.
-    const long long waves = (tiles + clusters - 1) / clusters;
-    if (mode == 0 && tiles * 100 < waves * clusters * 88) return PAIR_NOT_APPLICABLE;
-    const int Kp = padded_k(g.K);
-    alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-    int rc;
-    if ((rc = make_map(&ma_hi, a_hi, g.M, g.K, Kp, BM))) return rc;
-    if ((rc = make_map(&ma_lo, a_lo, g.M, g.K, Kp, BM))) return rc;
-    if ((rc = make_map(&mb_hi, b_hi, g.N, g.K, Kp, PairCfg::HALF_N))) return rc;
-    if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, PairCfg::HALF_N))) return rc;
-    Tf32x3Args a = {};
-    a.C = g.C;
-    a.M = g.M; a.N = g.N; a.K = g.K;
-    a.ldc = g.ldc;
-    a.tiles_m = tiles_m; a.tiles_n = tiles_n;
-    a.dp_tiles = (int) tiles;
-    a.chunk_kb = 0x7fffffff;
-    a.order = g.order;
-    a.band = band_for(g.order, tiles_m, tiles_n, tn);
-    a.status_word = status_word;
-    const int grid = 2 * (int) std::min<long long>(tiles, clusters);
-    for (int first = 0; first < kblocks; first += range_kb) {
-        a.kb_first = first;
-        a.kblocks = std::min(range_kb, kblocks - first);
-        a.accumulate = (first > 0) ? 1 : g.accumulate;
-        a.bias = (first > 0) ? nullptr : g.bias;
-        sgemm_tf32x3_pair_kernel<<<grid, NUM_THREADS, PairCfg::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, a);
-        CAKE_CUDA_OK(cudaGetLastError());
-        if (launches) (*launches)++;
+// Whether a product with M rows runs its tiles on pairs of SMs.  Not for a K-sharded product (its tiles go
+// to their owners in 128-row units), not for a single row of tiles, and under the rule not where padding
+// the rows to 256 instead of 128 would add more than 7 % of work.
+bool use_pair(int M, bool owners) {
+    const int mode = option_get(OPT_PAIR);  // 0 = rule, 1 = wherever possible, 2 = never
+    if (mode == 2 || owners || M <= BM) return false;
+    if (pair_clusters() <= 0) return false;
+    if (mode == 1) return true;
+    const long long p256 = (M + 2 * BM - 1) / (2 * BM) * (2LL * BM), p128 = (M + BM - 1) / BM * (long long) BM;
+    return p256 * 100 <= p128 * 107;
+}
+inline int tile_rows(bool pair) { return pair ? 2 * BM : BM; }
+inline int tile_units(bool pair, int sm_count) { return pair ? pair_clusters() : sm_count; }
+
+template <int BN, bool PAIR>
+cudaError_t run_kernel(bool chunked, int grid_units, cudaStream_t stream, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo,
+                       const CUtensorMap& mb_hi, const CUtensorMap& mb_lo, const Tf32x3Args& args) {
+    using C_ = Cfg<BN, PAIR>;
+    static const cudaError_t attr_plain =
+        cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
+    static const cudaError_t attr_chunked = cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<BN, PAIR>,
+                                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES_CHUNKED);
+    if (attr_plain != cudaSuccess) return attr_plain;
+    if (attr_chunked != cudaSuccess) return attr_chunked;
+    if constexpr (PAIR) {
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) (2 * grid_units));
+        cfg.blockDim = dim3(chunked ? CHUNKED_THREADS : NUM_THREADS);
+        cfg.dynamicSmemBytes = chunked ? C_::SMEM_BYTES_CHUNKED : C_::SMEM_BYTES;
+        cfg.stream = stream;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        return chunked ? cudaLaunchKernelEx(&cfg, sgemm_tf32x3_chunked_kernel<BN, PAIR>, ma_hi, ma_lo, mb_hi, mb_lo, args)
+                       : cudaLaunchKernelEx(&cfg, sgemm_tf32x3_kernel<BN, PAIR>, ma_hi, ma_lo, mb_hi, mb_lo, args);
+    } else {
+        if (chunked)
+            sgemm_tf32x3_chunked_kernel<BN, PAIR><<<grid_units, CHUNKED_THREADS, C_::SMEM_BYTES_CHUNKED, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
+        else
+            sgemm_tf32x3_kernel<BN, PAIR><<<grid_units, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
+        return cudaGetLastError();
     }
-    return CAKEB200_OK;
 }
 
-// plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots)
-template <int BN>
+// plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots).  A plan must have been
+// built for the same PAIR (tile rows and unit count).
+template <int BN, bool PAIR>
 int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials, DevicePlan* plan,
            int* status_word, int sm_count, cudaStream_t stream, int* launches, const Tunables& tn) {
-    if (BN == 256) {
-        const int prc = launch_pair(g, a_hi, a_lo, b_hi, b_lo, status_word, sm_count, stream, launches, tn);
-        if (prc != PAIR_NOT_APPLICABLE) return prc;
-    }
+    using C_ = Cfg<BN, PAIR>;
+    const int units = tile_units(PAIR, sm_count);
     const int Kp = padded_k(g.K);
     alignas(64) CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
     if ((rc = make_map(&ma_hi, a_hi, g.M, g.K, Kp, BM))) return rc;
     if ((rc = make_map(&ma_lo, a_lo, g.M, g.K, Kp, BM))) return rc;
-    if ((rc = make_map(&mb_hi, b_hi, g.N, g.K, Kp, BN))) return rc;
-    if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, BN))) return rc;
+    if ((rc = make_map(&mb_hi, b_hi, g.N, g.K, Kp, C_::B_ROWS))) return rc;
+    if ((rc = make_map(&mb_lo, b_lo, g.N, g.K, Kp, C_::B_ROWS))) return rc;
 
     Tf32x3Args a;
     a.C = g.C;
     a.partials = partials;
+    a.slot_count = plan ? plan->slots : 0;
     a.M = g.M; a.N = g.N; a.K = g.K;
     a.ldc = g.ldc;
-    a.tiles_m = (g.M + BM - 1) / BM;
+    a.tiles_m = (g.M + C_::TILE_M - 1) / C_::TILE_M;
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
@@ -1488,54 +1290,43 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
         set_error("sgemm_tf32x3: too many tiles");
         return CAKEB200_ERR_TOO_LARGE;
     }
-    int grid;
+    int grid;  // units that take tiles: CTAs, or pairs of CTAs
     if (plan && plan->units && partials) {
         a.units = plan->units; a.cta_begin = plan->cta_begin; a.dp_tiles = plan->dp_tiles;
         grid = plan->grid;
     } else {
         a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
-        grid = (int) std::min<long long>(tiles, sm_count);
+        grid = (int) std::min<long long>(tiles, units);
     }
-    static const cudaError_t attr_plain =
-        cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
-    static const cudaError_t attr_chunked = cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                                 Cfg<BN>::SMEM_BYTES_CHUNKED);
-    CAKE_CUDA_OK(attr_plain);
-    CAKE_CUDA_OK(attr_chunked);
     // the chunked kernel only where some K range is longer than a chunk (whole tiles; pieces are shorter)
     auto run = [&](const Tf32x3Args& args) {
         const int longest = (plan && a.units && plan->dp_tiles == 0 && plan->longest_kb > 0) ? plan->longest_kb : args.kblocks;
-        if (args.chunk_kb < longest)
-            sgemm_tf32x3_chunked_kernel<BN><<<grid, CHUNKED_THREADS, Cfg<BN>::SMEM_BYTES_CHUNKED, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
-        else
-            sgemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, args);
+        return run_kernel<BN, PAIR>(args.chunk_kb < longest, grid, stream, ma_hi, ma_lo, mb_hi, mb_lo, args);
     };
     // A very deep product with many tiles is run as several launches over ranges of K, each adding to C.
     // Within one launch the CTAs of a wave share their A and B panels through L2 only while they work on
     // nearby slices of K; over thousands of slices they drift apart and the panels come from DRAM once per
     // CTA (32768^3: 400 ms in one launch, 313 ms in ranges of 8192, at the cost of re-reading C three times).
     const int total_kb = a.kblocks;
-    const int range_kb = (total_kb > 512 && tiles >= 4LL * sm_count && g.out_p == 0) ? 256 : total_kb;
+    const int range_kb = (total_kb > 512 && tiles * (PAIR ? 2 : 1) >= 4LL * sm_count && g.out_p == 0) ? 256 : total_kb;
     if (g.owners && !(range_kb == total_kb && a.units && plan->num_pieces > 0 && plan->dp_tiles == 0)) {
         set_error("sgemm_tf32x3: a K-sharded product needs a shape whose tiles are all cut into K pieces");
         return CAKEB200_ERR_ARG;
     }
     if (range_kb < total_kb) {
         a.units = nullptr; a.cta_begin = nullptr; a.dp_tiles = (int) tiles;
-        grid = (int) std::min<long long>(tiles, sm_count);
+        grid = (int) std::min<long long>(tiles, units);
         for (int first = 0; first < total_kb; first += range_kb) {
             a.kb_first = first;
             a.kblocks = std::min(range_kb, total_kb - first);
             a.accumulate = (first > 0) ? 1 : g.accumulate;
             a.bias = (first > 0) ? nullptr : g.bias;
-            run(a);
-            CAKE_CUDA_OK(cudaGetLastError());
+            CAKE_CUDA_OK(run(a));
             if (launches) (*launches)++;
         }
         return CAKEB200_OK;
     }
-    run(a);
-    CAKE_CUDA_OK(cudaGetLastError());
+    CAKE_CUDA_OK(run(a));
     if (launches) (*launches)++;
     if (g.owners) {
         reduce_pieces_to_owners_kernel<BN><<<dim3(plan->num_pieces, 16), 256, 0, stream>>>(partials, plan->pieces, g.M, g.N, *g.owners);
@@ -1555,6 +1346,16 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
         else CAKE_CUDA_OK(cudaEventRecord(plan->last_use, stream));
     }
     return CAKEB200_OK;
+}
+
+// The instantiation for a tile width and form.
+int launch_as(int bn, bool pair, const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b_lo, float* partials,
+              DevicePlan* plan, int* status_word, int sm_count, cudaStream_t stream, int* launches, const Tunables& tn) {
+    if (pair)
+        return (bn == 256) ? launch<256, true>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, launches, tn)
+                           : launch<128, true>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, launches, tn);
+    return (bn == 256) ? launch<256, false>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, launches, tn)
+                       : launch<128, false>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, launches, tn);
 }
 
 // rows [0, M) of A (leading dimension lda) -> hi / lo planes
@@ -1665,12 +1466,13 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     DevicePlan* plan = nullptr;
     const Tunables tn = resolve_tunables(rows, N, K, order);
     const int bn = tile_width(p.M, N, K, sm_count, tn);  // of the whole product, so that every band of rows uses one width
+    const bool pair = use_pair(rows, false);
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
-        int rc = get_plan((rows + BM - 1) / BM, (N + bn - 1) / bn, (K + BK - 1) / BK, order, sm_count, bn, tn, stream, &plan);
+        int rc = get_plan((rows + tile_rows(pair) - 1) / tile_rows(pair), (N + bn - 1) / bn, (K + BK - 1) / BK, order,
+                          tile_units(pair, sm_count), bn, tn, pair, stream, &plan);
         if (rc) return rc;
     }
-    return (bn == 256) ? launch<256>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr, tn)
-                       : launch<128>(g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr, tn);
+    return launch_as(bn, pair, g, a_hi, a_lo, p.b_hi, p.b_lo, p.partials, plan, status_word, sm_count, stream, nullptr, tn);
 }
 
 // scratch = A hi/lo planes + transposed B hi/lo planes + slots for the partial tiles of the last wave (worst case)
@@ -1679,6 +1481,8 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     const size_t a = align_up((size_t) M * Kp * 4, 1024), b = align_up((size_t) N * Kp * 4, 1024);
     return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
 }
+
+int tf32x3_tile_rows(int M) { return tile_rows(use_pair(M, false)); }
 
 size_t tf32x3_one_plane_bytes(int rows, int K) { return align_up((size_t) rows * padded_k(K) * 4, 1024); }
 
@@ -1694,7 +1498,7 @@ bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
     const int bn = tile_width(M, N, K, sm_count, tn), kblocks = (K + BK - 1) / BK;
     const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     if (tiles >= sm_count) return false;
-    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, tn);
+    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, tn, false);
     return hp.dp_tiles == 0 && !hp.pieces.empty();
 }
 
@@ -1747,15 +1551,16 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
     DevicePlan* plan = nullptr;
-    if ((rc = get_plan((g.M + BM - 1) / BM, (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order, sm_count, bn, tn, stream, &plan)))
+    const bool pair = use_pair(g.M, g.owners != nullptr);
+    if ((rc = get_plan((g.M + tile_rows(pair) - 1) / tile_rows(pair), (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order,
+                       tile_units(pair, sm_count), bn, tn, pair, stream, &plan)))
         return rc;
     int launches = split_launches;
-    rc = (bn == 256) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn)
-                     : launch<128>(g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn);
+    rc = launch_as(bn, pair, g, a_hi, a_lo, b_hi, b_lo, partials, plan, status_word, sm_count, stream, &launches, tn);
     if (rc) return rc;
     if (stats) {
         stats->launches += launches;
-        stats->tile_m = BM; stats->tile_n = bn; stats->tile_k = BK;
+        stats->tile_m = tile_rows(pair); stats->tile_n = bn; stats->tile_k = BK;
     }
     return CAKEB200_OK;
 }
@@ -1910,8 +1715,8 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
     // whole-K tiles only: cutting tiles along K would need slots for partial tiles, i.e. more scratch
-    rc = (N > 128) ? launch<256>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr, Tunables())
-                   : launch<128>(g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr, Tunables());
+    rc = launch_as(N > 128 ? 256 : 128, use_pair(M, false), g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr,
+                   Tunables());
     if (rc) return rc;
     int word[4] = {0, 0, 0, 0};
     CAKE_CUDA_OK(cudaMemcpyAsync(word, status_word, sizeof(word), cudaMemcpyDeviceToHost, s));

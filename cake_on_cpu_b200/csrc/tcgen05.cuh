@@ -164,6 +164,51 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PAIR_LEADER_MASK) : "memory");
 }
 
+// One source for the single-CTA and the pair form of a kernel: PAIR selects the instruction variants.
+template <bool PAIR>
+__device__ __forceinline__ void tma_load_2d_t(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    if constexpr (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
+    else tma_load_2d(dst, map, x, y, bar);
+}
+template <bool PAIR>
+__device__ __forceinline__ void umma_tf32_t(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (PAIR) umma_tf32_pair(tmem_d, desc_a, desc_b, idesc, accumulate);
+    else umma_tf32(tmem_d, desc_a, desc_b, idesc, accumulate);
+}
+template <bool PAIR>
+__device__ __forceinline__ void umma_commit_t(uint32_t bar) {
+    if constexpr (PAIR) umma_commit_pair(bar);
+    else umma_commit(bar);
+}
+// Arrive on the barrier the MMA issuer waits on: this CTA's, or the leader's in a pair.
+template <bool PAIR>
+__device__ __forceinline__ void mbar_arrive_t(uint32_t bar) {
+    if constexpr (PAIR) mbar_arrive_leader(bar);
+    else mbar_arrive(bar);
+}
+// Tensor-memory allocation by one whole warp (the same warp of both CTAs in a pair, same `slot` offset).
+template <bool PAIR>
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+    if constexpr (PAIR) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+}
+template <bool PAIR>
+__device__ __forceinline__ void tmem_free(uint32_t base, uint32_t cols) {
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+// Every thread of the CTA, or of both CTAs of the pair.
+template <bool PAIR>
+__device__ __forceinline__ void sync_all_t() {
+    if constexpr (PAIR) cluster_sync_all();
+    else __syncthreads();
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

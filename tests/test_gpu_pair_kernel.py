@@ -15,28 +15,50 @@ UNBROKEN = 1 << 20  # chunk length (slices of 32 of K) longer than any K here: o
 @pytest.fixture
 def pair_options(cake):
     yield cake
-    cake.set_option("pair", 0)
-    cake.set_option("chunk_kb", 0)
+    for name in ("pair", "chunk_kb", "k_pieces", "tile_n"):
+        cake.set_option(name, 0)
 
 
-def _product(cake, A, B, pair, **kw):
+def _product(cake, A, B, pair, chunk_kb=UNBROKEN, k_pieces=1, tile_n=0, **kw):
     cake.set_option("pair", pair)
-    cake.set_option("chunk_kb", UNBROKEN)
+    cake.set_option("chunk_kb", chunk_kb)
+    cake.set_option("k_pieces", k_pieces)  # 1: whole tiles only, so that both forms add in the same order
+    cake.set_option("tile_n", tile_n)
     C = np.full((A.shape[0], B.shape[1]), np.nan, np.float32)
-    cake.cake_sgemm_ex(A, B, C, kernel=cake.KERNEL_TF32X3, **kw) if kw else cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+    cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
     return C
 
 
-@pytest.mark.parametrize("shape", [(256, 64, 256), (512, 512, 512), (1000, 700, 900), (257, 33, 1030), (2111, 960, 2111)])
-def test_pair_kernel_matches_single_sm_kernel_and_oracle(pair_options, oracle, shape):
+SHAPES = [(256, 64, 256), (512, 512, 512), (1000, 700, 900), (257, 33, 1030), (2111, 960, 2111), (129, 100, 64)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("chunk_kb", [UNBROKEN, 8])
+@pytest.mark.parametrize("tile_n", [0, 128])
+def test_pair_kernel_matches_single_sm_kernel_and_oracle(pair_options, oracle, shape, chunk_kb, tile_n):
     cake = pair_options
     M, K, N = shape
     A, B = oracle.uniform((M, K), 1), oracle.uniform((K, N), 2)
     ref, _ = oracle.sgemm(A, B, 8, KMN)
-    pair = _product(cake, A, B, 1)
-    single = _product(cake, A, B, 2)
+    pair = _product(cake, A, B, 1, chunk_kb, 1, tile_n)
+    assert cake.last_stats()["tile_m"] == 256
+    single = _product(cake, A, B, 2, chunk_kb, 1, tile_n)
+    assert cake.last_stats()["tile_m"] == 128
     assert rel_err(pair, ref, A, B) <= TOL
     assert np.array_equal(pair, single)
+
+
+@pytest.mark.parametrize("shape", [(2111, 960, 2111), (1024, 4100, 1024), (3000, 3000, 3000), (640, 2048, 5000)])
+def test_pair_kernel_with_tiles_cut_along_k(pair_options, oracle, shape):
+    """The ragged last wave is cut into K pieces whose partial tiles (two 128-row halves per pair) are summed
+    by the reduction kernel; chunk length by the rule."""
+    cake = pair_options
+    M, K, N = shape
+    A, B = oracle.uniform((M, K), 5), oracle.uniform((K, N), 6)
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    for pair in (1, 2):
+        C = _product(cake, A, B, pair, 0, 0)
+        assert rel_err(C, exact, A, B) <= TOL, (pair, shape)
 
 
 @pytest.mark.parametrize("sch", [KMN, MKN, NKM])
@@ -64,6 +86,7 @@ def test_pair_kernel_bias_and_accumulate(pair_options):
     for pair in (1, 2):
         cake.set_option("pair", pair)
         cake.set_option("chunk_kb", UNBROKEN)
+        cake.set_option("k_pieces", 1)
         C = torch.full((M, N), float("nan"), device="cuda")
         cake.cake_sgemm_ex(A, B, C, bias=bias, kernel=cake.KERNEL_TF32X3)
         cake.cake_sgemm_ex(A, B, C, accumulate=True, kernel=cake.KERNEL_TF32X3)
@@ -85,6 +108,7 @@ def test_pair_kernel_full_size(pair_options):
     out = {}
     for pair in (1, 2):
         cake.set_option("pair", pair)
+        cake.set_option("k_pieces", 1)  # whole tiles in both forms: the same order of additions
         C = torch.empty((n, n), device="cuda")
         cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
         out[pair] = C
