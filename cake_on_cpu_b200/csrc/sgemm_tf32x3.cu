@@ -51,6 +51,7 @@
 
 #include <stdlib.h>
 #include <string.h>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -1222,12 +1223,18 @@ template <int BN, bool PAIR>
 cudaError_t run_kernel(bool chunked, int grid_units, cudaStream_t stream, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo,
                        const CUtensorMap& mb_hi, const CUtensorMap& mb_lo, const Tf32x3Args& args) {
     using C_ = Cfg<BN, PAIR>;
-    static const cudaError_t attr_plain =
-        cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
-    static const cudaError_t attr_chunked = cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<BN, PAIR>,
-                                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES_CHUNKED);
-    if (attr_plain != cudaSuccess) return attr_plain;
-    if (attr_chunked != cudaSuccess) return attr_chunked;
+    // the shared-memory opt-in is a property of the kernel on one device: once per device a product runs on
+    static std::atomic<unsigned long long> opted_in{0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !(opted_in.load() >> dev & 1)) {
+        e = cudaFuncSetAttribute(sgemm_tf32x3_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(sgemm_tf32x3_chunked_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES_CHUNKED);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) opted_in.fetch_or(1ULL << dev);
+    }
     if constexpr (PAIR) {
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
