@@ -135,9 +135,35 @@ int stage_out(const Operand& op, cudaStream_t s) {
     return CAKEB200_OK;
 }
 
+// Page-locked landing place for the status word, one per host thread: a device-to-host copy into
+// pageable memory goes through the driver's staging buffer and costs the blocking call tens of
+// microseconds; into page-locked memory it is a plain DMA.  Falls back to the caller's stack array.
+struct HostStatus {
+    int* word = nullptr;
+    HostStatus() {
+        if (cudaHostAlloc((void**) &word, 64, cudaHostAllocPortable) != cudaSuccess) {
+            cudaGetLastError();
+            word = nullptr;
+        }
+    }
+    ~HostStatus() {
+        if (word) cudaFreeHost(word);
+        cudaGetLastError();  // at process exit the runtime may already be gone
+    }
+};
+
+}  // namespace
+int* pinned_host_words() {
+    static thread_local HostStatus pinned;
+    return pinned.word;
+}
+namespace {
+
 int check_status_word(DeviceState* st, cudaStream_t s) {
-    int host_word[4] = {0, 0, 0, 0};
-    CAKE_CUDA_OK(cudaMemcpyAsync(host_word, st->status_word, sizeof(host_word), cudaMemcpyDeviceToHost, s));
+    int stack_word[4] = {0, 0, 0, 0};
+    int* pinned = pinned_host_words();
+    int* host_word = pinned ? pinned : stack_word;
+    CAKE_CUDA_OK(cudaMemcpyAsync(host_word, st->status_word, sizeof(stack_word), cudaMemcpyDeviceToHost, s));
     CAKE_CUDA_OK(cudaStreamSynchronize(s));
     if (host_word[0] != 0) {
         set_error("device-side wait gave up (code %d, where %d, info %d)", host_word[0], host_word[1], host_word[2]);

@@ -99,6 +99,9 @@ int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t st
 // Process-wide overrides set through cakeb200_set_option (abi.cu); 0 = the library's own rule.
 enum Option { OPT_TILE_N, OPT_BAND, OPT_K_PIECES, OPT_CHUNK_KB, OPT_CONV_ROUTE, OPT_SMALL_OPERANDS, OPT_PACK_SCALAR, OPT_PAIR, OPT_COUNT };
 int option_get(int id);
+// 16 page-locked ints of the calling host thread (nullptr if they could not be had): landing place for small
+// device-to-host reads; words 0-3 are the status word's, 8-9 a 64-bit count (abi.cu)
+int* pinned_host_words();
 // issue rate of dense TF32 MMAs on every SM (peak_tf32.cu)
 int measure_tf32_peak(int* status_word, int sm_count, float ms_target, cudaStream_t stream, float* tflops, float* ms_out);
 // batches of small products on the tensor cores, operands split inside the kernel (sgemm_small_tf32x3.cu)

@@ -21,7 +21,9 @@
 // Two kernels share this file.  Both: one CTA per SM, warp 0 issues TMA loads, warp 1 issues the MMAs
 // and owns the tensor-memory allocation.  The plain kernel has four more warps that drain finished
 // accumulators; the chunked kernel has three warp groups, the eight warps of the last two drain accumulators
-// (tcgen05.ld) while the MMAs already fill the other accumulator buffer.
+// (tcgen05.ld) while the MMAs already fill the other accumulator buffer.  Each exists in two forms,
+// chosen by the template parameter PAIR: one CTA per 128 x BN tile, or the two CTAs of a cluster on one
+// 256 x BN tile (tcgen05 cta_group::2, see Cfg), which is what products with more than 128 rows run.
 //
 // Accumulation in chunks of K.  The tensor core adds into tensor memory with
 // truncation, so the error of one long accumulation grows linearly with K (at

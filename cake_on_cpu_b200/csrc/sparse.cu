@@ -348,10 +348,12 @@ int sp_compact(const float* A, int M, int K, void* scratch, int* status_word, cu
         compact_rows_kernel<<<row_blocks, 256, 0, stream>>>(A, M, K, l.ptr, l.cols, l.vals, status_word);
     CAKE_CUDA_OK(cudaGetLastError());
     if ((rc = after_kernel("compact_rows_kernel", stream))) return rc;
-    long long total = 0;
-    CAKE_CUDA_OK(cudaMemcpyAsync(&total, l.ptr + M, sizeof(total), cudaMemcpyDeviceToHost, stream));
+    long long stack_total = 0;
+    int* pinned = pinned_host_words();
+    long long* total = pinned ? reinterpret_cast<long long*>(pinned + 8) : &stack_total;
+    CAKE_CUDA_OK(cudaMemcpyAsync(total, l.ptr + M, sizeof(*total), cudaMemcpyDeviceToHost, stream));
     CAKE_CUDA_OK(cudaStreamSynchronize(stream));
-    if (nnz) *nnz = total;
+    if (nnz) *nnz = *total;
     if (launches) *launches += 3;
     return CAKEB200_OK;
 }
