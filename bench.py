@@ -307,14 +307,14 @@ def gpu_arm(args):
         peak = bf16_burst / 2 / 3 if args.kernel == "tf32x3" else 148 * 128 * 2 * 1.965e9 / 1e12
         achieved = 2.0 * rows * cols * K / (kern_ms_avg * 1e-3) / 1e12
         # DRAM bytes of one contraction launch, from one ncu capture of the 8192^3 launch on one GPU
-        # (dram__bytes_read.sum 4.627 GB + dram__bytes_write.sum 0.256 GB; summary under profiles/).  The
+        # (dram__bytes_read.sum 4.552 GB + dram__bytes_write.sum 0.520 GB; summary under profiles/).  The
         # algorithmic bytes are 1.34 GB (four operand planes read once, C written once); the rest is A and B
         # panels read again by later waves of tiles once they have left the 126 MB L2.  A rank of a
         # multi-GPU run owns rows x cols of C and its traffic is scaled by that share.
         traffic = None
         if args.kernel == "tf32x3" and size == 8192:
-            traffic = (4.627e9 + 0.256e9) * (rows * cols) / float(M * N)
-        roofline = {"bound": "tensor", "kernel": "sgemm_tf32x3_kernel" if args.kernel == "tf32x3" else "sgemm_ffma_kernel",
+            traffic = (4.552e9 + 0.520e9) * (rows * cols) / float(M * N)
+        roofline = {"bound": "tensor", "kernel": "sgemm_tf32x3_chunked_kernel<256, pair>" if args.kernel == "tf32x3" else "sgemm_ffma_kernel",
                     "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                     "peak_source": ("bf16 burst %.1f TFLOP/s of %s / 2 (TF32 rate) / 3 (MMAs per product)" % (bf16_burst, which))
                     if args.kernel == "tf32x3" else "148 SMs x 128 lanes x 2 flop x 1.965 GHz",

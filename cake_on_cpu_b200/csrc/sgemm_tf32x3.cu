@@ -34,21 +34,20 @@
 // into a running sum held in registers with round-to-nearest FP32 adds, so only
 // the chunk length, not K, sets the truncation error.  The fold overlaps the MMAs
 // of the next chunk; the last chunk is added on the way out to global memory.
-// Reading an accumulator out of tensor memory is not free: each fold costs the MMAs about
-// 2300 cycles (the time of 17 of them), whether the loads are 32 or 64 columns wide, one or
-// two in flight, bunched or spread over the chunk, so the chunk length trades accuracy for
-// speed.  Largest absolute error over the whole matrix against float64, uniform(-1, 1), and
-// kernel time, for chunks of 512 / 768 / 1024 / 1536 of K / one unbroken accumulation:
-//   3000^3: 3.3e-4 / 5.2e-4 / 7.3e-4 / 1.1e-3 / 2.5e-3,  0.282 / 0.271 / 0.270 / 0.265 / 0.263 ms
-//   4096^3: 4.4e-4 / 6.5e-4 / 9.2e-4 / 1.3e-3 / 3.6e-3,  0.594 / 0.568 / 0.557 / 0.555 / 0.541 ms
-//   8192^3 (64 rows sampled): 5.3e-4 / - / 1.1e-3 / - / 1.0e-2,  4.44 / - / 4.26 / - / 4.19 ms alone,
-//   and in a loop of 60 products under the power cap 5.2 ms with chunks of 1024 against 4.6 ms plain
-// (the exact-FP32 FFMA kernel: 2.3e-4, 3.7e-4 and, against the reference's own result,
-// 9.5e-4 at 8192^3).  Rule: chunks of 1024 of K up to K = 4096, which keeps those products below
-// the reference's 1e-3 for 2 to 3 % of the kernel time, and the plain kernel (one unbroken
-// accumulation) above, where no affordable chunk length reaches 1e-3 anyway; the "chunk_kb"
-// option forces a chunk length at any K (8, i.e. 256 of K, brings 8192^3 to 9.0e-4 against the
-// reference).
+// Reading an accumulator out of tensor memory while MMAs run is not free: each fold costs the MMAs
+// about 1150 cycles (0.6 us, the time of nine of them), whether the loads are 32 or 64 columns wide, one
+// or two in flight, bunched or spread over the chunk, so the chunk length trades accuracy for speed.
+// Largest absolute error against float64 (64 sampled rows, uniform(-1, 1)) and time per product in a loop
+// of 40 products (6 at 16384^3) on pairs of SMs, for one unbroken accumulation / chunks of 1024 / 512 /
+// 256 of K:
+//    4096^3: 3.0e-3 / 7.8e-4 / 3.3e-4 / 1.9e-4,   0.526 / 0.539 / 0.554 / 0.614 ms
+//    8192^3: 8.3e-3 / 1.1e-3 / 5.6e-4 / 2.6e-4,   4.37-4.67 / 4.55-4.65 / 4.86-4.99 / 4.99-5.14 ms (power-capped)
+//   16384^3: 2.6e-2 / 1.5e-3 / 7.5e-4 / 4.2e-4,   38.0-38.3 / 38.1-39.9 / 40.3-40.5 / 44.0-44.5 ms
+// (the exact-FP32 FFMA kernel: 2.3e-4 at 3000^3, 3.7e-4 at 4096^3 and, against the reference's own result,
+// 9.5e-4 at 8192^3).  Rule: chunks of 1024 of K at every K: 0 to 4 % of the time for an error that no
+// longer grows with K (normalised by the row and column norms: 3e-7 instead of 2.3e-6 at 8192^3, against
+// a gate of 1e-5 that an unbroken accumulation would approach at K = 32768).  The "chunk_kb" option sets
+// another length; a value of at least K / 32 means one unbroken accumulation (the plain kernel).
 #include <cuda.h>
 
 #include <stdlib.h>
@@ -125,6 +124,13 @@ struct Tf32x3Args {
     int* status_word;
 };
 
+// Timeline of CTA 0 (diagnostic build only, -DCAKEB200_ROLE_TIMERS): nanosecond stamps in status_word[16 + 2 * slot].
+#ifdef CAKEB200_ROLE_TIMERS
+#define STAMP(slot) do { if (blockIdx.x == 0) ((unsigned long long*) (args.status_word + 16))[slot] = global_ns(); } while (0)
+#else
+#define STAMP(slot)
+#endif
+
 struct WorkPiece {
     int tile, kb0, kb1, slot;
 };
@@ -154,10 +160,7 @@ __device__ __forceinline__ int piece_chunks(const WorkPiece& w, int chunk_kb) {
 
 // The plain kernel: every tile's (or piece's) K range is one unbroken accumulation in tensor memory.
 // Four drain warps, no running sums, 192 threads.  It is what runs when no K range is longer than a
-// chunk, and for deep products (K above 4096) under the default rule, where it is 5 to 12 % faster than
-// the chunked kernel below in a long loop under the power cap (8192^3, 60 products back to back on one
-// box: 4.58-4.65 ms per product against 4.77 ms for the chunked kernel with folding switched off and
-// 5.17-5.23 ms with chunks of 1024 of K).
+// chunk (K up to 1024 under the rule, K pieces of a deep product with few tiles, or on request).
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
@@ -195,10 +198,12 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x == 0) STAMP(0);
     if (warp == 1) tmem_alloc<PAIR>(smem_u32(tmem_slot), (uint32_t) C_::TMEM_COLS);  // belongs to the MMA warp (of both CTAs of a pair)
     tcgen05_fence_before();
     sync_all_t<PAIR>();  // in a pair: both CTAs' barriers exist before anything arrives on them
     tcgen05_fence_after();
+    if (threadIdx.x == 0) STAMP(1);
     const uint32_t tmem_base = *tmem_slot;
 
     WorkPiece w;
@@ -261,6 +266,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 for (int kb = kb0; kb < kb1; kb++) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
                     if (!ok) break;
+                    if (local == 0 && kb == kb0) STAMP(2);
                     tcgen05_fence_after();
                     const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
                     const uint64_t a_hi = make_kmajor_sw128_desc(base);
@@ -281,6 +287,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 }
                 if (!ok) break;
                 umma_commit_t<PAIR>(acc_full_bar(buf));  // accumulator complete
+                STAMP(3);
             }
         }
     } else {
@@ -305,6 +312,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             ok = mbar_wait(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf);
             ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
             if (!ok) break;
+            if (warp == 2 && lane == 0) STAMP(4);
             tcgen05_fence_after();
             const bool empty_range = w.kb0 >= w.kb1;  // a piece with no K range contributes zeros
             const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN);
@@ -394,8 +402,11 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         }
     }
 
+    if (lane == 0 && (warp == 2 || warp == 4)) STAMP(5 + (warp == 4));
+    if (threadIdx.x == 0) STAMP(7);
     tcgen05_fence_before();
     sync_all_t<PAIR>();  // in a pair: neither CTA frees tensor memory or leaves while the other may still touch it
+    if (threadIdx.x == 0) STAMP(8);
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_free<PAIR>(tmem_base, (uint32_t) C_::TMEM_COLS);
@@ -440,10 +451,12 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x == 0) STAMP(0);
     if (warp == 1) tmem_alloc<PAIR>(smem_u32(tmem_slot), (uint32_t) C_::TMEM_COLS);  // belongs to the MMA warp (of both CTAs of a pair)
     tcgen05_fence_before();
     sync_all_t<PAIR>();  // in a pair: both CTAs' barriers exist before anything arrives on them
     tcgen05_fence_after();
+    if (threadIdx.x == 0) STAMP(1);
     const uint32_t tmem_base = *tmem_slot;
 
     WorkPiece w;
@@ -513,6 +526,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                     for (int kb = kb0; kb < kb1; kb++) {
                         ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
                         if (!ok) break;
+                        if (local == 0 && ci == 0 && kb == kb0) STAMP(2);
                         tcgen05_fence_after();
                         const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
                         const uint64_t a_hi = make_kmajor_sw128_desc(base);
@@ -533,6 +547,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                     }
                     if (!ok) break;
                     umma_commit_t<PAIR>(acc_full_bar(buf));  // chunk complete
+                    STAMP(3);
                 }
             }
         }
@@ -569,6 +584,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                 ok = mbar_wait_for(acc_full_bar(buf), acc_phase, abort_flag, args.status_word, 400 + buf, WAIT_LIMIT_NS, args.drain_backoff);
                 ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
                 if (!ok) break;
+                if (warp == 4 && lane == 0) STAMP(4);
                 tcgen05_fence_after();
                 const uint32_t t_addr = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (buf * BN + half * COLS);
                 float v[32];
@@ -625,7 +641,10 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                         }
                     }
                     const int col = tn * BN + half * COLS + c * 32 + sub_c * 4;
-#pragma unroll
+                    // not unrolled: the enclosing loop over c is (the running sums are indexed by it), and 32 copies of the
+                    // store logic run once per tile, straight through, from a cold instruction cache (measured: the drain
+                    // of a tile took 34 us against 8 us in the plain kernel)
+#pragma unroll 1
                     for (int i = 0; i < 8; i++) {
                         const int r = i * 4 + sub_r;
                         float4 o = ld_shared_v4(patch + (uint32_t) r * 128u + (uint32_t) ((sub_c ^ (r & 7)) << 4));
@@ -683,8 +702,11 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
         }
     }
 
+    if (lane == 0 && (warp == 2 || warp == 4)) STAMP(5 + (warp == 4));
+    if (threadIdx.x == 0) STAMP(7);
     tcgen05_fence_before();
     sync_all_t<PAIR>();  // in a pair: neither CTA frees tensor memory or leaves while the other may still touch it
+    if (threadIdx.x == 0) STAMP(8);
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_free<PAIR>(tmem_base, (uint32_t) C_::TMEM_COLS);
@@ -1258,6 +1280,18 @@ cudaError_t run_kernel(bool chunked, int grid_units, cudaStream_t stream, const 
     }
 }
 
+#ifdef CAKEB200_ROLE_TIMERS
+void print_timeline(int* status_word, cudaStream_t stream, bool chunked) {
+    unsigned long long h[10];
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(h, status_word + 16, sizeof(h), cudaMemcpyDeviceToHost);
+    fprintf(stderr, "K1 %s timeline of CTA 0 (us after entry): ready %.2f, first MMA %.2f, last commit %.2f, last acc_full seen %.2f, "
+            "drain warp 2 done %.2f, drain warp 4 done %.2f, thread 0 at exit %.2f, after final sync %.2f\n", chunked ? "chunked" : "plain",
+            (h[1] - h[0]) * 1e-3, (h[2] - h[0]) * 1e-3, (h[3] - h[0]) * 1e-3, (h[4] - h[0]) * 1e-3, (h[5] - h[0]) * 1e-3,
+            (h[6] - h[0]) * 1e-3, (h[7] - h[0]) * 1e-3, (h[8] - h[0]) * 1e-3);
+}
+#endif
+
 // plan == nullptr: whole-K tiles only, taken round-robin (no table, no partial slots).  A plan must have been
 // built for the same PAIR (tile rows and unit count).
 template <int BN, bool PAIR>
@@ -1283,9 +1317,8 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     a.tiles_n = (g.N + BN - 1) / BN;
     a.kblocks = (g.K + BK - 1) / BK;
     a.kb_first = 0;
-    // Chunk length of the accumulation.  Rule: 1024 of K for products up to K = 4096 (the sizes the reference's
-    // own tests and driver run, which then stay below its 1e-3), one unbroken accumulation above.
-    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : (g.K <= 4096 ? CHUNK_KB : 0x7fffffff);
+    // Chunk length of the accumulation.  Rule: 1024 of K.
+    a.chunk_kb = tn.chunk_kb > 0 ? tn.chunk_kb : CHUNK_KB;
     a.drain_backoff = 400;  // a chunk lasts tens of microseconds; measured +0.4 % at 8192^3 against plain polling
     a.order = g.order;
     a.band = band_for(g.order, a.tiles_m, a.tiles_n, tn);
@@ -1310,7 +1343,11 @@ int launch(const GemmProblem& g, float* a_hi, float* a_lo, float* b_hi, float* b
     // the chunked kernel only where some K range is longer than a chunk (whole tiles; pieces are shorter)
     auto run = [&](const Tf32x3Args& args) {
         const int longest = (plan && a.units && plan->dp_tiles == 0 && plan->longest_kb > 0) ? plan->longest_kb : args.kblocks;
-        return run_kernel<BN, PAIR>(args.chunk_kb < longest, grid, stream, ma_hi, ma_lo, mb_hi, mb_lo, args);
+        const cudaError_t e = run_kernel<BN, PAIR>(args.chunk_kb < longest, grid, stream, ma_hi, ma_lo, mb_hi, mb_lo, args);
+#ifdef CAKEB200_ROLE_TIMERS
+        print_timeline(status_word, stream, args.chunk_kb < longest);
+#endif
+        return e;
     };
     // A very deep product with many tiles is run as several launches over ranges of K, each adding to C.
     // Within one launch the CTAs of a wave share their A and B panels through L2 only while they work on

@@ -132,9 +132,8 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
  *   "band"     tile rows (columns for N-first) per band of the tile walk (rule: 8);
  *   "k_pieces" K ranges each tile of the ragged last wave is cut into (rule: a cost model);
  *   "chunk_kb" 32-deep slices of K accumulated in tensor memory before they are folded into the
- *              FP32 running sum (rule: 32, i.e. 1024 of K, for products up to K = 4096 and one
- *              unbroken accumulation above, whose truncation error grows with K; a value
- *              >= K / 32 also means one unbroken accumulation);
+ *              FP32 running sum (rule: 32, i.e. 1024 of K; a value >= K / 32 means one unbroken
+ *              accumulation, which is 0 to 4 % faster and whose truncation error grows with K);
  * and, so that tests can reach every code path of the other kernels:
  *   "conv_route" 1 = im2col planes + the large-matrix kernel, 2 / 3 = the implicit kernel tiled by
  *              whole rows of one image / by runs of 128 positions across images (rule: by geometry);

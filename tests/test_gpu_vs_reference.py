@@ -64,11 +64,13 @@ def test_full_product_against_the_reference(cake, oracle, reference, size):
         # The reference's own acceptance test (cake_sgemm_checker / mat_equals, absolute 1e-3 per element,
         # reference src/util.cpp:139-169).  The exact-FP32 kernel meets it at every size (at 8192^3 only
         # just: two FP32 summation orders differ by 9.5e-4 there); the tensor-core kernel folds its
-        # accumulation into an FP32 running sum every 1024 of K for products up to K = 4096 and meets it
-        # at 3000^3, the size the reference's own driver runs.  Deeper products run one unbroken
-        # accumulation by default (1e-2 at 8192^3) and meet 1e-3 with the "chunk_kb" option, below.
+        # accumulation into an FP32 running sum every 1024 of K and meets it up to 4096^3 (3000^3 is the
+        # size the reference's own driver runs).  At 8192^3 chunks of 1024 leave about 1.6e-3 against the
+        # reference (2e-3 allowed here) and the "chunk_kb" option brings it below 1e-3, below.
         if kernel == cake.KERNEL_FFMA or n <= 4096:
             assert err_a <= 1e-3
+        else:
+            assert err_a <= 2e-3
     if n > 4096:
         cake.set_option("chunk_kb", 8)
         try:
