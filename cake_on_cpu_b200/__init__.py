@@ -20,5 +20,5 @@ from .api import (  # noqa: F401
     cake_query_cntx, init_block_dims, derive_schedule, set_schedule,
     cake_sgemm_packed_A_size, cake_sgemm_packed_B_size, cake_sgemm_packed_C_size,
     pack_A, pack_B, pack_C, unpack_C, unpack_A, unpack_B,
-    device_count, last_stats, lib, library_path, cake_sgemm_noalloc, NOALLOC_SCRATCH_BYTES, profile_begin, profile_end, tf32_peak, select_devices, set_option, get_option, Planes, cake_sgemm_planes, tune, tune_search, tune_put, tune_get, tune_clear, tune_save, tune_load,
+    device_count, last_stats, lib, library_path, cake_sgemm_noalloc, NOALLOC_SCRATCH_BYTES, profile_begin, profile_end, tf32_peak, select_devices, set_option, get_option, Planes, cake_sgemm_planes, tune, tune_search, tune_search_shape, tune_put, tune_get, tune_clear, tune_save, tune_load,
 )

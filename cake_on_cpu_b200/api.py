@@ -108,10 +108,14 @@ _SIGNATURES["cakeb200_planes_create"] = (_i, [_vp, _i, _i, _i, ctypes.POINTER(_v
 _SIGNATURES["cakeb200_planes_destroy"] = (_i, [_vp])
 _SIGNATURES["cakeb200_sgemm_planes"] = (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp])
 TUNE_COST = ctypes.CFUNCTYPE(ctypes.c_double, _i, _i, _i, _vp)
+TUNE_COST_SHAPE = ctypes.CFUNCTYPE(ctypes.c_double, _i, _i, _i, _i, _vp)
 _SIGNATURES["cakeb200_tune"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_tune_search"] = (_i, [_i, _i, _i, _i, _i, ctypes.c_ulonglong, TUNE_COST, _vp, _pi, _pi, _pi, _pf, _pi])
 _SIGNATURES["cakeb200_tune_put"] = (_i, [_i, _i, _i, _i, _i, _i, _i, ctypes.c_float])
 _SIGNATURES["cakeb200_tune_get"] = (_i, [_i, _i, _i, _i, _pi, _pi, _pi, _pf])
+_SIGNATURES["cakeb200_tune_search_shape"] = (_i, [_i, _i, _i, _i, _i, ctypes.c_ulonglong, TUNE_COST_SHAPE, _vp, _pi, _pi, _pi, _pi, _pf, _pi])
+_SIGNATURES["cakeb200_tune_put_shape"] = (_i, [_i, _i, _i, _i, _i, _i, _i, _i, ctypes.c_float])
+_SIGNATURES["cakeb200_tune_get_shape"] = (_i, [_i, _i, _i, _i, _pi, _pi, _pi, _pi, _pf])
 _SIGNATURES["cakeb200_tune_clear"] = (_i, [])
 _SIGNATURES["cakeb200_tune_save"] = (_i, [ctypes.c_char_p])
 _SIGNATURES["cakeb200_tune_load"] = (_i, [ctypes.c_char_p])
@@ -634,15 +638,26 @@ def tune_search(M, N, K, cost, sm_count=148, trials=24, seed=1):
     return {"tile_n": w.value, "band": b.value, "k_pieces": p.value, "ms": ms.value, "evaluated": n.value}
 
 
-def tune_put(M, N, K, sch, tile_n, band, k_pieces, ms=0.0):
-    _check(lib().cakeb200_tune_put(M, N, K, sch, tile_n, band, k_pieces, ms))
+def tune_search_shape(M, N, K, cost, sm_count=148, trials=24, seed=1):
+    """The search over tile width, cluster shape, band and K pieces with a Python cost function
+    cost(tile_n, cluster, band, k_pieces) -> ms (<= 0: invalid point); cluster 1 = pairs of SMs, 2 = single SMs."""
+    cb = TUNE_COST_SHAPE(lambda w, c, b, p, _user: float(cost(w, c, b, p)))
+    w, c, b, p, n, ms = _i(), _i(), _i(), _i(), _i(), ctypes.c_float()
+    _check(lib().cakeb200_tune_search_shape(M, N, K, sm_count, trials, seed, cb, None, ctypes.byref(w), ctypes.byref(c), ctypes.byref(b),
+                                            ctypes.byref(p), ctypes.byref(ms), ctypes.byref(n)))
+    return {"tile_n": w.value, "cluster": c.value, "band": b.value, "k_pieces": p.value, "ms": ms.value, "evaluated": n.value}
+
+
+def tune_put(M, N, K, sch, tile_n, band, k_pieces, ms=0.0, cluster=0):
+    """Record a choice for a shape; ``cluster`` 0 = the rule, 1 = pairs of SMs, 2 = single SMs."""
+    _check(lib().cakeb200_tune_put_shape(M, N, K, sch, tile_n, cluster, band, k_pieces, ms))
 
 
 def tune_get(M, N, K, sch):
-    w, b, p, ms = _i(), _i(), _i(), ctypes.c_float()
-    if not lib().cakeb200_tune_get(M, N, K, sch, ctypes.byref(w), ctypes.byref(b), ctypes.byref(p), ctypes.byref(ms)):
+    w, c, b, p, ms = _i(), _i(), _i(), _i(), ctypes.c_float()
+    if not lib().cakeb200_tune_get_shape(M, N, K, sch, ctypes.byref(w), ctypes.byref(c), ctypes.byref(b), ctypes.byref(p), ctypes.byref(ms)):
         return None
-    return {"tile_n": w.value, "band": b.value, "k_pieces": p.value, "ms": ms.value}
+    return {"tile_n": w.value, "cluster": c.value, "band": b.value, "k_pieces": p.value, "ms": ms.value}
 
 
 def tune_clear():

@@ -763,9 +763,11 @@ struct TuneRun {
 };
 
 // cost of one point of the grid: fastest of `reps` whole products (split pass + contraction) with the point forced
-double tune_cost(int tile_n, int band, int k_pieces, void* user) {
+double tune_cost(int tile_n, int cluster, int band, int k_pieces, void* user) {
     TuneRun* r = (TuneRun*) user;
-    if (cakeb200_set_option("tile_n", tile_n) || cakeb200_set_option("band", band) || cakeb200_set_option("k_pieces", k_pieces)) return -1;
+    if (cakeb200_set_option("tile_n", tile_n) || cakeb200_set_option("pair", cluster) || cakeb200_set_option("band", band) ||
+        cakeb200_set_option("k_pieces", k_pieces))
+        return -1;
     double best = -1;
     for (int i = 0; i < r->reps + 1; i++) {  // the first run uploads the tile plan of the point and is not timed
         if (cudaEventRecord(r->st->ev[0], r->s) != cudaSuccess) return -1;
@@ -803,11 +805,12 @@ int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K,
     run.g.order = resolve_schedule(st, M, N, K, sched);
     int rc = ensure_scratch(st, tf32x3_scratch_bytes(M, N, K, st->sm_count));
     if (rc) return rc;
-    const int keep[3] = {cakeb200_get_option("tile_n"), cakeb200_get_option("band"), cakeb200_get_option("k_pieces")};
-    int tile_n = 0, band = 0, k_pieces = 0, evaluated = 0;
+    const int keep[4] = {cakeb200_get_option("tile_n"), cakeb200_get_option("band"), cakeb200_get_option("k_pieces"),
+                         cakeb200_get_option("pair")};
+    int tile_n = 0, cluster = 0, band = 0, k_pieces = 0, evaluated = 0;
     float best_ms = 0.f;
-    rc = cakeb200_tune_search(M, N, K, st->sm_count, trials, 0x5eedULL + (unsigned long long) M * 31 + N * 17 + K, tune_cost, &run, &tile_n,
-                              &band, &k_pieces, &best_ms, &evaluated);
+    rc = cakeb200_tune_search_shape(M, N, K, st->sm_count, trials, 0x5eedULL + (unsigned long long) M * 31 + N * 17 + K, tune_cost, &run,
+                                    &tile_n, &cluster, &band, &k_pieces, &best_ms, &evaluated);
     // The clocks drift while dozens of candidates run, so times taken minutes apart do not compare.  The winner
     // is therefore run again in turns with the rule's own choice, and it replaces the rule only when it is
     // at least 3 % faster on the median of those turns.
@@ -816,15 +819,15 @@ int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K,
         bool ok = true;
         run.reps = 2;
         for (int i = 0; i < 5 && ok; i++) {
-            rule[i] = tune_cost(0, 0, 0, &run);
-            win[i] = tune_cost(tile_n, band, k_pieces, &run);
+            rule[i] = tune_cost(0, 0, 0, 0, &run);
+            win[i] = tune_cost(tile_n, cluster, band, k_pieces, &run);
             ok = rule[i] > 0 && win[i] > 0;
         }
         if (ok) {
             std::sort(win, win + 5);
             std::sort(rule, rule + 5);
             if (win[2] > 0.97 * rule[2]) {  // not clearly better: record the rule itself
-                tile_n = 0; band = 8; k_pieces = 0;
+                tile_n = 0; cluster = 0; band = 8; k_pieces = 0;
                 best_ms = (float) rule[2];
             } else {
                 best_ms = (float) win[2];
@@ -834,11 +837,12 @@ int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K,
     cakeb200_set_option("tile_n", keep[0]);
     cakeb200_set_option("band", keep[1]);
     cakeb200_set_option("k_pieces", keep[2]);
+    cakeb200_set_option("pair", keep[3]);
     if (rc) return run.rc ? run.rc : rc;
     if ((rc = check_status_word(st, run.s))) return rc;
-    if ((rc = cakeb200_tune_put(M, N, K, run.g.order, tile_n, band, k_pieces, best_ms))) return rc;
+    if ((rc = cakeb200_tune_put_shape(M, N, K, run.g.order, tile_n, cluster, band, k_pieces, best_ms))) return rc;
     if (const char* path = getenv("CAKE_AUTOTUNE_CACHE")) cakeb200_tune_save(path);
-    g_stats.tile_m = 128; g_stats.tile_n = tile_n; g_stats.tile_k = 32;
+    g_stats.tile_m = (cluster == 1 || (cluster == 0 && tf32x3_tile_rows(M) == 256)) ? 256 : 128; g_stats.tile_n = tile_n; g_stats.tile_k = 32;
     g_stats.ms_gemm = best_ms;
     g_stats.launches = evaluated;
     g_stats.kernel = CAKEB200_KERNEL_TF32X3;

@@ -60,7 +60,7 @@
 #include "tcgen05.cuh"
 
 namespace cakeb200 {
-bool tune_lookup(int M, int N, int K, int sched, int* tile_n, int* band, int* k_pieces);  // tune.cpp
+bool tune_lookup(int M, int N, int K, int sched, int* tile_n, int* band, int* k_pieces, int* cluster);  // tune.cpp
 
 namespace {
 
@@ -988,6 +988,7 @@ inline int padded_k(int K) { return (K + 3) / 4 * 4; }  // TMA row pitch must be
 // cakeb200_set_option and the tuning cache (resolve_tunables); the rules are what an untuned shape gets.
 struct Tunables {
     int bn = 0, band = 0, pieces = 0, chunk_kb = 0;
+    int pair = 0;  // cluster shape: 1 = pairs of SMs wherever possible, 2 = single SMs
 };
 
 // What applies to one product: an explicit override wins, then the tuning cache's entry for the
@@ -995,11 +996,13 @@ struct Tunables {
 Tunables resolve_tunables(int M, int N, int K, int order) {
     Tunables t;
     t.bn = option_get(OPT_TILE_N); t.band = option_get(OPT_BAND); t.pieces = option_get(OPT_K_PIECES); t.chunk_kb = option_get(OPT_CHUNK_KB);
-    int w = 0, b = 0, p = 0;
-    if (tune_lookup(M, N, K, order, &w, &b, &p)) {
+    t.pair = option_get(OPT_PAIR);
+    int w = 0, b = 0, p = 0, c = 0;
+    if (tune_lookup(M, N, K, order, &w, &b, &p, &c)) {
         if (!t.bn) t.bn = w;
         if (!t.band) t.band = b;
         if (!t.pieces) t.pieces = p;
+        if (!t.pair) t.pair = c;
     }
     return t;
 }
@@ -1009,13 +1012,21 @@ Tunables resolve_tunables(int M, int N, int K, int order) {
 // tiles than SMs leaves most of the machine to the K cut alone, which has little K to cut, and 128-wide
 // tiles then give twice the tiles to spread (measured: 2048^3 0.145 -> 0.117 ms, 1024^3 0.053 -> 0.048 ms;
 // 3000^3 and larger are faster with 256, and so is a deep product with few tiles, 1024 x 262144 x 1024:
-// 2.6 ms against 3.4 ms, because its K cut fills the machine by itself).
-inline int tile_width(int M, int N, int K, int sm_count, const Tunables& t) {
+// 2.6 ms against 3.4 ms, because its K cut fills the machine by itself).  On pairs of SMs (`pair_units` of
+// them, 0 = single-SM form) a product whose 256 x 256 tiles fill at least three quarters of one wave runs
+// them whole, with no cut along K and no reduction (2048^3: 64 tiles on 74 pairs, 0.107 -> 0.099 ms).
+inline int tile_width(int M, int N, int K, int sm_count, const Tunables& t, int pair_units = 0) {
     if ((t.bn == 128 || t.bn == 256) && !(t.bn == 256 && N <= 128)) return t.bn;
     if (N <= 128) return 128;
     const long long wide_tiles = (long long) ((M + BM - 1) / BM) * ((N + 255) / 256);
+    if (pair_units > 0) {
+        const long long pair_tiles = (long long) ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+        if (pair_tiles <= pair_units && pair_tiles * 4 >= 3LL * pair_units) return 256;
+    }
     return (wide_tiles <= sm_count && K <= 4096) ? 128 : 256;
 }
+int pair_clusters();
+bool use_pair(int M, bool owners, int mode);
 
 // Band height of the tile walk.  Tiles that run together should cover a patch of C with
 // few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
@@ -1232,8 +1243,7 @@ int pair_clusters() {
 // Whether a product with M rows runs its tiles on pairs of SMs.  Not for a K-sharded product (its tiles go
 // to their owners in 128-row units), not for a single row of tiles, and under the rule not where padding
 // the rows to 256 instead of 128 would add more than 7 % of work.
-bool use_pair(int M, bool owners) {
-    const int mode = option_get(OPT_PAIR);  // 0 = rule, 1 = wherever possible, 2 = never
+bool use_pair(int M, bool owners, int mode) {  // mode: 0 = rule, 1 = wherever possible, 2 = never
     if (mode == 2 || owners || M <= BM) return false;
     if (pair_clusters() <= 0) return false;
     if (mode == 1) return true;
@@ -1511,8 +1521,9 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
     DevicePlan* plan = nullptr;
     const Tunables tn = resolve_tunables(rows, N, K, order);
-    const int bn = tile_width(p.M, N, K, sm_count, tn);  // of the whole product, so that every band of rows uses one width
-    const bool pair = use_pair(rows, false);
+    const bool pair = use_pair(rows, false, tn.pair);
+    // of the whole product, so that every band of rows uses one width
+    const int bn = tile_width(p.M, N, K, sm_count, tn, use_pair(p.M, false, tn.pair) ? pair_clusters() : 0);
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
         int rc = get_plan((rows + tile_rows(pair) - 1) / tile_rows(pair), (N + bn - 1) / bn, (K + BK - 1) / BK, order,
                           tile_units(pair, sm_count), bn, tn, pair, stream, &plan);
@@ -1528,7 +1539,7 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
 }
 
-int tf32x3_tile_rows(int M) { return tile_rows(use_pair(M, false)); }
+int tf32x3_tile_rows(int M) { return tile_rows(use_pair(M, false, option_get(OPT_PAIR))); }
 
 size_t tf32x3_one_plane_bytes(int rows, int K) { return align_up((size_t) rows * padded_k(K) * 4, 1024); }
 
@@ -1565,7 +1576,8 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
     const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
-    const int bn = tile_width(g.M, g.N, g.K, sm_count, tn);
+    const bool pair = use_pair(g.M, g.owners != nullptr, tn.pair);
+    const int bn = tile_width(g.M, g.N, g.K, sm_count, tn, pair ? pair_clusters() : 0);
     const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);
@@ -1597,7 +1609,6 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     if (prepass_events) CAKE_CUDA_OK(cudaEventRecord(prepass_events[1], stream));
 
     DevicePlan* plan = nullptr;
-    const bool pair = use_pair(g.M, g.owners != nullptr);
     if ((rc = get_plan((g.M + tile_rows(pair) - 1) / tile_rows(pair), (g.N + bn - 1) / bn, (g.K + BK - 1) / BK, g.order,
                        tile_units(pair, sm_count), bn, tn, pair, stream, &plan)))
         return rc;
@@ -1761,7 +1772,7 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
     // whole-K tiles only: cutting tiles along K would need slots for partial tiles, i.e. more scratch
-    rc = launch_as(N > 128 ? 256 : 128, use_pair(M, false), g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr,
+    rc = launch_as(N > 128 ? 256 : 128, use_pair(M, false, option_get(OPT_PAIR)), g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr,
                    Tunables());
     if (rc) return rc;
     int word[4] = {0, 0, 0, 0};

@@ -178,7 +178,8 @@ int cakeb200_sgemm_planes(const cakeb200_planes* A_planes, const float* A, const
  * Replaces the reference's block-size autotuner (reference src/autotune_sa.cpp:13-82 and
  * include/autotune.h:82-86: random-step search over (m_c, k_c, n_c) with a visited set; dead
  * code there, not compiled by its Makefile).  On a GPU the blocks worth searching are the tile
- * width, the band height of the tile walk and the cut of the last wave's tiles along K.
+ * width, the cluster shape (one or two CTAs per tile), the band height of the tile walk and the
+ * cut of the last wave's tiles along K.
  *
  * cakeb200_tune times the large-matrix kernel on the caller's operands (device pointers; C is
  * overwritten with the product every time) at up to `trials` points of that grid, walking it by
@@ -199,6 +200,16 @@ int cakeb200_sgemm_planes(const cakeb200_planes* A_planes, const float* A, const
  * milliseconds (<= 0: not a valid point) and may be anything, which is how the search is tested
  * without a device. */
 typedef double (*cakeb200_tune_cost)(int tile_n, int band, int k_pieces, void* user);
+/* The _shape forms add the cluster shape to the grid: `cluster` 1 = the two CTAs of a thread-block
+ * cluster on one 256-row tile (a pair of SMs), 2 = one CTA per 128-row tile, 0 = the library's rule
+ * (the "pair" option has the same values).  cakeb200_tune searches and records all four choices;
+ * the forms without _shape leave the cluster shape to the rule. */
+typedef double (*cakeb200_tune_cost_shape)(int tile_n, int cluster, int band, int k_pieces, void* user);
+int cakeb200_tune_search_shape(int M, int N, int K, int sm_count, int trials, unsigned long long seed,
+                               cakeb200_tune_cost_shape cost, void* user, int* tile_n, int* cluster, int* band,
+                               int* k_pieces, float* best_ms, int* evaluated);
+int cakeb200_tune_put_shape(int M, int N, int K, int sched, int tile_n, int cluster, int band, int k_pieces, float ms);
+int cakeb200_tune_get_shape(int M, int N, int K, int sched, int* tile_n, int* cluster, int* band, int* k_pieces, float* ms);
 int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K, int sched, int trials, void* stream);
 int cakeb200_tune_search(int M, int N, int K, int sm_count, int trials, unsigned long long seed, cakeb200_tune_cost cost,
                          void* user, int* tile_n, int* band, int* k_pieces, float* best_ms, int* evaluated);

@@ -19,7 +19,8 @@ def test_cache_round_trips_through_a_file(cake, tmp_path):
     path = tmp_path / "tune.json"
     assert cake.tune_save(path) == 2
     text = json.loads(path.read_text())  # the file is JSON
-    assert text["version"] == 1 and len(text["entries"]) == 2
+    assert text["version"] == 2 and len(text["entries"]) == 2
+    assert all(e["cluster"] == 0 for e in text["entries"])  # the cluster shape was left to the rule
     cake.tune_clear()
     assert cake.tune_get(3000, 3000, 3000, cake.MKN) is None
     assert cake.tune_load(path) == 2
@@ -73,6 +74,49 @@ def test_random_step_search_finds_the_cheapest_point(cake):
     assert {w for w, _, _ in seen} == {128}
 
 
+def test_cluster_shape_is_part_of_an_entry_and_of_the_search(cake, tmp_path):
+    """The cluster shape (1 = the two CTAs of a cluster on a 256-row tile, 2 = one CTA per 128-row tile) is recorded
+    with the tile shape, survives the file, defaults to the rule (0) in a file written without it, and is an axis
+    of the search."""
+    cake.tune_clear()
+    cake.tune_put(8192, 8192, 8192, cake.KMN, 256, 8, 0, 3.6, cluster=1)
+    cake.tune_put(300, 4096, 4096, cake.MKN, 256, 8, 2, 0.1, cluster=2)
+    assert cake.tune_get(8192, 8192, 8192, cake.KMN)["cluster"] == 1
+    path = tmp_path / "shapes.json"
+    assert cake.tune_save(path) == 2
+    cake.tune_clear()
+    assert cake.tune_load(path) == 2
+    assert cake.tune_get(300, 4096, 4096, cake.MKN)["cluster"] == 2
+    with pytest.raises(cake.CakeError):
+        cake.tune_put(10, 10, 10, cake.KMN, 128, 8, 0, cluster=3)
+    old = tmp_path / "old.json"
+    old.write_text('{"version": 1, "kernel": "sgemm_tf32x3", "entries": [\n'
+                   '  {"M": 512, "N": 512, "K": 512, "sched": 0, "tile_n": 128, "band": 4, "k_pieces": 2, "ms": 0.020000}\n]}\n')
+    cake.tune_clear()
+    assert cake.tune_load(old) == 1
+    got = cake.tune_get(512, 512, 512, cake.KMN)
+    assert (got["tile_n"], got["cluster"], got["band"], got["k_pieces"]) == (128, 0, 4, 2)
+    cake.tune_clear()
+
+    seen = []
+
+    def cost(tile_n, cluster, band, k_pieces):
+        seen.append((tile_n, cluster, band, k_pieces))
+        return 1.0 + (0.5 if cluster == 1 else 0.0) + abs(tile_n - 256) / 256.0 + abs(band - 16) * 0.01 + k_pieces * 0.01
+
+    got = cake.tune_search_shape(4096, 4096, 4096, cost, trials=400, seed=5)
+    assert len(seen) == len(set(seen)) == got["evaluated"]
+    assert seen[0] == (256, 1, 8, 0)  # the rule: wide tile on pairs of SMs, bands of 8, the library's own cut
+    assert (got["tile_n"], got["cluster"], got["band"], got["k_pieces"]) == (256, 2, 16, 0)
+    # a single row of tiles has nothing to pair, and 300 rows would be padded to 512: the rule starts from single SMs
+    seen.clear()
+    cake.tune_search_shape(100, 4096, 4096, cost, trials=500)
+    assert {c for _, c, _, _ in seen} == {2}
+    seen.clear()
+    cake.tune_search_shape(300, 4096, 4096, cost, trials=3)
+    assert seen[0][1] == 2
+
+
 @pytest.mark.gpu
 def test_search_on_the_device_records_a_winner_that_later_products_use(cake):
     import torch
@@ -86,6 +130,7 @@ def test_search_on_the_device_records_a_winner_that_later_products_use(cake):
     before = C.clone()
     entry = cake.tune(A, B, C, trials=12)
     assert entry["evaluated"] == 12 and entry["tile_n"] in (0, 128, 256) and entry["ms"] > 0  # 0: the rule was not beaten
+    assert entry["cluster"] in (0, 1, 2)
     sched = cake.last_stats()["sched"]
     assert cake.tune_get(M, N, K, sched) is not None
     # the product with the tuned shape is still the product
@@ -96,5 +141,5 @@ def test_search_on_the_device_records_a_winner_that_later_products_use(cake):
     assert ((C[:64].double() - exact).abs() / den).max().item() <= 1e-5
     assert ((before[:64].double() - exact).abs() / den).max().item() <= 1e-5
     # options were restored by the search
-    assert [cake.get_option(k) for k in ("tile_n", "band", "k_pieces")] == [0, 0, 0]
+    assert [cake.get_option(k) for k in ("tile_n", "band", "k_pieces", "pair")] == [0, 0, 0, 0]
     cake.tune_clear()
