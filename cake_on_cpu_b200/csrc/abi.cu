@@ -312,7 +312,7 @@ int sgemm_host_pipelined(DeviceState* st, const float* A, const float* B, float*
 
     // bands of whole tiles (128 rows, or 256 where the tensor-core kernel runs on pairs of SMs); enough of
     // them that the first and last are short
-    const int tile_rows = (kernel == CAKEB200_KERNEL_TF32X3) ? tf32x3_tile_rows(M) : 128;
+    const int tile_rows = (kernel == CAKEB200_KERNEL_TF32X3) ? tf32x3_tile_rows(M, N, K, g.order, st->sm_count) : 128;
     const int tiles = (M + tile_rows - 1) / tile_rows;
     const int bands = std::max(1, std::min(std::min(DeviceState::MAX_BANDS, 16), tiles / 2));
     CAKE_CUDA_OK(cudaEventRecord(st->ev[0], s));
@@ -842,7 +842,7 @@ int cakeb200_tune(const float* A, const float* B, float* C, int M, int N, int K,
     if ((rc = check_status_word(st, run.s))) return rc;
     if ((rc = cakeb200_tune_put_shape(M, N, K, run.g.order, tile_n, cluster, band, k_pieces, best_ms))) return rc;
     if (const char* path = getenv("CAKE_AUTOTUNE_CACHE")) cakeb200_tune_save(path);
-    g_stats.tile_m = (cluster == 1 || (cluster == 0 && tf32x3_tile_rows(M) == 256)) ? 256 : 128; g_stats.tile_n = tile_n; g_stats.tile_k = 32;
+    g_stats.tile_m = (cluster == 1 || (cluster == 0 && tf32x3_tile_rows(M, N, K, run.g.order, st->sm_count) == 256)) ? 256 : 128; g_stats.tile_n = tile_n; g_stats.tile_k = 32;
     g_stats.ms_gemm = best_ms;
     g_stats.launches = evaluated;
     g_stats.kernel = CAKEB200_KERNEL_TF32X3;

@@ -142,8 +142,8 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
 // hi / lo planes of one operand, for callers that keep an operand split across many products (weights):
 // bytes of one plane and the split itself (transpose: `mat` is K x rows row-major, as B is; else rows x K)
 size_t tf32x3_one_plane_bytes(int rows, int K);
-// rows of C per tile for a product with M rows: 256 where it runs on pairs of SMs, else 128
-int tf32x3_tile_rows(int M);
+// rows of C per tile of a product: 256 where it runs on pairs of SMs, else 128
+int tf32x3_tile_rows(int M, int N, int K, int order, int sm_count);
 int tf32x3_make_planes(const float* mat, int rows, int K, int ld, bool transpose, float* hi, float* lo, int sm_count,
                        cudaStream_t stream);
 // true when the tile plan of this shape cuts every tile into K pieces, so that the kernel that sums the

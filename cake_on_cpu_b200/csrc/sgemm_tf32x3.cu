@@ -1027,6 +1027,10 @@ inline int tile_width(int M, int N, int K, int sm_count, const Tunables& t, int 
 }
 int pair_clusters();
 bool use_pair(int M, bool owners, int mode);
+// With 128-wide tiles an MMA of either form is bound by its issue, not by shared memory, and the single-SM
+// form spreads twice as many tiles: 1 to 6 % faster on the shapes that get narrow tiles (1024^3: 0.0351
+// against 0.0372 ms).  Under the rule pairs are therefore for 256-wide tiles.
+inline bool pair_pays(int bn, int mode) { return mode == 1 || bn == 256; }
 
 // Band height of the tile walk.  Tiles that run together should cover a patch of C with
 // few distinct A and B panels; 8 rows (or columns) per band measured best on the square,
@@ -1521,9 +1525,9 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     float* a_lo = p.a_lo + (size_t) r0 * p.Kp;
     DevicePlan* plan = nullptr;
     const Tunables tn = resolve_tunables(rows, N, K, order);
-    const bool pair = use_pair(rows, false, tn.pair);
     // of the whole product, so that every band of rows uses one width
     const int bn = tile_width(p.M, N, K, sm_count, tn, use_pair(p.M, false, tn.pair) ? pair_clusters() : 0);
+    const bool pair = use_pair(rows, false, tn.pair) && pair_pays(bn, tn.pair);
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
         int rc = get_plan((rows + tile_rows(pair) - 1) / tile_rows(pair), (N + bn - 1) / bn, (K + BK - 1) / BK, order,
                           tile_units(pair, sm_count), bn, tn, pair, stream, &plan);
@@ -1539,7 +1543,12 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
     return 2 * a + 2 * b + partial_slot_bytes(sm_count) + 2048;
 }
 
-int tf32x3_tile_rows(int M) { return tile_rows(use_pair(M, false, option_get(OPT_PAIR))); }
+int tf32x3_tile_rows(int M, int N, int K, int order, int sm_count) {
+    const Tunables tn = resolve_tunables(M, N, K, order);
+    const bool by_rows = use_pair(M, false, tn.pair);
+    const int bn = tile_width(M, N, K, sm_count, tn, by_rows ? pair_clusters() : 0);
+    return tile_rows(by_rows && pair_pays(bn, tn.pair));
+}
 
 size_t tf32x3_one_plane_bytes(int rows, int K) { return align_up((size_t) rows * padded_k(K) * 4, 1024); }
 
@@ -1576,8 +1585,9 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
     const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
-    const bool pair = use_pair(g.M, g.owners != nullptr, tn.pair);
-    const int bn = tile_width(g.M, g.N, g.K, sm_count, tn, pair ? pair_clusters() : 0);
+    const bool by_rows = use_pair(g.M, g.owners != nullptr, tn.pair);
+    const int bn = tile_width(g.M, g.N, g.K, sm_count, tn, by_rows ? pair_clusters() : 0);
+    const bool pair = by_rows && pair_pays(bn, tn.pair);
     const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
     if (need > scratch_bytes) {
         set_error("sgemm_tf32x3: scratch too small (%zu < %zu)", scratch_bytes, need);

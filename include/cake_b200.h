@@ -142,8 +142,8 @@ int cakeb200_sgemm_after(const float* A, const float* B, float* C, int M, int N,
  *   "pack_scalar" 1 = pack / unpack move one element per thread instead of 16 bytes.
  *   "pair"      form of the large-matrix tensor-core kernels: 1 = 256-row tiles on pairs of SMs
  *               (tcgen05 cta_group::2) wherever the product has more than 128 rows, 2 = always one
- *               CTA per 128-row tile; rule: pairs unless padding M to a multiple of 256 instead of
- *               128 adds more than 7 % of rows.  Both forms give the same bits when no tile is
+ *               CTA per 128-row tile; rule: pairs for 256-wide tiles, unless padding M to a multiple
+ *               of 256 instead of 128 adds more than 7 % of rows.  Both forms give the same bits when no tile is
  *               cut along K ("k_pieces" 1).
  * They take the place of the block sizes a caller of the reference forces with mcu / kcu / ncu
  * (reference include/cake.h:12-14, src/block_sizing.cpp:363-368) and of update_mr_nr
