@@ -92,6 +92,7 @@ _SIGNATURES["cakeb200_profile_end"] = (_i, [ctypes.POINTER(ctypes.c_float), ctyp
 _SIGNATURES["cakeb200_sgemm_ex"] = (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp])
 _SIGNATURES["cakeb200_conv_plan_query"] = (_i, [_i] * 10 + [ctypes.POINTER(ConvPlan)])
 _SIGNATURES["cakeb200_selftest_bounded_wait"] = (_i, [_i, _vp])
+_SIGNATURES["cakeb200_selftest_bounded_wait_pair"] = (_i, [_i, _vp])
 _pi = ctypes.POINTER(_i)
 _SIGNATURES["cakeb200_kshard_rows"] = (_i, [_i, _i, _i, _pi, _pi])
 _SIGNATURES["cakeb200_kshard_supported"] = (_i, [_i, _i, _i, _i])

@@ -956,7 +956,13 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
     return CAKEB200_OK;
 }
 
-int cakeb200_selftest_bounded_wait(int limit_us, void* stream) {
+namespace {
+int selftest_bounded_wait(int limit_us, void* stream, bool pair);
+}
+int cakeb200_selftest_bounded_wait(int limit_us, void* stream) { return selftest_bounded_wait(limit_us, stream, false); }
+int cakeb200_selftest_bounded_wait_pair(int limit_us, void* stream) { return selftest_bounded_wait(limit_us, stream, true); }
+namespace {
+int selftest_bounded_wait(int limit_us, void* stream, bool pair) {
     g_stats = cakeb200_stats();
     if (limit_us < 1 || limit_us > 1000000) {
         set_error("limit must be between 1 us and 1 s");
@@ -965,10 +971,11 @@ int cakeb200_selftest_bounded_wait(int limit_us, void* stream) {
     DeviceState* st = device_state();
     if (!st) return CAKEB200_ERR_NO_DEVICE;
     cudaStream_t s = (cudaStream_t) stream;
-    int rc = launch_bounded_wait_selftest(st->status_word, limit_us, s);
+    int rc = launch_bounded_wait_selftest(st->status_word, limit_us, s, pair);
     if (rc) return rc;
-    return check_status_word(st, s);  // expected: CAKEB200_ERR_DEVICE_TIMEOUT, "where" 900
+    return check_status_word(st, s);  // expected: CAKEB200_ERR_DEVICE_TIMEOUT, "where" 900 (901 for the pair)
 }
+}  // namespace
 
 // ---- K-sharded product over the GPUs of one box: exchange object
 

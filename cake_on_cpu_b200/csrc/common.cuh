@@ -95,7 +95,7 @@ int ensure_scratch(DeviceState* st, size_t bytes);
 int launch_sgemm_ffma(const GemmProblem& g, cudaStream_t stream);  // untransposed operands only
 int launch_transpose_copy(const float* src, float* dst, int rows, int cols, int ld_src, cudaStream_t stream);
 // one CTA runs a bounded wait that must give up (sgemm_tf32x3.cu)
-int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream);
+int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream, bool pair = false);
 // Process-wide overrides set through cakeb200_set_option (abi.cu); 0 = the library's own rule.
 enum Option { OPT_TILE_N, OPT_BAND, OPT_K_PIECES, OPT_CHUNK_KB, OPT_CONV_ROUTE, OPT_SMALL_OPERANDS, OPT_PACK_SCALAR, OPT_PAIR, OPT_COUNT };
 int option_get(int id);

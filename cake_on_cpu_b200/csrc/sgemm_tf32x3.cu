@@ -1655,9 +1655,40 @@ __global__ void bounded_wait_selftest_kernel(int* status_word, long long limit_n
     if (threadIdx.x == 0) mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status_word, 900, limit_ns);
     __syncthreads();
 }
+// The same for a pair of CTAs: the leader waits for an arrival that its peer would send to the leader's barrier
+// and never does (as if the peer's drain warps had stalled).  The leader gives up, and both CTAs still meet
+// at the cluster barrier that ends every pair kernel, so neither leaves while the other could touch it.
+__global__ void __launch_bounds__(32) bounded_wait_pair_selftest_kernel(int* status_word, long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    const uint32_t rank = cluster_ctarank();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 2);  // one arrival from each CTA; only the leader's own ever comes
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cluster_sync_all();
+    if (threadIdx.x == 0 && rank == 0) {
+        mbar_arrive_leader(smem_u32(&bar));
+        mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status_word, 901, limit_ns);
+    }
+    cluster_sync_all();
+}
 }  // namespace
 
-int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream) {
+int launch_bounded_wait_selftest(int* status_word, int limit_us, cudaStream_t stream, bool pair) {
+    if (pair) {
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2);
+        cfg.blockDim = dim3(32);
+        cfg.stream = stream;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        CAKE_CUDA_OK(cudaLaunchKernelEx(&cfg, bounded_wait_pair_selftest_kernel, status_word, (long long) limit_us * 1000));
+        return CAKEB200_OK;
+    }
     bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status_word, (long long) limit_us * 1000);
     CAKE_CUDA_OK(cudaGetLastError());
     return CAKEB200_OK;

@@ -269,6 +269,10 @@ int cakeb200_sgemm_batched(const float* A, const float* B, float* C, int M, int 
  * context stays usable.  (The reference stops the process with exit(1) on its errors,
  * reference src/cake_sgemm.cpp:49-52.) */
 int cakeb200_selftest_bounded_wait(int limit_us, void* stream);
+/* The same for the kernels that run on pairs of SMs: in a cluster of two CTAs the leader waits for
+ * an arrival its peer never sends, gives up after `limit_us` ("where 901"), and both CTAs still
+ * leave through the cluster barrier that ends those kernels. */
+int cakeb200_selftest_bounded_wait_pair(int limit_us, void* stream);
 
 /* ---- One product with K sharded over the GPUs of one box, one process per GPU.
  *

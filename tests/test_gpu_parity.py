@@ -517,6 +517,20 @@ def test_a_stalled_wait_gives_up_and_the_context_survives(cake, oracle):
     for kernel in (cake.KERNEL_TF32X3, cake.KERNEL_FFMA):
         assert rel_err(cake.cake_sgemm(A, B, kernel=kernel), ref, A, B) <= TOL
     assert cake.lib().cakeb200_selftest_bounded_wait(0, None) == -1  # argument error, nothing launched
+    # the same in a cluster of two CTAs: the leader waits for an arrival of its peer that never comes
+    t0 = time.perf_counter()
+    rc = cake.lib().cakeb200_selftest_bounded_wait_pair(2000, None)
+    waited = time.perf_counter() - t0
+    assert rc == -4, rc
+    assert b"where 901" in cake.lib().cakeb200_last_error()
+    assert 0.0015 <= waited < 0.5, waited
+    big = oracle.uniform((512, 256), 3), oracle.uniform((256, 512), 4)
+    ref, _ = oracle.sgemm(big[0], big[1], 8, NA)
+    cake.set_option("pair", 1)
+    try:
+        assert rel_err(cake.cake_sgemm(*big, kernel=cake.KERNEL_TF32X3), ref, *big) <= TOL
+    finally:
+        cake.set_option("pair", 0)
 
 
 def test_errors_are_status_codes(cake):
