@@ -98,7 +98,7 @@ struct Cfg {
     static constexpr int SMEM_BYTES_CHUNKED = SMEM_BYTES + (EPI_WARPS - 4) * 32 * 32 * 4;  // eight patches
 };
 
-// Work of one CTA: first whole tiles taken round-robin (tile = blockIdx.x + i * gridDim.x
+// Work of one unit (a CTA, or a pair of CTAs): first whole tiles taken round-robin (tile = unit + i * units
 // for tiles below dp_tiles), then the K-range pieces listed for it in `units`.  A piece
 // that covers only part of K stores its accumulator in a slot of `partials`; a separate
 // kernel adds the slots of each tile up in a fixed order.
@@ -107,7 +107,7 @@ struct Tf32x3Args {
     float* partials;         // [slot][BM x BN]; in a pair the odd CTA's halves follow at slot + slot_count
     int slot_count;
     const int4* units;       // {tile, first k-block, end k-block, slot or -1 = whole K, store to C}
-    const int* cta_begin;    // units of CTA b are [cta_begin[b], cta_begin[b + 1])
+    const int* cta_begin;    // pieces of unit b are [cta_begin[b], cta_begin[b + 1])
     int dp_tiles;
     int M, N, K;
     int ldc;
