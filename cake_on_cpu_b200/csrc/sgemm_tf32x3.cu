@@ -1026,7 +1026,7 @@ inline int tile_width(int M, int N, int K, int sm_count, const Tunables& t, int 
     return (wide_tiles <= sm_count && K <= 4096) ? 128 : 256;
 }
 int pair_clusters();
-bool use_pair(int M, bool owners, int mode);
+bool use_pair(int M, int mode);
 // With 128-wide tiles an MMA of either form is bound by its issue, not by shared memory, and the single-SM
 // form spreads twice as many tiles: 1 to 6 % faster on the shapes that get narrow tiles (1024^3: 0.0351
 // against 0.0372 ms).  Under the rule pairs are therefore for 256-wide tiles.
@@ -1244,11 +1244,10 @@ int pair_clusters() {
     return cached[dev] > 0 ? cached[dev] : 0;
 }
 
-// Whether a product with M rows runs its tiles on pairs of SMs.  Not for a K-sharded product (its tiles go
-// to their owners in 128-row units), not for a single row of tiles, and under the rule not where padding
-// the rows to 256 instead of 128 would add more than 7 % of work.
-bool use_pair(int M, bool owners, int mode) {  // mode: 0 = rule, 1 = wherever possible, 2 = never
-    if (mode == 2 || owners || M <= BM) return false;
+// Whether a product with M rows runs its tiles on pairs of SMs.  Not for a single row of tiles, and under
+// the rule not where padding the rows to 256 instead of 128 would add more than 7 % of work.
+bool use_pair(int M, int mode) {  // mode: 0 = rule, 1 = wherever possible, 2 = never
+    if (mode == 2 || M <= BM) return false;
     if (pair_clusters() <= 0) return false;
     if (mode == 1) return true;
     const long long p256 = (M + 2 * BM - 1) / (2 * BM) * (2LL * BM), p128 = (M + BM - 1) / BM * (long long) BM;
@@ -1526,8 +1525,8 @@ int tf32x3_multiply_rows(const Tf32x3Planes& p, float* C, int ldc, int r0, int r
     DevicePlan* plan = nullptr;
     const Tunables tn = resolve_tunables(rows, N, K, order);
     // of the whole product, so that every band of rows uses one width
-    const int bn = tile_width(p.M, N, K, sm_count, tn, use_pair(p.M, false, tn.pair) ? pair_clusters() : 0);
-    const bool pair = use_pair(rows, false, tn.pair) && pair_pays(bn, tn.pair);
+    const int bn = tile_width(p.M, N, K, sm_count, tn, use_pair(p.M, tn.pair) ? pair_clusters() : 0);
+    const bool pair = use_pair(rows, tn.pair) && pair_pays(bn, tn.pair);
     if (p.partials && r0 == 0 && rows == p.M) {  // the whole product at once: balance its tiles
         int rc = get_plan((rows + tile_rows(pair) - 1) / tile_rows(pair), (N + bn - 1) / bn, (K + BK - 1) / BK, order,
                           tile_units(pair, sm_count), bn, tn, pair, stream, &plan);
@@ -1545,7 +1544,7 @@ size_t tf32x3_scratch_bytes(int M, int N, int K, int sm_count) {
 
 int tf32x3_tile_rows(int M, int N, int K, int order, int sm_count) {
     const Tunables tn = resolve_tunables(M, N, K, order);
-    const bool by_rows = use_pair(M, false, tn.pair);
+    const bool by_rows = use_pair(M, tn.pair);
     const int bn = tile_width(M, N, K, sm_count, tn, by_rows ? pair_clusters() : 0);
     return tile_rows(by_rows && pair_pays(bn, tn.pair));
 }
@@ -1560,11 +1559,15 @@ int tf32x3_make_planes(const float* mat, int rows, int K, int ld, bool transpose
 
 bool tf32x3_all_tiles_in_pieces(int M, int N, int K, int order, int sm_count) {
     if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return false;
+    // the same choices as launch_sgemm_tf32x3 makes for this shape
     const Tunables tn = resolve_tunables(M, N, K, order);
-    const int bn = tile_width(M, N, K, sm_count, tn), kblocks = (K + BK - 1) / BK;
-    const long long tiles = (long long) ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-    if (tiles >= sm_count) return false;
-    const HostPlan hp = build_plan((M + BM - 1) / BM, (N + bn - 1) / bn, kblocks, order, sm_count, tn, false);
+    const bool by_rows = use_pair(M, tn.pair);
+    const int bn = tile_width(M, N, K, sm_count, tn, by_rows ? pair_clusters() : 0), kblocks = (K + BK - 1) / BK;
+    const bool pair = by_rows && pair_pays(bn, tn.pair);
+    const int tm = (M + tile_rows(pair) - 1) / tile_rows(pair), units = tile_units(pair, sm_count);
+    const long long tiles = (long long) tm * ((N + bn - 1) / bn);
+    if (tiles >= units) return false;
+    const HostPlan hp = build_plan(tm, (N + bn - 1) / bn, kblocks, order, units, tn, pair);
     return hp.dp_tiles == 0 && !hp.pieces.empty();
 }
 
@@ -1585,7 +1588,7 @@ int launch_sgemm_tf32x3(const GemmProblem& g, void* scratch, size_t scratch_byte
     float* partials = (float*) (base + 2 * a_bytes + 2 * b_bytes);
 
     const Tunables tn = resolve_tunables(g.M, g.N, g.K, g.order);
-    const bool by_rows = use_pair(g.M, g.owners != nullptr, tn.pair);
+    const bool by_rows = use_pair(g.M, tn.pair);
     const int bn = tile_width(g.M, g.N, g.K, sm_count, tn, by_rows ? pair_clusters() : 0);
     const bool pair = by_rows && pair_pays(bn, tn.pair);
     const size_t need = 2 * a_bytes + 2 * b_bytes + partial_slot_bytes(sm_count) + 1024;
@@ -1813,7 +1816,8 @@ extern "C" int cakeb200_sgemm_noalloc(const float* A, const float* B, float* C, 
     g.batch = 1;
     g.order = CAKEB200_SCHED_KMN;
     // whole-K tiles only: cutting tiles along K would need slots for partial tiles, i.e. more scratch
-    rc = launch_as(N > 128 ? 256 : 128, use_pair(M, false, option_get(OPT_PAIR)), g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr,
+    const int bn_na = N > 128 ? 256 : 128, mode_na = option_get(OPT_PAIR);
+    rc = launch_as(bn_na, use_pair(M, mode_na) && pair_pays(bn_na, mode_na), g, a_hi, a_lo, b_hi, b_lo, nullptr, nullptr, status_word, sm_count, s, nullptr,
                    Tunables());
     if (rc) return rc;
     int word[4] = {0, 0, 0, 0};
