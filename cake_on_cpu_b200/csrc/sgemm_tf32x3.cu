@@ -127,8 +127,10 @@ struct Tf32x3Args {
 // Timeline of CTA 0 (diagnostic build only, -DCAKEB200_ROLE_TIMERS): nanosecond stamps in status_word[16 + 2 * slot].
 #ifdef CAKEB200_ROLE_TIMERS
 #define STAMP(slot) do { if (blockIdx.x == 0) ((unsigned long long*) (args.status_word + 16))[slot] = global_ns(); } while (0)
+#define STAMP_CYCLES(slot) do { if (blockIdx.x == 0) ((unsigned long long*) (args.status_word + 16))[slot] = (unsigned long long) clock64(); } while (0)
 #else
 #define STAMP(slot)
+#define STAMP_CYCLES(slot)
 #endif
 
 struct WorkPiece {
@@ -266,7 +268,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 for (int kb = kb0; kb < kb1; kb++) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
                     if (!ok) break;
-                    if (local == 0 && kb == kb0) STAMP(2);
+                    if (local == 0 && kb == kb0) { STAMP(2); STAMP_CYCLES(9); }
                     tcgen05_fence_after();
                     const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
                     const uint64_t a_hi = make_kmajor_sw128_desc(base);
@@ -287,7 +289,7 @@ sgemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 }
                 if (!ok) break;
                 umma_commit_t<PAIR>(acc_full_bar(buf));  // accumulator complete
-                STAMP(3);
+                STAMP(3); STAMP_CYCLES(10);
             }
         }
     } else {
@@ -526,7 +528,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                     for (int kb = kb0; kb < kb1; kb++) {
                         ok = mbar_wait(full_bar(stage), phase, abort_flag, args.status_word, 300 + stage);
                         if (!ok) break;
-                        if (local == 0 && ci == 0 && kb == kb0) STAMP(2);
+                        if (local == 0 && ci == 0 && kb == kb0) { STAMP(2); STAMP_CYCLES(9); }
                         tcgen05_fence_after();
                         const uint32_t base = smem_u32(tiles + stage * C_::STAGE_BYTES);
                         const uint64_t a_hi = make_kmajor_sw128_desc(base);
@@ -547,7 +549,7 @@ sgemm_tf32x3_chunked_kernel(const __grid_constant__ CUtensorMap map_a_hi, const 
                     }
                     if (!ok) break;
                     umma_commit_t<PAIR>(acc_full_bar(buf));  // chunk complete
-                    STAMP(3);
+                    STAMP(3); STAMP_CYCLES(10);
                 }
             }
         }
@@ -1295,13 +1297,13 @@ cudaError_t run_kernel(bool chunked, int grid_units, cudaStream_t stream, const 
 
 #ifdef CAKEB200_ROLE_TIMERS
 void print_timeline(int* status_word, cudaStream_t stream, bool chunked) {
-    unsigned long long h[10];
+    unsigned long long h[12];
     cudaStreamSynchronize(stream);
     cudaMemcpy(h, status_word + 16, sizeof(h), cudaMemcpyDeviceToHost);
     fprintf(stderr, "K1 %s timeline of CTA 0 (us after entry): ready %.2f, first MMA %.2f, last commit %.2f, last acc_full seen %.2f, "
-            "drain warp 2 done %.2f, drain warp 4 done %.2f, thread 0 at exit %.2f, after final sync %.2f\n", chunked ? "chunked" : "plain",
+            "drain warp 2 done %.2f, drain warp 4 done %.2f, thread 0 at exit %.2f, after final sync %.2f; first MMA to last commit %llu cycles\n", chunked ? "chunked" : "plain",
             (h[1] - h[0]) * 1e-3, (h[2] - h[0]) * 1e-3, (h[3] - h[0]) * 1e-3, (h[4] - h[0]) * 1e-3, (h[5] - h[0]) * 1e-3,
-            (h[6] - h[0]) * 1e-3, (h[7] - h[0]) * 1e-3, (h[8] - h[0]) * 1e-3);
+            (h[6] - h[0]) * 1e-3, (h[7] - h[0]) * 1e-3, (h[8] - h[0]) * 1e-3, h[10] - h[9]);
 }
 #endif
 
