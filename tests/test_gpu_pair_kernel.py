@@ -117,3 +117,24 @@ def test_pair_kernel_full_size(pair_options):
     exact = A[rows].double() @ B.double()
     den = A[rows].double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
     assert ((out[1][rows].double() - exact).abs() / den).max().item() <= TOL
+
+
+def test_pair_kernel_stores_a_convolution_output(pair_options, oracle):
+    """The im2col route of the convolution multiplies filters (rows = output channels) by the patch matrix and
+    stores straight to NCHW from the epilogue; forced onto pairs of SMs it must agree with the implicit kernel."""
+    cake = pair_options
+    x, w = oracle.normal((3, 40, 12, 12), 4, 0.1), oracle.normal((300, 40, 3, 3), 5, 0.1)
+    implicit = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
+    cake.set_option("conv_route", 1)
+    cake.set_option("pair", 1)
+    try:
+        paired = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
+        cake.set_option("pair", 2)
+        single = cake.cake_conv2d(x, w, 1, 1, kernel=cake.KERNEL_TF32X3)
+    finally:
+        cake.set_option("conv_route", 0)
+    col = oracle.im2col(x, 3, 3, 1, 1)
+    flat = lambda t: t.transpose(1, 0, 2, 3).reshape(300, -1)
+    assert rel_err(flat(paired), flat(implicit), w.reshape(300, -1), col) <= TOL
+    assert rel_err(flat(paired), flat(single), w.reshape(300, -1), col) <= TOL
+

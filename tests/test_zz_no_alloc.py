@@ -110,3 +110,28 @@ print('RESULT', int(torch.equal(C1, C2)), int(free_after >= free_before), err)
     assert line, r.stderr[-2000:]
     same, no_new_memory, err = line[0].split()[1:]
     assert same == "1" and no_new_memory == "1" and float(err) <= TOL
+
+
+def test_no_alloc_entry_point_on_pairs_of_sms(cake):
+    """The same entry point with its tiles forced onto pairs of SMs (256-row tiles) and onto single SMs: the same
+    bits, no allocation either way."""
+    import torch
+    M, K, N = 768, 512, 1024
+    g = torch.Generator(device="cuda").manual_seed(8)
+    A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
+    B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
+    out = {}
+    try:
+        for pair in (1, 2, 1):
+            cake.set_option("pair", pair)
+            C = torch.full((M, N), float("nan"), device="cuda")
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            cake.cake_sgemm_noalloc(A, B, C)
+            if pair in out:  # the first call of either form may load its kernels; the repeat may not take memory
+                assert torch.cuda.mem_get_info()[0] >= free_before
+            out[pair] = C
+    finally:
+        cake.set_option("pair", 0)
+    assert torch.equal(out[1], out[2])
+    assert _norm_err(out[1], A.double() @ B.double(), A, B) <= TOL
