@@ -61,6 +61,27 @@ def test_pair_kernel_with_tiles_cut_along_k(pair_options, oracle, shape):
         assert rel_err(C, exact, A, B) <= TOL, (pair, shape)
 
 
+def test_pair_kernel_with_an_empty_k_piece(pair_options):
+    """Sixteen slices of K cut into five pieces of four leave the last piece empty: it still hands an accumulator
+    over (zeros), in both CTAs of the pair."""
+    import torch
+    cake = pair_options
+    M, K, N = 512, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(9)
+    A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
+    B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
+    exact = A.double() @ B.double()
+    den = A.double().norm(dim=1)[:, None] * B.double().norm(dim=0)[None, :]
+    for pair in (1, 2):
+        for tile_n in (128, 256):
+            for name, v in (("pair", pair), ("chunk_kb", UNBROKEN), ("k_pieces", 5), ("tile_n", tile_n)):
+                cake.set_option(name, v)
+            C = torch.full((M, N), float("nan"), device="cuda")
+            cake.cake_sgemm(A, B, C, kernel=cake.KERNEL_TF32X3)
+            assert cake.last_stats()["launches"] == 4  # two splits, the product, the sum of the pieces
+            assert ((C.double() - exact).abs() / den).max().item() <= TOL, (pair, tile_n)
+
+
 @pytest.mark.parametrize("sch", [KMN, MKN, NKM])
 def test_pair_kernel_every_schedule(pair_options, oracle, sch):
     cake = pair_options
